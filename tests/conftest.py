@@ -1,0 +1,79 @@
+"""Shared pytest configuration.
+
+Markers:
+  gpu -- needs a CUDA device (the parity tests proper; they call the CUDA kernels
+         through the C-ABI). Everything else runs on CPU only.
+"""
+import json
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: test needs a CUDA device")
+
+
+def _has_gpu():
+    try:
+        import torch
+        return torch.cuda.is_available()
+    except Exception:
+        return False
+
+
+def pytest_collection_modifyitems(config, items):
+    if _has_gpu():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    from oracle import bindings
+    bindings.build()
+    return bindings.Oracle()
+
+
+@pytest.fixture(scope="session")
+def reference_cpu():
+    """The reference's own CPU code, where oracle/_ref could be built."""
+    from oracle import bindings
+    if not os.path.exists(bindings.REF_CPU_SO):
+        if os.path.isdir("/root/reference/src"):
+            bindings.build(ref=True)
+        else:
+            pytest.skip("oracle/_ref not built (reference tree absent)")
+    return bindings.Reference()
+
+
+@pytest.fixture(scope="session")
+def kats():
+    with open(os.path.join(ROOT, "tests", "golden", "reference_kats.json")) as f:
+        return json.load(f)
+
+
+def kat_expect(entry, name=None):
+    """[(index, value, tol)] of one known-answer test, optionally for one array name."""
+    return [(i, v, t) for (n, i, v, t) in entry["expect"] if name is None or n == name]
+
+
+def assert_kat(entry, got, name=None, float_eq_ulps=4):
+    """Apply a reference test's EXPECT_NEAR / EXPECT_FLOAT_EQ lines to `got`."""
+    got = np.asarray(got, np.float32).ravel()
+    for idx, val, tol in kat_expect(entry, name):
+        if tol is None:  # EXPECT_FLOAT_EQ: within 4 ULPs
+            want = np.float32(val)
+            ulp = np.spacing(np.abs(want)) if want != 0 else np.float32(1e-37)
+            assert abs(got[idx] - want) <= float_eq_ulps * ulp, (idx, got[idx], val)
+        else:
+            assert abs(float(got[idx]) - val) <= tol, (idx, got[idx], val, tol)

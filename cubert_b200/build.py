@@ -1,0 +1,111 @@
+"""In-tree build of the native libraries for sm_100a.
+
+    python -m cubert_b200.build          # build what is stale
+    python -m cubert_b200.build --force  # rebuild everything
+
+Produces, next to this file:
+    lib/libcubert_kernels.so  -- the fused kernels and their C ABI (include/cubert_kernels.h)
+    lib/libcuBERT.so          -- the host library with the cuBERT C API (include/cuBERT.h),
+                                 linked against libcubert_kernels.so, cuBLAS and cuBLASLt
+
+nvcc cross-compiles without a GPU, so this also runs on a CPU-only machine.
+"""
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+CSRC = os.path.join(HERE, "csrc")
+LIBDIR = os.path.join(HERE, "lib")
+OBJDIR = os.path.join(HERE, "build")
+INCLUDE = os.path.join(ROOT, "include")
+
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
+HOST_CXX = "g++"  # the image's $CXX points at a compiler without OpenMP specs; use the system one
+
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ARCH_FLAGS + ["-lineinfo", "-O3", "-std=c++17", "-ccbin", HOST_CXX, "-cudart", "shared",
+                           "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "-I" + INCLUDE]
+
+KERNEL_LIB = os.path.join(LIBDIR, "libcubert_kernels.so")
+HOST_LIB = os.path.join(LIBDIR, "libcuBERT.so")
+
+
+def _sources(sub):
+    d = os.path.join(CSRC, sub)
+    if not os.path.isdir(d):
+        return [], []
+    files = sorted(os.listdir(d))
+    srcs = [os.path.join(d, f) for f in files if f.endswith((".cu", ".cpp"))]
+    hdrs = [os.path.join(d, f) for f in files if f.endswith((".cuh", ".h", ".hpp"))]
+    return srcs, hdrs
+
+
+def _mtime(p):
+    return os.path.getmtime(p) if os.path.exists(p) else 0.0
+
+
+def _run(cmd):
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("command failed: %s\n%s" % (" ".join(cmd), proc.stdout))
+    return proc.stdout
+
+
+def _compile(sub, extra_flags, force, verbose):
+    srcs, hdrs = _sources(sub)
+    public = [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE)]
+    newest_hdr = max([_mtime(h) for h in hdrs + public] + [_mtime(os.path.abspath(__file__))])
+    os.makedirs(os.path.join(OBJDIR, sub), exist_ok=True)
+    jobs, objs = [], []
+    for src in srcs:
+        obj = os.path.join(OBJDIR, sub, os.path.basename(src) + ".o")
+        objs.append(obj)
+        if force or _mtime(obj) < max(_mtime(src), newest_hdr):
+            jobs.append([NVCC] + NVCC_FLAGS + extra_flags + ["-x", "cu", "-c", src, "-o", obj])
+    if jobs:
+        if verbose:
+            print("[build] compiling %d file(s) in csrc/%s" % (len(jobs), sub), file=sys.stderr)
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as pool:
+            list(pool.map(_run, jobs))
+    return objs, bool(jobs)
+
+
+def build_kernels(force=False, verbose=True):
+    objs, changed = _compile("kernels", [], force, verbose)
+    if not objs:
+        raise RuntimeError("no kernel sources under %s" % CSRC)
+    if changed or not os.path.exists(KERNEL_LIB):
+        os.makedirs(LIBDIR, exist_ok=True)
+        _run([NVCC] + ARCH_FLAGS + ["-shared", "-cudart", "shared", "-ccbin", HOST_CXX, "-o", KERNEL_LIB] + objs +
+             ["-Xlinker", "-rpath," + os.path.join(CUDA_HOME, "lib64")])
+    return KERNEL_LIB
+
+
+def build_host(force=False, verbose=True):
+    srcs, _ = _sources("host")
+    if not srcs:
+        return None
+    kernel_lib = build_kernels(force=False, verbose=verbose)
+    objs, changed = _compile("host", ["-I" + os.path.join(CSRC, "host")], force, verbose)
+    if changed or _mtime(HOST_LIB) < _mtime(kernel_lib):
+        _run([NVCC] + ARCH_FLAGS + ["-shared", "-cudart", "shared", "-ccbin", HOST_CXX, "-o", HOST_LIB] + objs +
+             ["-L" + LIBDIR, "-lcubert_kernels", "-lcublas", "-lcublasLt",
+              "-Xlinker", "-rpath,$ORIGIN", "-Xlinker", "-rpath," + os.path.join(CUDA_HOME, "lib64")])
+    return HOST_LIB
+
+
+def build_all(force=False, verbose=True):
+    out = [build_kernels(force, verbose)]
+    host = build_host(force, verbose)
+    if host:
+        out.append(host)
+    return out
+
+
+if __name__ == "__main__":
+    for lib in build_all(force="--force" in sys.argv):
+        print(lib)

@@ -1,0 +1,218 @@
+// Shared device/host helpers for the fused BERT layer kernels (sm_100a).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "cubert_kernels.h"
+
+namespace cubk {
+
+// ---------------------------------------------------------------- launch status
+void set_last_error(cudaError_t err);
+
+inline int check_launch() {
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) {
+        set_last_error(err);
+        return CUBK_ERR_LAUNCH;
+    }
+    return CUBK_OK;
+}
+
+inline bool aligned16(const void *p) {
+    return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
+
+inline bool aligned8(const void *p) {
+    return (reinterpret_cast<uintptr_t>(p) & 7u) == 0;
+}
+
+// ---------------------------------------------------------------- 16-byte vectors
+// One 128-bit global transaction holds EPV elements: 4 floats or 8 halves.
+template <typename T>
+struct Vec;
+
+template <>
+struct Vec<float> {
+    static constexpr int EPV = 4;
+    static __device__ __forceinline__ void unpack(const uint4 &raw, float (&v)[4]) {
+        v[0] = __uint_as_float(raw.x);
+        v[1] = __uint_as_float(raw.y);
+        v[2] = __uint_as_float(raw.z);
+        v[3] = __uint_as_float(raw.w);
+    }
+    static __device__ __forceinline__ uint4 pack(const float (&v)[4]) {
+        return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]),
+                          __float_as_uint(v[3]));
+    }
+};
+
+template <>
+struct Vec<__half> {
+    static constexpr int EPV = 8;
+    static __device__ __forceinline__ void unpack(const uint4 &raw, float (&v)[8]) {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2 h = *reinterpret_cast<const __half2 *>(&w[i]);
+            float2 f = __half22float2(h);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ uint4 pack(const float (&v)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
+// Streaming 128-bit load: data that is read once (activations, scores).
+__device__ __forceinline__ uint4 ld_stream(const void *p) {
+    return __ldcs(reinterpret_cast<const uint4 *>(p));
+}
+
+// Read-only cached 128-bit load: small operands every block re-reads (bias, gamma, beta, tables).
+__device__ __forceinline__ uint4 ld_param(const void *p) {
+    return __ldg(reinterpret_cast<const uint4 *>(p));
+}
+
+__device__ __forceinline__ void st_vec(void *p, const uint4 &v) {
+    *reinterpret_cast<uint4 *>(p) = v;
+}
+
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) {
+    return v;
+}
+template <>
+__device__ __forceinline__ float to_float<__half>(__half v) {
+    return __half2float(v);
+}
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) {
+    return v;
+}
+template <>
+__device__ __forceinline__ __half from_float<__half>(float v) {
+    return __float2half_rn(v);
+}
+
+// 2^x on the special-function unit: one MUFU.EX2, about 2 ulp, results below 2^-126 flush to 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// ---------------------------------------------------------------- reductions
+// Butterfly reductions across the WIDTH (power of two, <= 32) adjacent lanes that share a row.
+template <int WIDTH>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+    for (int o = WIDTH / 2; o > 0; o >>= 1) {
+        v += __shfl_xor_sync(0xffffffffu, v, o, 32);
+    }
+    return v;
+}
+
+template <int WIDTH>
+__device__ __forceinline__ float group_max(float v) {
+#pragma unroll
+    for (int o = WIDTH / 2; o > 0; o >>= 1) {
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o, 32));
+    }
+    return v;
+}
+
+// Sum over all threads of a block of NWARPS warps; every thread gets the result.
+// `smem` must hold NWARPS floats and is reusable after the call returns.
+template <int NWARPS>
+__device__ __forceinline__ float block_sum(float v, float *smem) {
+    v = group_sum<32>(v);
+    if (NWARPS == 1) {
+        return v;
+    }
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    __syncthreads();  // protect smem from the previous use
+    if (lane == 0) {
+        smem[warp] = v;
+    }
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) {
+        t += smem[w];
+    }
+    return t;
+}
+
+template <int NWARPS>
+__device__ __forceinline__ float block_max(float v, float *smem) {
+    v = group_max<32>(v);
+    if (NWARPS == 1) {
+        return v;
+    }
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) {
+        smem[warp] = v;
+    }
+    __syncthreads();
+    float t = smem[0];
+#pragma unroll
+    for (int w = 1; w < NWARPS; ++w) {
+        t = fmaxf(t, smem[w]);
+    }
+    return t;
+}
+
+// ---------------------------------------------------------------- unsigned division by a runtime constant
+// q = n / d for 32-bit n via one multiply-high and a shift (round-up method).
+struct FastDiv {
+    uint32_t mul;
+    uint32_t shift;
+    uint32_t div;
+};
+
+inline FastDiv make_fastdiv(uint32_t d) {
+    FastDiv f;
+    f.div = d;
+    if (d == 1) {
+        f.mul = 0;
+        f.shift = 0;
+        return f;
+    }
+    uint32_t l = 0;
+    while ((1ull << l) < d) {
+        ++l;
+    }
+    // m = floor(2^32 * (2^l - d) / d) + 1
+    f.mul = (uint32_t) (((1ull << 32) * ((1ull << l) - d)) / d + 1);
+    f.shift = l;
+    return f;
+}
+
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, const FastDiv &f) {
+    if (f.div == 1) {
+        return n;
+    }
+    uint32_t t = __umulhi(n, f.mul);
+    // (t + ((n - t) >> 1)) >> (shift - 1)
+    return (t + ((n - t) >> 1)) >> (f.shift - 1);
+}
+
+}  // namespace cubk

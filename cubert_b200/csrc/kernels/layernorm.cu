@@ -1,0 +1,388 @@
+// K1 (embedding lookup + add + LayerNorm) and K2 (bias + residual + LayerNorm).
+//
+// Both keep one row in registers: TPR threads share a row, each holding VPT 16-byte
+// vectors, so the row is read from HBM exactly once and written once. Mean and the
+// centred second moment are reduced with warp shuffles (plus one shared-memory hop when
+// a row spans a whole block). All arithmetic is float32.
+//
+// HBM traffic per row: K2 reads x and residual and writes out (3 * C * e bytes);
+// K1 reads one gathered word row and writes out (2 * H * e bytes) plus 5 index bytes.
+#include "common.cuh"
+
+namespace cubk {
+
+constexpr float kLayerNormEps = 1e-12f;  // src/cuBERT/op/LayerNorm.cpp:35, op/LayerNorm.cu:70
+
+template <int TPR, int BLOCK>
+__device__ __forceinline__ float row_sum(float v, float *smem) {
+    if (TPR <= 32) {
+        return group_sum<TPR>(v);
+    } else {
+        static_assert(TPR <= 32 || TPR == BLOCK, "a row spans a sub-warp group or the whole block");
+        return block_sum<BLOCK / 32>(v, smem);
+    }
+}
+
+// Normalise the register-resident row `v` and store it.
+template <typename T, int TPR, int VPT, int BLOCK>
+__device__ __forceinline__ void normalise_store(float (&v)[VPT][Vec<T>::EPV], int lane, int nvec, int channels,
+                                                bool active, const T *gamma, const T *beta, T *out_row,
+                                                float *smem) {
+    constexpr int EPV = Vec<T>::EPV;
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        if (lane + k * TPR < nvec) {
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) {
+                s += v[k][e];
+            }
+        }
+    }
+    const float mean = row_sum<TPR, BLOCK>(s, smem) / (float) channels;
+
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        if (lane + k * TPR < nvec) {
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) {
+                const float d = v[k][e] - mean;
+                q += d * d;
+            }
+        }
+    }
+    const float var = row_sum<TPR, BLOCK>(q, smem) / (float) channels;
+    const float rstd = 1.f / sqrtf(var + kLayerNormEps);
+
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int idx = lane + k * TPR;
+        if (active && idx < nvec) {
+            float g[EPV], b[EPV], o[EPV];
+            Vec<T>::unpack(ld_param(gamma + (size_t) idx * EPV), g);
+            Vec<T>::unpack(ld_param(beta + (size_t) idx * EPV), b);
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) {
+                o[e] = b[e] + g[e] * rstd * (v[k][e] - mean);
+            }
+            st_vec(out_row + (size_t) idx * EPV, Vec<T>::pack(o));
+        }
+    }
+}
+
+// ------------------------------------------------------------------ K2
+template <typename T, int TPR, int VPT, int BLOCK>
+__global__ void __launch_bounds__(BLOCK)
+bias_residual_ln_kernel(const T *x, const T *bias, const T *residual, const T *gamma, const T *beta,
+                        T *out, int64_t rows, int channels, int nvec) {
+    constexpr int EPV = Vec<T>::EPV;
+    constexpr int RPB = BLOCK / TPR;
+    __shared__ float smem[BLOCK / 32];
+
+    const int lane = threadIdx.x % TPR;
+    const int64_t row = (int64_t) blockIdx.x * RPB + threadIdx.x / TPR;
+    const bool active = row < rows;
+    const int64_t base = active ? row * (int64_t) channels : 0;
+
+    // Issue every load of the row before the first use.
+    uint4 rx[VPT], rr[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int idx = lane + k * TPR;
+        const bool ok = active && idx < nvec;
+        rx[k] = ok ? ld_stream(x + base + (int64_t) idx * EPV) : make_uint4(0, 0, 0, 0);
+        if (residual != nullptr) {
+            rr[k] = ok ? ld_stream(residual + base + (int64_t) idx * EPV) : make_uint4(0, 0, 0, 0);
+        }
+    }
+
+    float v[VPT][EPV];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int idx = lane + k * TPR;
+        Vec<T>::unpack(rx[k], v[k]);
+        if (bias != nullptr && idx < nvec) {
+            float b[EPV];
+            Vec<T>::unpack(ld_param(bias + (size_t) idx * EPV), b);
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) {
+                v[k][e] += b[e];
+            }
+        }
+        if (residual != nullptr) {
+            float r[EPV];
+            Vec<T>::unpack(rr[k], r);
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) {
+                v[k][e] += r[e];
+            }
+        }
+    }
+
+    normalise_store<T, TPR, VPT, BLOCK>(v, lane, nvec, channels, active, gamma, beta, out + base, smem);
+}
+
+// ------------------------------------------------------------------ K1
+template <typename T, int TPR, int VPT, int BLOCK>
+__global__ void __launch_bounds__(BLOCK)
+embed_ln_kernel(const int32_t *ids, const int8_t *segment_ids, const T *word, const T *pos, const T *type,
+                const T *gamma, const T *beta, T *out, uint32_t tokens, FastDiv seq_div, int hidden, int nvec,
+                int vocab, int type_vocab, uint32_t *status) {
+    constexpr int EPV = Vec<T>::EPV;
+    constexpr int RPB = BLOCK / TPR;
+    __shared__ float smem[BLOCK / 32];
+
+    const int lane = threadIdx.x % TPR;
+    const uint32_t token = blockIdx.x * RPB + threadIdx.x / TPR;
+    const bool active = token < tokens;
+
+    int id = 0, seg = 0;
+    uint32_t s = 0;
+    if (active) {
+        id = ids[token];
+        seg = segment_ids[token];
+        s = token - fast_div(token, seq_div) * seq_div.div;
+        uint32_t bad = 0;
+        if (id < 0 || id >= vocab) {
+            bad |= CUBK_STATUS_BAD_TOKEN_ID;
+            id = min(max(id, 0), vocab - 1);
+        }
+        if (seg < 0 || seg >= type_vocab) {
+            bad |= CUBK_STATUS_BAD_SEGMENT_ID;
+            seg = min(max(seg, 0), type_vocab - 1);
+        }
+        if (bad != 0 && status != nullptr && lane == 0) {
+            atomicOr(status, bad);
+        }
+    }
+
+    const T *wrow = word + (size_t) id * hidden;
+    const T *prow = pos + (size_t) s * hidden;
+    const T *trow = type + (size_t) seg * hidden;
+
+    uint4 rw[VPT], rp[VPT], rt[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int idx = lane + k * TPR;
+        const bool ok = active && idx < nvec;
+        rw[k] = ok ? ld_param(wrow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
+        rp[k] = ok ? ld_param(prow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
+        rt[k] = ok ? ld_param(trow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
+    }
+
+    float v[VPT][EPV];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        float p[EPV], t[EPV];
+        Vec<T>::unpack(rw[k], v[k]);
+        Vec<T>::unpack(rp[k], p);
+        Vec<T>::unpack(rt[k], t);
+#pragma unroll
+        for (int e = 0; e < EPV; ++e) {
+            v[k][e] = (v[k][e] + p[e]) + t[e];  // (word + pos) + type, the reference's order
+        }
+    }
+
+    normalise_store<T, TPR, VPT, BLOCK>(v, lane, nvec, hidden, active, gamma, beta,
+                                        out + (size_t) token * (active ? hidden : 0), smem);
+}
+
+// ------------------------------------------------------------------ generic rows (any width, any alignment)
+// One block per row, three scalar passes over the row (sum, centred squares, write).
+template <typename T>
+struct ResidualLoader {
+    const T *x, *bias, *residual;
+    int channels;
+    __device__ __forceinline__ float operator()(int64_t row, int c) const {
+        const int64_t i = row * (int64_t) channels + c;
+        float t = to_float<T>(x[i]);
+        if (bias != nullptr) {
+            t += to_float<T>(bias[c]);
+        }
+        if (residual != nullptr) {
+            t += to_float<T>(residual[i]);
+        }
+        return t;
+    }
+};
+
+template <typename T>
+struct EmbedLoader {
+    const int32_t *ids;
+    const int8_t *segment_ids;
+    const T *word, *pos, *type;
+    int hidden, seq, vocab, type_vocab;
+    uint32_t *status;
+    __device__ __forceinline__ float operator()(int64_t row, int c) const {
+        int id = ids[row];
+        int seg = segment_ids[row];
+        uint32_t bad = 0;
+        if (id < 0 || id >= vocab) {
+            bad |= CUBK_STATUS_BAD_TOKEN_ID;
+            id = min(max(id, 0), vocab - 1);
+        }
+        if (seg < 0 || seg >= type_vocab) {
+            bad |= CUBK_STATUS_BAD_SEGMENT_ID;
+            seg = min(max(seg, 0), type_vocab - 1);
+        }
+        if (bad != 0 && status != nullptr && c == 0) {
+            atomicOr(status, bad);
+        }
+        const int s = (int) (row % seq);
+        return (to_float<T>(word[(size_t) id * hidden + c]) + to_float<T>(pos[(size_t) s * hidden + c])) +
+               to_float<T>(type[(size_t) seg * hidden + c]);
+    }
+};
+
+template <typename T, typename Loader>
+__global__ void __launch_bounds__(128)
+generic_ln_kernel(Loader load, const T *gamma, const T *beta, T *out, int channels) {
+    __shared__ float smem[4];
+    const int64_t row = blockIdx.x;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < channels; c += 128) {
+        s += load(row, c);
+    }
+    const float mean = block_sum<4>(s, smem) / (float) channels;
+    float q = 0.f;
+    for (int c = threadIdx.x; c < channels; c += 128) {
+        const float d = load(row, c) - mean;
+        q += d * d;
+    }
+    const float var = block_sum<4>(q, smem) / (float) channels;
+    const float rstd = 1.f / sqrtf(var + kLayerNormEps);
+    for (int c = threadIdx.x; c < channels; c += 128) {
+        const float t = load(row, c);
+        out[row * (int64_t) channels + c] =
+            from_float<T>(to_float<T>(beta[c]) + to_float<T>(gamma[c]) * rstd * (t - mean));
+    }
+}
+
+// ------------------------------------------------------------------ dispatch
+// Picks (threads per row, vectors per thread) for a row of `nvec` 16-byte vectors.
+// Rows up to 256 vectors stay inside one warp; up to 1024 vectors use one 128-thread block.
+#define CUBK_LN_DISPATCH(NVEC, LAUNCH)                      \
+    do {                                                    \
+        if ((NVEC) <= 32) { LAUNCH(32, 1, 128); }           \
+        else if ((NVEC) <= 64) { LAUNCH(32, 2, 128); }      \
+        else if ((NVEC) <= 96) { LAUNCH(32, 3, 128); }      \
+        else if ((NVEC) <= 128) { LAUNCH(32, 4, 128); }     \
+        else if ((NVEC) <= 192) { LAUNCH(32, 6, 128); }     \
+        else if ((NVEC) <= 256) { LAUNCH(32, 8, 128); }     \
+        else if ((NVEC) <= 384) { LAUNCH(128, 3, 128); }    \
+        else if ((NVEC) <= 512) { LAUNCH(128, 4, 128); }    \
+        else if ((NVEC) <= 768) { LAUNCH(128, 6, 128); }    \
+        else { LAUNCH(128, 8, 128); }                       \
+    } while (0)
+
+constexpr int kMaxRowVectors = 1024;
+
+template <typename T>
+int bias_residual_ln(const T *x, const T *bias, const T *residual, const T *gamma, const T *beta,
+                     int64_t rows, int channels, T *out, cudaStream_t stream) {
+    if (x == nullptr || gamma == nullptr || beta == nullptr || out == nullptr || rows < 0 || channels <= 0) {
+        return CUBK_ERR_INVALID_ARG;
+    }
+    if (rows == 0) {
+        return CUBK_OK;
+    }
+    if (rows > 0x7fffffffLL) {
+        return CUBK_ERR_UNSUPPORTED;
+    }
+    constexpr int EPV = Vec<T>::EPV;
+    const bool vec_ok = channels % EPV == 0 && channels / EPV <= kMaxRowVectors && aligned16(x) &&
+                        aligned16(out) && aligned16(gamma) && aligned16(beta) &&
+                        (bias == nullptr || aligned16(bias)) && (residual == nullptr || aligned16(residual));
+    if (vec_ok) {
+        const int nvec = channels / EPV;
+#define LAUNCH(TPR, VPT, BLOCK)                                                                       \
+    {                                                                                                 \
+        const int64_t grid = (rows + (BLOCK / TPR) - 1) / (BLOCK / TPR);                              \
+        bias_residual_ln_kernel<T, TPR, VPT, BLOCK><<<(unsigned) grid, BLOCK, 0, stream>>>(           \
+            x, bias, residual, gamma, beta, out, rows, channels, nvec);                               \
+    }
+        CUBK_LN_DISPATCH(nvec, LAUNCH);
+#undef LAUNCH
+    } else {
+        ResidualLoader<T> loader{x, bias, residual, channels};
+        generic_ln_kernel<T, ResidualLoader<T>><<<(unsigned) rows, 128, 0, stream>>>(loader, gamma, beta, out,
+                                                                                    channels);
+    }
+    return check_launch();
+}
+
+template <typename T>
+int embed_ln(const int32_t *ids, const int8_t *segment_ids, const T *word, const T *pos, const T *type,
+             const T *gamma, const T *beta, int batch, int seq, int hidden, int vocab, int type_vocab,
+             T *out, uint32_t *status, cudaStream_t stream) {
+    if (ids == nullptr || segment_ids == nullptr || word == nullptr || pos == nullptr || type == nullptr ||
+        gamma == nullptr || beta == nullptr || out == nullptr || batch < 0 || seq <= 0 || hidden <= 0 ||
+        vocab <= 0 || type_vocab <= 0) {
+        return CUBK_ERR_INVALID_ARG;
+    }
+    const int64_t tokens = (int64_t) batch * seq;
+    if (tokens == 0) {
+        return CUBK_OK;
+    }
+    if (tokens > 0x7fffffffLL) {
+        return CUBK_ERR_UNSUPPORTED;
+    }
+    constexpr int EPV = Vec<T>::EPV;
+    const bool vec_ok = hidden % EPV == 0 && hidden / EPV <= kMaxRowVectors && aligned16(word) &&
+                        aligned16(pos) && aligned16(type) && aligned16(gamma) && aligned16(beta) &&
+                        aligned16(out);
+    if (vec_ok) {
+        const int nvec = hidden / EPV;
+        const FastDiv seq_div = make_fastdiv((uint32_t) seq);
+#define LAUNCH(TPR, VPT, BLOCK)                                                                       \
+    {                                                                                                 \
+        const int64_t grid = (tokens + (BLOCK / TPR) - 1) / (BLOCK / TPR);                            \
+        embed_ln_kernel<T, TPR, VPT, BLOCK><<<(unsigned) grid, BLOCK, 0, stream>>>(                   \
+            ids, segment_ids, word, pos, type, gamma, beta, out, (uint32_t) tokens, seq_div, hidden,  \
+            nvec, vocab, type_vocab, status);                                                         \
+    }
+        CUBK_LN_DISPATCH(nvec, LAUNCH);
+#undef LAUNCH
+    } else {
+        EmbedLoader<T> loader{ids, segment_ids, word, pos, type, hidden, seq, vocab, type_vocab, status};
+        generic_ln_kernel<T, EmbedLoader<T>><<<(unsigned) tokens, 128, 0, stream>>>(loader, gamma, beta, out,
+                                                                                   hidden);
+    }
+    return check_launch();
+}
+
+}  // namespace cubk
+
+extern "C" {
+
+int cubk_bias_residual_ln_f32(const float *x, const float *bias, const float *residual, const float *gamma,
+                              const float *beta, int64_t rows, int channels, float *out, void *stream) {
+    return cubk::bias_residual_ln<float>(x, bias, residual, gamma, beta, rows, channels, out,
+                                         (cudaStream_t) stream);
+}
+
+int cubk_bias_residual_ln_f16(const void *x, const void *bias, const void *residual, const void *gamma,
+                              const void *beta, int64_t rows, int channels, void *out, void *stream) {
+    return cubk::bias_residual_ln<__half>((const __half *) x, (const __half *) bias, (const __half *) residual,
+                                          (const __half *) gamma, (const __half *) beta, rows, channels,
+                                          (__half *) out, (cudaStream_t) stream);
+}
+
+int cubk_embed_ln_f32(const int32_t *ids, const int8_t *segment_ids, const float *word, const float *pos,
+                      const float *type, const float *gamma, const float *beta, int batch, int seq, int hidden,
+                      int vocab, int type_vocab, float *out, uint32_t *status, void *stream) {
+    return cubk::embed_ln<float>(ids, segment_ids, word, pos, type, gamma, beta, batch, seq, hidden, vocab,
+                                 type_vocab, out, status, (cudaStream_t) stream);
+}
+
+int cubk_embed_ln_f16(const int32_t *ids, const int8_t *segment_ids, const void *word, const void *pos,
+                      const void *type, const void *gamma, const void *beta, int batch, int seq, int hidden,
+                      int vocab, int type_vocab, void *out, uint32_t *status, void *stream) {
+    return cubk::embed_ln<__half>(ids, segment_ids, (const __half *) word, (const __half *) pos,
+                                  (const __half *) type, (const __half *) gamma, (const __half *) beta, batch,
+                                  seq, hidden, vocab, type_vocab, (__half *) out, status,
+                                  (cudaStream_t) stream);
+}
+
+}

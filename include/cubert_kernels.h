@@ -1,0 +1,157 @@
+/*
+ * cubert_kernels.h -- C ABI of the fused non-GEMM BERT layer kernels for NVIDIA B200 (sm_100a).
+ *
+ * This is the launch layer that sits below cuBERT's host code. Every entry point takes
+ * plain device pointers and sizes plus a CUDA stream, enqueues its kernel(s) on that
+ * stream and returns immediately with a status: 0 on success, a negative CUBK_ERR_* code
+ * otherwise. Nothing here allocates, synchronises, exits the process or traps on the
+ * device. There is no CPU fallback: without a CUDA device every call fails.
+ *
+ * Each function names the reference operator interface it replaces (path:line inside the
+ * zhihu/cuBERT source tree). The reference's operators are `void`, unchecked and one
+ * kernel per elementary step; the functions below fuse the steps the reference spreads
+ * over several kernels, GEMM alpha/beta tricks and device-to-device copies.
+ *
+ * Conventions
+ *   - `_f32` entry points work on float storage, `_f16` on IEEE binary16 storage
+ *     (`__half`); arithmetic is float32 in both.
+ *   - Row-major tensors; rows are contiguous. Element counts are 64-bit safe
+ *     (rows * channels may exceed 2^31).
+ *   - A fast path is taken when pointers are 16-byte aligned and the row length is a
+ *     multiple of 16 bytes; any other shape or alignment runs a slower generic kernel
+ *     with identical results.
+ *   - `stream` is a `cudaStream_t` passed as `void *` (as the reference does).
+ */
+#ifndef CUBERT_KERNELS_H
+#define CUBERT_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CUBK_OK                 0
+#define CUBK_ERR_INVALID_ARG   -1   /* null pointer, non-positive size, bad enum */
+#define CUBK_ERR_UNSUPPORTED   -2   /* shape outside what the kernel family handles */
+#define CUBK_ERR_LAUNCH        -3   /* the CUDA runtime refused the launch (see cubk_last_cuda_error) */
+#define CUBK_ERR_SCRATCH       -4   /* scratch buffer missing or too small */
+
+/* Bits OR-ed into the device status word of cubk_embed_* when an index is out of range.
+ * The offending index is clamped into range so that no out-of-bounds read happens. */
+#define CUBK_STATUS_BAD_TOKEN_ID   1u
+#define CUBK_STATUS_BAD_SEGMENT_ID 2u
+
+/* Library version and the text of the last CUDA error seen by a failed launch (thread-local). */
+int cubk_version(void);
+const char *cubk_last_cuda_error(void);
+
+/* ---- K1: embedding lookup + position/token-type add + LayerNorm --------------------------
+ * out[b,s,:] = LayerNorm((word[ids[b,s]] + pos[s]) + type[segment_ids[b,s]]; gamma, beta)
+ * Replaces BertEmbeddings<T>::compute (src/cuBERT/op_bert/BertEmbeddings.cpp:50-66), i.e.
+ * two embedding<T,V> gathers (op/Embedding.h:10), a rank-1 GEMM and layer_norm_<T>.
+ * ids int32 [batch*seq], segment_ids int8 [batch*seq], word [vocab,hidden],
+ * pos [>=seq,hidden], type [type_vocab,hidden], gamma/beta [hidden], out [batch*seq,hidden].
+ * status: optional device uint32 word (may be NULL) that receives CUBK_STATUS_* bits. */
+int cubk_embed_ln_f32(const int32_t *ids, const int8_t *segment_ids,
+                      const float *word, const float *pos, const float *type,
+                      const float *gamma, const float *beta,
+                      int batch, int seq, int hidden, int vocab, int type_vocab,
+                      float *out, uint32_t *status, void *stream);
+int cubk_embed_ln_f16(const int32_t *ids, const int8_t *segment_ids,
+                      const void *word, const void *pos, const void *type,
+                      const void *gamma, const void *beta,
+                      int batch, int seq, int hidden, int vocab, int type_vocab,
+                      void *out, uint32_t *status, void *stream);
+
+/* Plain row gather out[i,:] = table[ids[i],:], bit-exact copy.
+ * Replaces embedding<int,V> / embedding<int8_t,V> (src/cuBERT/op/Embedding.h:10-15,
+ * op/Embedding.cu:8-41). elem_bytes is 4 (float) or 2 (half). */
+int cubk_embed_gather_i32(const int32_t *ids, int64_t n, const void *table, int vocab, int width,
+                          int elem_bytes, void *out, uint32_t *status, void *stream);
+int cubk_embed_gather_i8(const int8_t *ids, int64_t n, const void *table, int vocab, int width,
+                         int elem_bytes, void *out, uint32_t *status, void *stream);
+
+/* ---- K2: bias + residual + LayerNorm -------------------------------------------------------
+ * t = x (+ bias) (+ residual);  out = beta + gamma * (t - mean(t)) / sqrt(var(t) + 1e-12)
+ * Replaces layer_norm_<T> (src/cuBERT/op/LayerNorm.h:6-15, op/LayerNorm.cu:11-100) together
+ * with the Dense bias prefill it depends on (op/Dense.cpp:41-45). x, residual, out
+ * [rows, channels]; bias, gamma, beta [channels]. bias and residual may be NULL. out may
+ * alias x (the reference's in-place form: x = inout, residual = in). */
+int cubk_bias_residual_ln_f32(const float *x, const float *bias, const float *residual,
+                              const float *gamma, const float *beta,
+                              int64_t rows, int channels, float *out, void *stream);
+int cubk_bias_residual_ln_f16(const void *x, const void *bias, const void *residual,
+                              const void *gamma, const void *beta,
+                              int64_t rows, int channels, void *out, void *stream);
+
+/* ---- K3: bias + GELU ------------------------------------------------------------------------
+ * y = x (+ bias);  out = y * 0.5 * (1 + erf(y / sqrt(2)))
+ * Replaces gelu<T> (src/cuBERT/op/GELU.h:7, op/GELU.cu:14-26) plus the Dense bias prefill.
+ * x, out [rows, channels] (out may alias x); bias [channels] or NULL. */
+int cubk_bias_gelu_f32(const float *x, const float *bias, int64_t rows, int channels,
+                       float *out, void *stream);
+int cubk_bias_gelu_f16(const void *x, const void *bias, int64_t rows, int channels,
+                       void *out, void *stream);
+
+/* ---- K4: masked scaled softmax ----------------------------------------------------------------
+ * For row r of a [rows, seq] score matrix, with b = r / rows_per_batch:
+ *   v[j] = scale * scores[r,j] + (mask && mask[b*seq + j] == 0 ? -10000 : 0)
+ *   out[r,:] = softmax(v)
+ * Replaces softmax_<T> (src/cuBERT/op/Softmax.h:9-14, op/Softmax.cu:17-115), _not<T> and the
+ * mask broadcast (op_att/AttentionMask.h:9, op_att/AttentionMask.cpp:41-54), the per-layer
+ * device copy of the broadcast mask and the GEMM's beta = -10000 accumulate
+ * (op_att/AttentionSelf.cpp:58-60,99-101). For cuBERT's attention scores [B, S, heads, S]
+ * pass rows = B*S*heads and rows_per_batch = S*heads. mask is int8 [rows/rows_per_batch, seq]
+ * over the key axis, or NULL. out may alias scores. */
+int cubk_masked_softmax_f32(const float *scores, const int8_t *mask, int64_t rows, int64_t rows_per_batch,
+                            int seq, float scale, float *out, void *stream);
+int cubk_masked_softmax_f16(const void *scores, const int8_t *mask, int64_t rows, int64_t rows_per_batch,
+                            int seq, float scale, void *out, void *stream);
+
+/* ---- K5a: bias + tanh (BERT pooler activation) ---------------------------------------------------
+ * out = tanh(x (+ bias)). Replaces tanh_<T> (src/cuBERT/op_bert/BertPooler.h:9,
+ * op_bert/BertPooler.cu:14-26) plus the bias prefill of BertPooler<T>::compute
+ * (op_bert/BertPooler.cpp:62-77). x, out [rows, channels]; out may alias x. */
+int cubk_bias_tanh_f32(const float *x, const float *bias, int64_t rows, int channels,
+                       float *out, void *stream);
+int cubk_bias_tanh_f16(const void *x, const void *bias, int64_t rows, int channels,
+                       void *out, void *stream);
+
+/* ---- K5b: mean pooling over the sequence axis ---------------------------------------------------
+ * out[b,c] = (sum_s x[b,s,c]) / seq   (every position counts; the mask is ignored)
+ * Replaces reduce_mean_1<T> (src/cuBERT/op_bert/BertPooler.h:14-16, op_bert/BertPooler.cu:35-66).
+ * When batch is small the sequence axis is split over several thread blocks and the float32
+ * partial sums go through `scratch` (device memory, 256-byte aligned, at least
+ * cubk_mean_pool_scratch_bytes(batch, seq, hidden) bytes; may be NULL when that is 0). */
+size_t cubk_mean_pool_scratch_bytes(int batch, int seq, int hidden);
+int cubk_mean_pool_f32(const float *x, int batch, int seq, int hidden, float *out,
+                       void *scratch, size_t scratch_bytes, void *stream);
+int cubk_mean_pool_f16(const void *x, int batch, int seq, int hidden, void *out,
+                       void *scratch, size_t scratch_bytes, void *stream);
+
+/* ---- K5c: classifier head ---------------------------------------------------------------------
+ * logits[b,l] = sum_c pooled[b,c] * weights[l,c] (+ bias[l]);  probs[b,:] = softmax(logits[b,:])
+ * Replaces ClassifierOutputLayer<T>::_pre_compute/_in_compute
+ * (src/cuBERT/op_out/AdditionalOutputLayer.cpp:44-66): bias copy, an n = num_labels GEMM and
+ * the five softmax launches. weights [labels, hidden]; bias [labels] or NULL; probs may be
+ * NULL. labels <= 4096. */
+int cubk_logits_probs_f32(const float *pooled, const float *weights, const float *bias,
+                          int batch, int hidden, int labels, float *logits, float *probs, void *stream);
+int cubk_logits_probs_f16(const void *pooled, const void *weights, const void *bias,
+                          int batch, int hidden, int labels, void *logits, void *probs, void *stream);
+
+/* ---- helpers ------------------------------------------------------------------------------------
+ * out[i] = !in[i] as 0/1 in the storage type. Replaces _not<T> (src/cuBERT/op_att/AttentionMask.h:9). */
+int cubk_not_f32(const int8_t *in, float *out, int64_t n, void *stream);
+int cubk_not_f16(const int8_t *in, void *out, int64_t n, void *stream);
+
+/* binary16 -> float32 on the device. Replaces the host loop half2float
+ * (src/cuBERT/common.h:101-106) used by Bert<half>::output_to_float (src/cuBERT/Bert.cpp:218-259). */
+int cubk_half_to_float(const void *in, float *out, int64_t n, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUBERT_KERNELS_H */

@@ -1,0 +1,369 @@
+"""Parity of the CUDA kernels (called through the C ABI) against the CPU oracle.
+
+float32 storage: within 1e-5 relative. binary16 storage: the oracle runs in float32 on the
+binary16-rounded inputs; the kernel output must be within 1e-3 relative / 1e-2 absolute.
+Gathers and index handling: bit-exact.
+"""
+import numpy as np
+import pytest
+import torch
+
+import gpu_harness as G
+from conftest import assert_kat
+from cubert_b200 import kernels
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["f32", "f16"]
+
+
+def _prep(a, t):
+    """(device tensor in storage type, float32 host copy of what the kernel sees)."""
+    a = np.asarray(a, np.float32)
+    if t == "f16":
+        a = G.round_f16(a)
+    return G.dev(a, G.TORCH_DTYPE[t]), a
+
+
+def _check(got, ref, t, floor, what):
+    if t == "f32":
+        G.assert_close(G.host(got), ref, G.F32_RTOL, floor, what)
+    else:
+        g = G.host(got)
+        G.assert_close(g, ref, G.F16_RTOL, floor, what)
+        assert np.max(np.abs(g - ref)) <= G.F16_ATOL
+
+
+def A(entry, name, dtype=np.float32, shape=None):
+    a = np.asarray(entry["arrays"][name], dtype=dtype)
+    return a.reshape(shape) if shape else a
+
+
+# ============================================================================ known answers of the reference tests
+
+def test_kat_layer_norm(kats):
+    e = kats["op/LayerNormTest.cpp::layer_norm_ext"]
+    out = G.bias_residual_ln(G.dev(A(e, "inout", shape=(2, 3))), None, G.dev(A(e, "in", shape=(2, 3))),
+                             G.dev(A(e, "gamma")), G.dev(A(e, "beta")), inplace=True)
+    assert_kat(e, G.host(out))
+
+
+def test_kat_softmax(kats):
+    e = kats["op/SoftmaxTest.cpp::softmax_"]
+    out = G.masked_softmax(G.dev(A(e, "inout", shape=(2, 3))), None, 2, inplace=True)
+    assert_kat(e, G.host(out))
+
+
+def test_kat_gelu(kats):
+    e = kats["op/GELUTest.cpp::gelu"]
+    out = G.bias_gelu(G.dev(A(e, "inout", shape=(1, 5))), None, inplace=True)
+    assert_kat(e, G.host(out))
+    # binary16 storage variant of the same vector: within binary16 rounding of the double answer
+    out16 = G.bias_gelu(G.dev(A(e, "inout", shape=(1, 5)), torch.float16), None, t="f16")
+    want = np.array([v for (_, _, v, _) in e["expect"]])
+    assert np.max(np.abs(G.host(out16).ravel() - want)) < 1e-3
+
+
+def test_kat_embedding(kats):
+    e = kats["op/EmbeddingTest.cpp::embedding"]
+    out = G.embed_gather(G.dev(A(e, "input_ids", np.int32)), G.dev(A(e, "embedding_table", shape=(4, 3))))
+    assert_kat(e, G.host(out))
+
+
+def test_kat_bert_embeddings(kats):
+    e = kats["op_bert/BertEmbeddingsTest.cpp::bert_embedding"]
+    out = G.embed_ln(G.dev(A(e, "input_ids", np.int32, (2, 4))), G.dev(A(e, "segment_ids", np.int8, (2, 4))),
+                     G.dev(A(e, "word_embeddings", shape=(5, 3))), G.dev(A(e, "position_embeddings", shape=(4, 3))),
+                     G.dev(A(e, "token_type_embeddings", shape=(2, 3))), G.dev(A(e, "gamma")), G.dev(A(e, "beta")))
+    # EXPECT_FLOAT_EQ(out, 0) lines: our centred two-pass mean gives exactly 0 there as well
+    assert_kat(e, G.host(out))
+
+
+def test_kat_attention_mask(kats, oracle):
+    """The reference materialises neg mask [B, S*H, S]; our softmax applies the int8 mask directly.
+    Check that the rows our kernel treats as masked are exactly the reference tensor's ones."""
+    e = kats["op_att/AttentionMaskTest.cpp::attention_mask"]
+    mask = A(e, "in", np.int8, (2, 2))
+    neg = G.host(G.logical_not(G.dev(mask)))
+    assert np.array_equal(neg, oracle.not_(mask))
+    expect = np.array([v for (_, _, v, _) in e["expect"]], np.float32).reshape(2, 6, 2)
+    assert np.array_equal(np.broadcast_to(neg[:, None, :], (2, 6, 2)), expect)
+    # and through the kernel: zero scores, masked keys get ~0 probability unless the whole row is masked
+    probs = G.host(G.masked_softmax(torch.zeros((12, 2), device="cuda"), G.dev(mask), 6))
+    assert np.allclose(probs[:6], [[1, 0]] * 6) and np.allclose(probs[6:], 0.5)
+
+
+def test_kat_poolers(kats):
+    e = kats["op_bert/BertPoolerTest.cpp::bert_pooler"]
+    x = A(e, "in", shape=(2, 3, 2))
+    pre = x[:, 0, :] @ A(e, "kernel", shape=(2, 2))  # the GEMM stays outside the kernels
+    out = G.bias_tanh(G.dev(pre), G.dev(A(e, "bias")))
+    assert_kat(e, G.host(out))
+    e = kats["op_bert/BertPoolerTest.cpp::mean_pooler"]
+    assert_kat(e, G.host(G.mean_pool(G.dev(A(e, "in", shape=(2, 3, 2))))))
+
+
+def test_kat_classifier(kats):
+    e = kats["op_out/AdditionalOutputLayerTest.cpp::additional_output"]
+    logits, _ = G.logits_probs(G.dev(A(e, "in", shape=(2, 3))), G.dev(A(e, "output_weights", shape=(1, 3))), None,
+                               want_probs=False)
+    assert_kat(e, G.host(logits))
+
+
+# ============================================================================ K2 bias + residual + LayerNorm
+
+LN_SHAPES = [(2, 3), (5, 5), (7, 6), (1, 8), (33, 768), (17, 1024), (9, 3072), (5, 4096), (6, 200), (3, 1000),
+             (4, 8192), (3, 8200), (130, 64), (257, 96)]
+
+
+@pytest.mark.parametrize("t", DTYPES)
+@pytest.mark.parametrize("rows,ch", LN_SHAPES)
+def test_bias_residual_ln(oracle, t, rows, ch):
+    rng = np.random.default_rng(rows * 7919 + ch)
+    x, xh = _prep(rng.standard_normal((rows, ch)), t)
+    r, rh = _prep(rng.standard_normal((rows, ch)), t)
+    b, bh = _prep(rng.standard_normal(ch) * 0.5, t)
+    g, gh = _prep(1 + 0.1 * rng.standard_normal(ch), t)
+    be, beh = _prep(0.1 * rng.standard_normal(ch), t)
+    ref = oracle.layer_norm_(rh, xh + bh[None, :], beh, gh)
+    _check(G.bias_residual_ln(x, b, r, g, be, t), ref, t, 1.0, "ln")
+    # in place, and without bias / residual
+    ref2 = oracle.layer_norm_(rh, xh, beh, gh)
+    _check(G.bias_residual_ln(x.clone(), None, r, g, be, t, inplace=True), ref2, t, 1.0, "ln in place")
+    ref3 = oracle.layer_norm_(np.zeros_like(xh), xh, beh, gh)
+    _check(G.bias_residual_ln(x, None, None, g, be, t), ref3, t, 1.0, "ln plain")
+
+
+@pytest.mark.parametrize("t", DTYPES)
+def test_ln_unaligned_pointers_take_generic_path(oracle, t):
+    rng = np.random.default_rng(3)
+    rows, ch = 6, 768
+    big, _ = _prep(rng.standard_normal(rows * ch + 1), t)
+    x = big[1:].view(rows, ch)  # 4- or 2-byte aligned only
+    xh = G.host(x)
+    g, gh = _prep(np.ones(ch), t)
+    be, beh = _prep(np.zeros(ch), t)
+    ref = oracle.layer_norm_(np.zeros_like(xh), xh, beh, gh)
+    _check(G.bias_residual_ln(x, None, None, g, be, t), ref, t, 1.0, "ln unaligned")
+
+
+def test_ln_constant_rows_are_finite():
+    """A constant row has zero variance: the centred two-pass form returns beta exactly, where the
+    reference's E[t^2] - mean^2 may go negative and produce NaN (src/cuBERT/op/LayerNorm.cpp:32-35)."""
+    x = torch.full((4, 768), 3.14159, device="cuda")
+    g = torch.full((768,), 2.0, device="cuda")
+    be = torch.full((768,), 0.25, device="cuda")
+    out = G.host(G.bias_residual_ln(x, None, None, g, be))
+    assert np.array_equal(out, np.full((4, 768), 0.25, np.float32))
+
+
+# ============================================================================ K3 bias + GELU, K5a bias + tanh
+
+ACT_SHAPES = [(1, 5), (3, 7), (5, 768), (4, 3072), (9, 1024), (2, 2048), (3, 4096), (6, 200), (5, 1001), (1000, 96)]
+
+
+def _gelu_floor(xb):
+    # |gelu| is tiny for very negative inputs, where the reference's 1 + erf cancels (its erff is
+    # good to about 1e-7 absolute, i.e. |x| * 1e-7 in the result); bound the error there relative
+    # to max(|y|, 2e-2 * |x|) instead of |y| alone.
+    return np.maximum(2e-2 * np.abs(xb), 1e-3)
+
+
+@pytest.mark.parametrize("t", DTYPES)
+@pytest.mark.parametrize("rows,ch", ACT_SHAPES)
+def test_bias_gelu(oracle, t, rows, ch):
+    rng = np.random.default_rng(rows * 31 + ch)
+    x, xh = _prep(rng.standard_normal((rows, ch)) * 2, t)
+    b, bh = _prep(rng.standard_normal(ch) * 0.5, t)
+    ref = oracle.gelu(xh + bh[None, :])
+    _check(G.bias_gelu(x, b, t), ref, t, _gelu_floor(xh + bh[None, :]), "gelu")
+    ref2 = oracle.gelu(xh)
+    _check(G.bias_gelu(x.clone(), None, t, inplace=True), ref2, t, _gelu_floor(xh), "gelu in place")
+
+
+@pytest.mark.parametrize("t", DTYPES)
+def test_gelu_full_input_range(t):
+    """Every interesting input (dense grid on [-12, 12] plus huge values) against double erf."""
+    from scipy.special import ndtr
+    xs = np.concatenate([np.linspace(-12, 12, 48001), [-65504, -100, 100, 65504, 0.0, -0.0]]).astype(np.float32)
+    pad = (-len(xs)) % 8
+    xs = np.concatenate([xs, np.zeros(pad, np.float32)])
+    x, xh = _prep(xs.reshape(1, -1), t)
+    got = G.host(G.bias_gelu(x, None, t)).ravel().astype(np.float64)
+    want = xh.ravel().astype(np.float64) * ndtr(xh.ravel().astype(np.float64))
+    tol = 1e-5 if t == "f32" else 1e-3
+    err = np.abs(got - want) / np.maximum(np.abs(want), np.maximum(2e-2 * np.abs(xh.ravel()), 1e-3))
+    assert err.max() < tol, (err.max(), xh.ravel()[err.argmax()])
+
+
+@pytest.mark.parametrize("t", DTYPES)
+@pytest.mark.parametrize("rows,ch", [(2, 2), (128, 768), (7, 1024), (3, 13)])
+def test_bias_tanh(oracle, t, rows, ch):
+    rng = np.random.default_rng(rows + ch)
+    x, xh = _prep(rng.standard_normal((rows, ch)) * 2, t)
+    b, bh = _prep(rng.standard_normal(ch), t)
+    _check(G.bias_tanh(x, b, t), oracle.tanh_(xh + bh[None, :]), t, 1e-2, "tanh")
+
+
+# ============================================================================ K4 masked scaled softmax
+
+SOFTMAX_SHAPES = [  # (batch, heads, seq)
+    (2, 3, 2), (1, 1, 3), (3, 2, 5), (2, 2, 8), (4, 12, 32), (2, 12, 128), (1, 16, 512), (2, 3, 64), (2, 2, 48),
+    (1, 2, 1024), (1, 1, 2048), (2, 2, 200), (1, 2, 1000), (1, 1, 4096),
+]
+
+
+def _mask(rng, batch, seq, kind):
+    if kind == "prefix":
+        lens = rng.integers(1, seq + 1, batch)
+        return (np.arange(seq)[None, :] < lens[:, None]).astype(np.int8)
+    if kind == "random":
+        m = rng.integers(0, 2, (batch, seq)).astype(np.int8)
+        m[:, 0] = 1
+        return m * rng.integers(1, 100, (batch, seq)).astype(np.int8)  # any non-zero value keeps
+    if kind == "empty_row":
+        m = np.ones((batch, seq), np.int8)
+        m[0, :] = 0  # a sequence with every key masked
+        return m
+    return None
+
+
+@pytest.mark.parametrize("t", DTYPES)
+@pytest.mark.parametrize("kind", ["prefix", "random", "empty_row", "none"])
+@pytest.mark.parametrize("batch,heads,seq", SOFTMAX_SHAPES)
+def test_masked_softmax(oracle, t, kind, batch, heads, seq):
+    rng = np.random.default_rng(batch * 1000 + heads * 100 + seq)
+    x, xh = _prep(rng.standard_normal((batch, seq, heads, seq)) * 3, t)
+    mask = _mask(rng, batch, seq, kind)
+    scale = 0.125 if kind != "none" else 1.0
+    ref = oracle.masked_softmax(xh, mask, scale)
+    got = G.masked_softmax(x.view(-1, seq), None if mask is None else G.dev(mask), seq * heads, scale, t)
+    # probabilities: relative to max(|p|, 1e-4) -- a masked key is exactly 0 on both sides
+    _check(got.view(batch, seq, heads, seq), ref, t, 1e-4 if t == "f32" else 1e-1, "softmax " + kind)
+    if kind == "prefix":
+        p = G.host(got).reshape(batch, seq, heads, seq)
+        assert np.all(p[np.broadcast_to(mask[:, None, None, :] == 0, p.shape)] == 0)
+    # in place
+    got2 = G.masked_softmax(x.view(-1, seq).clone(), None if mask is None else G.dev(mask), seq * heads, scale, t,
+                            inplace=True)
+    assert torch.equal(got, got2)
+
+
+# ============================================================================ K1 embedding + add + LayerNorm
+
+@pytest.mark.parametrize("t", DTYPES)
+@pytest.mark.parametrize("batch,seq,hidden,vocab", [(2, 4, 3, 5), (3, 7, 10, 11), (4, 32, 768, 2000), (2, 128, 1024, 3000),
+                                                    (1, 16, 200, 50), (2, 5, 4096, 30)])
+def test_embed_ln(oracle, t, batch, seq, hidden, vocab):
+    rng = np.random.default_rng(hidden + vocab)
+    word, wh = _prep(rng.standard_normal((vocab, hidden)) * 0.02, t)
+    pos, ph = _prep(rng.standard_normal((seq + 3, hidden)) * 0.02, t)
+    typ, th = _prep(rng.standard_normal((2, hidden)) * 0.02, t)
+    g, gh = _prep(1 + 0.1 * rng.standard_normal(hidden), t)
+    be, beh = _prep(0.1 * rng.standard_normal(hidden), t)
+    ids = rng.integers(0, vocab, (batch, seq), dtype=np.int32)
+    seg = rng.integers(0, 2, (batch, seq)).astype(np.int8)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = G.embed_ln(G.dev(ids), G.dev(seg), word, pos, typ, g, be, t, status)
+    ref = oracle.bert_embeddings(ids, seg, wh, ph[:seq], th, beh, gh)
+    _check(got, ref, t, 1.0, "embed_ln")
+    assert int(status.item()) == 0
+
+
+def test_embed_out_of_range_ids_are_clamped_and_flagged(oracle):
+    rng = np.random.default_rng(0)
+    vocab, hidden, seq = 10, 768, 4
+    word = rng.standard_normal((vocab, hidden)).astype(np.float32)
+    pos = rng.standard_normal((seq, hidden)).astype(np.float32)
+    typ = rng.standard_normal((2, hidden)).astype(np.float32)
+    g, be = np.ones(hidden, np.float32), np.zeros(hidden, np.float32)
+    ids = np.array([[1, 99, -5, 3]], np.int32)
+    seg = np.array([[0, 1, 7, -1]], np.int8)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = G.embed_ln(G.dev(ids), G.dev(seg), G.dev(word), G.dev(pos), G.dev(typ), G.dev(g), G.dev(be), "f32", status)
+    ref = oracle.bert_embeddings(np.array([[1, 9, 0, 3]], np.int32), np.array([[0, 1, 1, 0]], np.int8),
+                                 word, pos, typ, be, g)
+    G.assert_close(G.host(got), ref, G.F32_RTOL, 1.0, "clamped")
+    assert int(status.item()) == (kernels.STATUS_BAD_TOKEN_ID | kernels.STATUS_BAD_SEGMENT_ID)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("width", [3, 8, 768, 1000])
+@pytest.mark.parametrize("idt", [np.int32, np.int8])
+def test_embed_gather_bit_exact(dtype, width, idt):
+    rng = np.random.default_rng(width)
+    vocab = 100
+    table = torch.from_numpy(rng.standard_normal((vocab, width)).astype(np.float32)).to(dtype).cuda()
+    ids = rng.integers(0, vocab, 777).astype(idt)
+    got = G.embed_gather(G.dev(ids), table)
+    assert torch.equal(got, table[torch.from_numpy(ids.astype(np.int64)).cuda()])
+
+
+# ============================================================================ K5b mean pool, K5c classifier head
+
+@pytest.mark.parametrize("t", DTYPES)
+@pytest.mark.parametrize("batch,seq,hidden", [(2, 3, 2), (3, 5, 7), (4, 32, 768), (2, 512, 1024), (64, 512, 1024),
+                                              (1, 128, 768), (300, 16, 64), (2, 100, 200)])
+def test_mean_pool(oracle, t, batch, seq, hidden):
+    rng = np.random.default_rng(batch + seq + hidden)
+    x, xh = _prep(rng.standard_normal((batch, seq, hidden)), t)
+    got = G.mean_pool(x, t)
+    _check(got, oracle.reduce_mean_1(xh), t, 0.1, "mean_pool")
+
+
+def test_mean_pool_scratch_contract():
+    lib = kernels.load()
+    assert lib.cubk_mean_pool_scratch_bytes(512, 512, 1024) == 0      # enough blocks without splitting
+    need = lib.cubk_mean_pool_scratch_bytes(2, 512, 1024)
+    assert need > 0
+    x = torch.randn((2, 512, 1024), device="cuda")
+    out = torch.empty((2, 1024), device="cuda")
+    rc = lib.cubk_mean_pool_f32(x.data_ptr(), 2, 512, 1024, out.data_ptr(), None, 0, G.stream())
+    assert rc == kernels.CUBK_ERR_SCRATCH
+    small = torch.empty(need - 4, dtype=torch.uint8, device="cuda")
+    rc = lib.cubk_mean_pool_f32(x.data_ptr(), 2, 512, 1024, out.data_ptr(), small.data_ptr(), need - 4, G.stream())
+    assert rc == kernels.CUBK_ERR_SCRATCH
+
+
+@pytest.mark.parametrize("t", DTYPES)
+@pytest.mark.parametrize("batch,hidden,labels,bias", [(2, 3, 1, False), (128, 768, 2, True), (5, 1024, 3, True),
+                                                      (3, 100, 37, True), (2, 64, 1000, False)])
+def test_logits_probs(oracle, t, batch, hidden, labels, bias):
+    rng = np.random.default_rng(batch + hidden + labels)
+    x, xh = _prep(rng.standard_normal((batch, hidden)), t)
+    w, wh = _prep(rng.standard_normal((labels, hidden)) * 0.1, t)
+    b, bh = _prep(rng.standard_normal(labels), t) if bias else (None, None)
+    logits, probs = G.logits_probs(x, w, b, t)
+    ref_logits, ref_probs = oracle.classifier(xh, wh, bh)
+    _check(logits, ref_logits, t, 1.0, "logits")
+    _check(probs, ref_probs, t, 1e-3 if t == "f32" else 1e-1, "probs")
+
+
+# ============================================================================ helpers and argument checking
+
+def test_half_to_float_and_not():
+    rng = np.random.default_rng(1)
+    for n in (1, 7, 8, 1000, 4099):
+        h = torch.from_numpy(rng.standard_normal(n).astype(np.float16)).cuda()
+        assert torch.equal(G.half_to_float(h), h.float())
+        m = torch.from_numpy(rng.integers(-2, 3, n).astype(np.int8)).cuda()
+        assert torch.equal(G.logical_not(m, "f16").float(), (m == 0).float())
+
+
+def test_argument_checks_and_empty_inputs():
+    lib = kernels.load()
+    x = torch.zeros((4, 8), device="cuda")
+    s = G.stream()
+    assert lib.cubk_bias_residual_ln_f32(None, None, None, x.data_ptr(), x.data_ptr(), 4, 8, x.data_ptr(), s) \
+        == kernels.CUBK_ERR_INVALID_ARG
+    assert lib.cubk_bias_gelu_f32(x.data_ptr(), None, 4, 0, x.data_ptr(), s) == kernels.CUBK_ERR_INVALID_ARG
+    assert lib.cubk_masked_softmax_f32(x.data_ptr(), x.data_ptr(), 4, 0, 8, 1.0, x.data_ptr(), s) \
+        == kernels.CUBK_ERR_INVALID_ARG
+    assert lib.cubk_logits_probs_f32(x.data_ptr(), x.data_ptr(), None, 4, 8, 5000, x.data_ptr(), None, s) \
+        == kernels.CUBK_ERR_UNSUPPORTED
+    # batch 0 / rows 0: success, nothing launched (src/cuBERT/Bert.cpp:102-103 returns silently)
+    assert lib.cubk_bias_residual_ln_f32(x.data_ptr(), None, None, x.data_ptr(), x.data_ptr(), 0, 8, x.data_ptr(), s) == 0
+    assert lib.cubk_bias_gelu_f32(x.data_ptr(), None, 0, 8, x.data_ptr(), s) == 0
+    assert lib.cubk_masked_softmax_f32(x.data_ptr(), None, 0, 1, 8, 1.0, x.data_ptr(), s) == 0
+    assert lib.cubk_mean_pool_f32(x.data_ptr(), 0, 4, 8, x.data_ptr(), None, 0, s) == 0
+    torch.cuda.synchronize()

@@ -1,0 +1,483 @@
+#include "bert.h"
+
+#include <cmath>
+#include <cstring>
+#include <iostream>
+
+#include "cubert_kernels.h"
+
+namespace cubert {
+
+namespace {
+
+// Kernel entry points by storage type.
+template <typename T>
+struct K;
+
+template <>
+struct K<float> {
+    static constexpr auto embed_ln = cubk_embed_ln_f32;
+    static constexpr auto bias_residual_ln = cubk_bias_residual_ln_f32;
+    static constexpr auto bias_gelu = cubk_bias_gelu_f32;
+    static constexpr auto masked_softmax = cubk_masked_softmax_f32;
+    static constexpr auto bias_tanh = cubk_bias_tanh_f32;
+    static constexpr auto mean_pool = cubk_mean_pool_f32;
+    static constexpr auto logits_probs = cubk_logits_probs_f32;
+};
+
+template <>
+struct K<__half> {
+    static constexpr auto embed_ln = cubk_embed_ln_f16;
+    static constexpr auto bias_residual_ln = cubk_bias_residual_ln_f16;
+    static constexpr auto bias_gelu = cubk_bias_gelu_f16;
+    static constexpr auto masked_softmax = cubk_masked_softmax_f16;
+    static constexpr auto bias_tanh = cubk_bias_tanh_f16;
+    static constexpr auto mean_pool = cubk_mean_pool_f16;
+    static constexpr auto logits_probs = cubk_logits_probs_f16;
+};
+
+template <typename T>
+const T *find(const std::unordered_map<std::string, const T *> &var, const std::string &name) {
+    auto it = var.find(name);
+    if (it == var.end()) {
+        throw std::invalid_argument("model has no tensor named " + name);
+    }
+    return it->second;
+}
+
+template <typename T>
+void upload(DeviceBuffer &dst, const T *src, size_t count) {
+    dst.allocate(count * sizeof(T));
+    dst.upload(src, count * sizeof(T));
+}
+
+}  // namespace
+
+template <typename T>
+Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_batch_size_, size_t seq_length_,
+              size_t vocab_size_, size_t type_vocab_size_, size_t hidden_size_, size_t num_hidden_layers_,
+              size_t num_attention_heads_, size_t intermediate_size_, size_t num_labels_, int device)
+    : max_batch_size(max_batch_size_),
+      seq_length(seq_length_),
+      vocab_size(vocab_size_),
+      type_vocab_size(type_vocab_size_),
+      hidden_size(hidden_size_),
+      num_hidden_layers(num_hidden_layers_),
+      num_attention_heads(num_attention_heads_),
+      intermediate_size(intermediate_size_),
+      num_labels(num_labels_),
+      device_(device) {
+    if (max_batch_size == 0 || seq_length == 0 || hidden_size == 0 || num_attention_heads == 0 ||
+        hidden_size % num_attention_heads != 0 || vocab_size == 0 || type_vocab_size == 0) {
+        throw std::invalid_argument("invalid model geometry");
+    }
+    CUDA_CHECK(cudaSetDevice(device_));
+    CUDA_CHECK(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+    blas_.reset(new Blas(stream_));
+
+    const bool half = Storage<T>::is_half;
+    algo_attention_ = gemm_algo_from_env("GEMM_ALGO_ATTENTION", half);
+    algo_intermediate_ = gemm_algo_from_env("GEMM_ALGO_INTERMEDIATE", half);
+    algo_output_ = gemm_algo_from_env("GEMM_ALGO_OUTPUT", half);
+    algo_pooler_ = gemm_algo_from_env("GEMM_ALGO_POOLER", half);
+    algo_qk_ = gemm_algo_from_env("GEMM_BATCH_ALGO_QK", half);
+    algo_qkv_ = gemm_algo_from_env("GEMM_BATCH_ALGO_QKV", half);
+
+    const size_t H = hidden_size, I = intermediate_size, S = seq_length, B = max_batch_size;
+    const size_t heads = num_attention_heads, d = H / heads;
+    const size_t R = B * S;
+
+    // ---- embeddings (only the first seq_length position rows are needed,
+    //      src/cuBERT/op_bert/BertEmbeddings.cpp:27-29)
+    upload(word_emb_, find(var, "bert/embeddings/word_embeddings"), vocab_size * H);
+    upload(type_emb_, find(var, "bert/embeddings/token_type_embeddings"), type_vocab_size * H);
+    upload(pos_emb_, find(var, "bert/embeddings/position_embeddings"), S * H);
+    upload(emb_ln_gamma_, find(var, "bert/embeddings/LayerNorm/gamma"), H);
+    upload(emb_ln_beta_, find(var, "bert/embeddings/LayerNorm/beta"), H);
+
+    // ---- encoder layers
+    layers_.resize(num_hidden_layers);
+    std::vector<T> fused(H * 3 * H), fused_bias(3 * H);
+    for (size_t l = 0; l < num_hidden_layers; ++l) {
+        const std::string p = "bert/encoder/layer_" + std::to_string(l);
+        Layer &L = layers_[l];
+        const T *w[3] = {find(var, p + "/attention/self/query/kernel"), find(var, p + "/attention/self/key/kernel"),
+                         find(var, p + "/attention/self/value/kernel")};
+        const T *b[3] = {find(var, p + "/attention/self/query/bias"), find(var, p + "/attention/self/key/bias"),
+                         find(var, p + "/attention/self/value/bias")};
+        for (size_t r = 0; r < H; ++r) {
+            for (int j = 0; j < 3; ++j) {
+                std::memcpy(static_cast<void *>(&fused[r * 3 * H + j * H]), w[j] + r * H, H * sizeof(T));
+            }
+        }
+        for (int j = 0; j < 3; ++j) {
+            std::memcpy(static_cast<void *>(&fused_bias[j * H]), b[j], H * sizeof(T));
+        }
+        upload(L.qkv_kernel, fused.data(), fused.size());
+        upload(L.qkv_bias, fused_bias.data(), fused_bias.size());
+        upload(L.att_out_kernel, find(var, p + "/attention/output/dense/kernel"), H * H);
+        upload(L.att_out_bias, find(var, p + "/attention/output/dense/bias"), H);
+        upload(L.att_ln_gamma, find(var, p + "/attention/output/LayerNorm/gamma"), H);
+        upload(L.att_ln_beta, find(var, p + "/attention/output/LayerNorm/beta"), H);
+        upload(L.inter_kernel, find(var, p + "/intermediate/dense/kernel"), H * I);
+        upload(L.inter_bias, find(var, p + "/intermediate/dense/bias"), I);
+        upload(L.out_kernel, find(var, p + "/output/dense/kernel"), I * H);
+        upload(L.out_bias, find(var, p + "/output/dense/bias"), H);
+        upload(L.out_ln_gamma, find(var, p + "/output/LayerNorm/gamma"), H);
+        upload(L.out_ln_beta, find(var, p + "/output/LayerNorm/beta"), H);
+    }
+
+    // ---- pooler and classifier (src/cuBERT/Bert.cpp:34-53)
+    has_pooler_dense_ = var.count("bert/pooler/dense/kernel") != 0;
+    if (has_pooler_dense_) {
+        upload(pooler_kernel_, find(var, "bert/pooler/dense/kernel"), H * H);
+        upload(pooler_bias_, find(var, "bert/pooler/dense/bias"), H);
+    }
+    has_classifier_ = var.count("output_weights") != 0;
+    if (has_classifier_) {
+        if (num_labels == 0) {
+            throw std::invalid_argument("classifier weights present but num_labels is 0");
+        }
+        upload(output_weights_, find(var, "output_weights"), num_labels * H);
+        has_classifier_bias_ = var.count("output_bias") != 0;
+        if (has_classifier_bias_) {
+            upload(output_bias_, find(var, "output_bias"), num_labels);
+        }
+        logits_.allocate(sizeof(T) * B * num_labels);
+        probs_.allocate(sizeof(T) * B * num_labels);
+    }
+
+    // ---- inputs, activations
+    ids_.allocate(sizeof(int32_t) * R);
+    mask_.allocate(sizeof(int8_t) * R);
+    segments_.allocate(sizeof(int8_t) * R);
+    status_.allocate(sizeof(uint32_t));
+    CUDA_CHECK(cudaMemset(status_.get(), 0, sizeof(uint32_t)));
+    embedding_.allocate(sizeof(T) * R * H);
+    hidden_[0].allocate(sizeof(T) * R * H);
+    hidden_[1].allocate(sizeof(T) * R * H);
+    qkv_.allocate(sizeof(T) * R * 3 * H);
+    scores_.allocate(sizeof(T) * B * heads * S * S);
+    context_.allocate(sizeof(T) * R * H);
+    dense_out_.allocate(sizeof(T) * R * H);
+    att_out_.allocate(sizeof(T) * R * H);
+    inter_.allocate(sizeof(T) * R * I);
+    pooled_.allocate(sizeof(T) * B * H);
+    if (!has_pooler_dense_) {
+        // small batches split the sequence axis further, so size the scratch for the worst batch
+        size_t need = 0;
+        for (size_t b = 1; b <= B; ++b) {
+            const size_t n = cubk_mean_pool_scratch_bytes((int) b, (int) S, (int) H);
+            need = n > need ? n : need;
+        }
+        if (need > 0) {
+            pool_scratch_.allocate(need);
+        }
+    }
+    if (half) {
+        float_staging_.allocate(sizeof(float) * R * H);
+    }
+
+    // ---- pointer arrays of the batched attention products, one entry per (sequence, head).
+    // Layouts follow src/cuBERT/op_att/BatchMatMul.h:10-14: Q/K/V [B, S, heads, d] (here the three
+    // interleaved in one [B*S, 3*hidden] buffer), scores [B, S, heads, S], context [B, S, heads, d].
+    std::vector<const T *> qp(B * heads), kp(B * heads), vp(B * heads);
+    std::vector<T *> sp(B * heads), cp(B * heads);
+    for (size_t b = 0; b < B; ++b) {
+        for (size_t h = 0; h < heads; ++h) {
+            const T *base = qkv_.template as<T>() + b * S * 3 * H + h * d;
+            qp[b * heads + h] = base;
+            kp[b * heads + h] = base + H;
+            vp[b * heads + h] = base + 2 * H;
+            sp[b * heads + h] = scores_.template as<T>() + b * S * S * heads + S * h;
+            cp[b * heads + h] = context_.template as<T>() + b * S * H + h * d;
+        }
+    }
+    upload(q_ptrs_, qp.data(), qp.size());
+    upload(k_ptrs_, kp.data(), kp.size());
+    upload(v_ptrs_, vp.data(), vp.size());
+    upload(score_ptrs_, sp.data(), sp.size());
+    upload(ctx_ptrs_, cp.data(), cp.size());
+
+    sequence_output_ = num_hidden_layers == 0 ? embedding_.template as<T>() : hidden_[(num_hidden_layers - 1) % 2].template as<T>();
+    CUDA_CHECK(cudaDeviceSynchronize());
+}
+
+template <typename T>
+Bert<T>::~Bert() {
+    cudaSetDevice(device_);
+    if (stream_ != nullptr) {
+        cudaStreamSynchronize(stream_);
+    }
+    for (cudaEvent_t e : event_pool_) {
+        cudaEventDestroy(e);
+    }
+    for (Timed &t : pending_) {
+        cudaEventDestroy(t.start);
+        cudaEventDestroy(t.stop);
+    }
+    blas_.reset();
+    if (stream_ != nullptr) {
+        cudaStreamDestroy(stream_);
+    }
+}
+
+// ------------------------------------------------------------------ profiling
+template <typename T>
+cudaEvent_t Bert<T>::take_event() {
+    if (!event_pool_.empty()) {
+        cudaEvent_t e = event_pool_.back();
+        event_pool_.pop_back();
+        return e;
+    }
+    cudaEvent_t e;
+    CUDA_CHECK(cudaEventCreate(&e));
+    return e;
+}
+
+template <typename T>
+void Bert<T>::begin(int family) {
+    (void) family;
+    if (profiling_) {
+        open_start_ = take_event();
+        CUDA_CHECK(cudaEventRecord(open_start_, stream_));
+    }
+}
+
+template <typename T>
+void Bert<T>::end(int family, int64_t bytes) {
+    launches_[family] += 1;
+    bytes_[family] += bytes;
+    if (profiling_) {
+        cudaEvent_t stop = take_event();
+        CUDA_CHECK(cudaEventRecord(stop, stream_));
+        pending_.push_back(Timed{family, open_start_, stop});
+        open_start_ = nullptr;
+    }
+}
+
+template <typename T>
+void Bert<T>::profile_enable(bool on) {
+    CUDA_CHECK(cudaSetDevice(device_));
+    profiling_ = on;
+}
+
+template <typename T>
+void Bert<T>::profile_read(cubert_b200_profile *out) {
+    CUDA_CHECK(cudaSetDevice(device_));
+    CUDA_CHECK(cudaStreamSynchronize(stream_));
+    for (Timed &t : pending_) {
+        float ms = 0.f;
+        CUDA_CHECK(cudaEventElapsedTime(&ms, t.start, t.stop));
+        ms_[t.family] += ms;
+        event_pool_.push_back(t.start);
+        event_pool_.push_back(t.stop);
+    }
+    pending_.clear();
+    for (int k = 0; k < CUBERT_B200_K_COUNT; ++k) {
+        out->ms[k] = ms_[k];
+        out->launches[k] = launches_[k];
+        out->bytes[k] = bytes_[k];
+        ms_[k] = 0.0;
+        launches_[k] = 0;
+        bytes_[k] = 0;
+    }
+}
+
+// ------------------------------------------------------------------ forward pass
+template <typename T>
+void Bert<T>::compute(size_t batch_size, const int *input_ids, const int8_t *input_mask,
+                      const int8_t *segment_ids) {
+    if (batch_size > max_batch_size) {
+        throw std::invalid_argument("batch_size > max_batch_size");
+    } else if (batch_size == 0) {
+        return;
+    }
+    if (input_ids == nullptr || input_mask == nullptr || segment_ids == nullptr) {
+        throw std::invalid_argument("null input");
+    }
+    CUDA_CHECK(cudaSetDevice(device_));
+    const size_t n = batch_size * seq_length;
+    CUDA_CHECK(cudaMemcpyAsync(ids_.get(), input_ids, sizeof(int32_t) * n, cudaMemcpyHostToDevice, stream_));
+    CUDA_CHECK(cudaMemcpyAsync(mask_.get(), input_mask, sizeof(int8_t) * n, cudaMemcpyHostToDevice, stream_));
+    CUDA_CHECK(cudaMemcpyAsync(segments_.get(), segment_ids, sizeof(int8_t) * n, cudaMemcpyHostToDevice, stream_));
+    forward(batch_size, ids_.template as<int32_t>(), mask_.template as<int8_t>(), segments_.template as<int8_t>());
+}
+
+template <typename T>
+void Bert<T>::compute_device(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask,
+                             const int8_t *d_segments) {
+    if (batch_size > max_batch_size) {
+        throw std::invalid_argument("batch_size > max_batch_size");
+    } else if (batch_size == 0) {
+        return;
+    }
+    if (d_ids == nullptr || d_mask == nullptr || d_segments == nullptr) {
+        throw std::invalid_argument("null input");
+    }
+    CUDA_CHECK(cudaSetDevice(device_));
+    forward(batch_size, d_ids, d_mask, d_segments);
+}
+
+template <typename T>
+void Bert<T>::forward(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments) {
+    const int B = (int) batch_size, S = (int) seq_length, H = (int) hidden_size, I = (int) intermediate_size;
+    const int heads = (int) num_attention_heads, d = H / heads;
+    const int64_t R = (int64_t) B * S;
+    const int64_t e = sizeof(T);
+    void *st = stream_;
+
+    // K1: embeddings (src/cuBERT/op_bert/BertEmbeddings.cpp:50-66)
+    begin(CUBERT_B200_K_EMBED_LN);
+    KERNEL_CHECK(K<T>::embed_ln(d_ids, d_segments, word_emb_.template as<T>(), pos_emb_.template as<T>(), type_emb_.template as<T>(),
+                                emb_ln_gamma_.template as<T>(), emb_ln_beta_.template as<T>(), B, S, H, (int) vocab_size,
+                                (int) type_vocab_size, embedding_.template as<T>(), status_.template as<uint32_t>(), st));
+    end(CUBERT_B200_K_EMBED_LN, 2 * R * H * e + 5 * R + (int64_t) S * H * e + (int64_t) type_vocab_size * H * e +
+                                    2 * H * e);
+
+    // encoder (src/cuBERT/op_att/Transformer.cpp:145-175, op_att/AttentionSelf.cpp:96-111)
+    const float att_scale = (float) (1.0 / std::sqrt((double) d));  // op_att/AttentionSelf.cpp:58-60
+    const T *x = embedding_.template as<T>();
+    for (size_t l = 0; l < num_hidden_layers; ++l) {
+        Layer &L = layers_[l];
+        T *y = hidden_[l % 2].template as<T>();
+
+        // Q, K, V in one projection with the bias in the GEMM epilogue
+        begin(CUBERT_B200_K_GEMM);
+        blas_->gemm_bias<T>(3 * H, (int) R, H, L.qkv_kernel.template as<T>(), 3 * H, x, H, L.qkv_bias.template as<T>(), qkv_.template as<T>(),
+                            3 * H);
+        end(CUBERT_B200_K_GEMM, 0);
+
+        // scores[b, i, h, j] = (1/sqrt(d)) * sum_c K[b,j,h,c] * Q[b,i,h,c]   (op_att/BatchMatMul.cpp:57-68)
+        begin(CUBERT_B200_K_GEMM);
+        blas_->gemm_batched<T>(true, false, S, S, d, att_scale, k_ptrs_.template as<const T *>(), 3 * H,
+                               q_ptrs_.template as<const T *>(), 3 * H, 0.f, score_ptrs_.template as<T *>(), S * heads, B * heads,
+                               algo_qk_);
+        end(CUBERT_B200_K_GEMM, 0);
+
+        // K4: mask + softmax in place over rows [B*S*heads, S]
+        begin(CUBERT_B200_K_MASKED_SOFTMAX);
+        KERNEL_CHECK(K<T>::masked_softmax(scores_.template as<T>(), d_mask, R * heads, (int64_t) S * heads, S, 1.0f,
+                                          scores_.template as<T>(), st));
+        end(CUBERT_B200_K_MASKED_SOFTMAX, 2 * R * heads * S * e + R);
+
+        // context[b, i, h, c] = sum_j V[b,j,h,c] * P[b,i,h,j]   (op_att/BatchMatMul.cpp:124-135)
+        begin(CUBERT_B200_K_GEMM);
+        blas_->gemm_batched<T>(false, false, d, S, S, 1.f, v_ptrs_.template as<const T *>(), 3 * H,
+                               score_ptrs_.template as<const T *>(), S * heads, 0.f, ctx_ptrs_.template as<T *>(), H, B * heads,
+                               algo_qkv_);
+        end(CUBERT_B200_K_GEMM, 0);
+
+        // attention output projection, then K2: LayerNorm(dense + bias + layer input)
+        begin(CUBERT_B200_K_GEMM);
+        blas_->gemm<T>(false, false, H, (int) R, H, 1.f, L.att_out_kernel.template as<T>(), H, context_.template as<T>(), H, 0.f,
+                       dense_out_.template as<T>(), H, algo_attention_);
+        end(CUBERT_B200_K_GEMM, 0);
+        begin(CUBERT_B200_K_BIAS_RESIDUAL_LN);
+        KERNEL_CHECK(K<T>::bias_residual_ln(dense_out_.template as<T>(), L.att_out_bias.template as<T>(), x, L.att_ln_gamma.template as<T>(),
+                                            L.att_ln_beta.template as<T>(), R, H, att_out_.template as<T>(), st));
+        end(CUBERT_B200_K_BIAS_RESIDUAL_LN, 3 * R * H * e + 3 * H * e);
+
+        // intermediate projection, then K3: bias + GELU in place
+        begin(CUBERT_B200_K_GEMM);
+        blas_->gemm<T>(false, false, I, (int) R, H, 1.f, L.inter_kernel.template as<T>(), I, att_out_.template as<T>(), H, 0.f,
+                       inter_.template as<T>(), I, algo_intermediate_);
+        end(CUBERT_B200_K_GEMM, 0);
+        begin(CUBERT_B200_K_BIAS_GELU);
+        KERNEL_CHECK(K<T>::bias_gelu(inter_.template as<T>(), L.inter_bias.template as<T>(), R, I, inter_.template as<T>(), st));
+        end(CUBERT_B200_K_BIAS_GELU, 2 * R * I * e + I * e);
+
+        // output projection, then K2: LayerNorm(dense + bias + attention output)
+        begin(CUBERT_B200_K_GEMM);
+        blas_->gemm<T>(false, false, H, (int) R, I, 1.f, L.out_kernel.template as<T>(), H, inter_.template as<T>(), I, 0.f,
+                       dense_out_.template as<T>(), H, algo_output_);
+        end(CUBERT_B200_K_GEMM, 0);
+        begin(CUBERT_B200_K_BIAS_RESIDUAL_LN);
+        KERNEL_CHECK(K<T>::bias_residual_ln(dense_out_.template as<T>(), L.out_bias.template as<T>(), att_out_.template as<T>(),
+                                            L.out_ln_gamma.template as<T>(), L.out_ln_beta.template as<T>(), R, H, y, st));
+        end(CUBERT_B200_K_BIAS_RESIDUAL_LN, 3 * R * H * e + 3 * H * e);
+
+        x = y;
+    }
+
+    // pooler (src/cuBERT/op_bert/BertPooler.cpp:62-77,93-96)
+    if (has_pooler_dense_) {
+        begin(CUBERT_B200_K_GEMM);
+        blas_->gemm<T>(false, false, H, B, H, 1.f, pooler_kernel_.template as<T>(), H, x, H * S, 0.f, pooled_.template as<T>(), H,
+                       algo_pooler_);
+        end(CUBERT_B200_K_GEMM, 0);
+        begin(CUBERT_B200_K_BIAS_TANH);
+        KERNEL_CHECK(K<T>::bias_tanh(pooled_.template as<T>(), pooler_bias_.template as<T>(), B, H, pooled_.template as<T>(), st));
+        end(CUBERT_B200_K_BIAS_TANH, 2 * (int64_t) B * H * e + H * e);
+    } else {
+        begin(CUBERT_B200_K_MEAN_POOL);
+        KERNEL_CHECK(K<T>::mean_pool(x, B, S, H, pooled_.template as<T>(), pool_scratch_.get(), pool_scratch_.bytes(), st));
+        end(CUBERT_B200_K_MEAN_POOL, R * H * e + (int64_t) B * H * e);
+    }
+
+    // classifier head (src/cuBERT/op_out/AdditionalOutputLayer.cpp:44-66)
+    if (has_classifier_) {
+        begin(CUBERT_B200_K_LOGITS_PROBS);
+        KERNEL_CHECK(K<T>::logits_probs(pooled_.template as<T>(), output_weights_.template as<T>(),
+                                        has_classifier_bias_ ? output_bias_.template as<T>() : nullptr, B, H,
+                                        (int) num_labels, logits_.template as<T>(), probs_.template as<T>(), st));
+        end(CUBERT_B200_K_LOGITS_PROBS,
+            (int64_t) B * H * e + (int64_t) num_labels * H * e + 2 * (int64_t) B * num_labels * e);
+    }
+}
+
+// ------------------------------------------------------------------ outputs
+template <typename T>
+void Bert<T>::output(size_t batch_size, cuBERT_Output *out, bool to_float) {
+    if (batch_size == 0) {
+        return;
+    }
+    CUDA_CHECK(cudaSetDevice(device_));
+    const size_t B = batch_size, S = seq_length, H = hidden_size;
+    if ((out->logits != nullptr || out->probs != nullptr) && !has_classifier_) {
+        // the reference warns and copies from unallocated buffers (src/cuBERT/Bert.cpp:140-142)
+        std::cerr << "model does not have additional_output_layer, the output logits is wrong." << std::endl;
+    }
+    auto copy = [&](void *dst, const T *src, size_t count) {
+        if (dst == nullptr || src == nullptr) {
+            return;
+        }
+        if (to_float && Storage<T>::is_half) {
+            begin(CUBERT_B200_K_HALF_TO_FLOAT);
+            KERNEL_CHECK(cubk_half_to_float(src, float_staging_.template as<float>(), (int64_t) count, stream_));
+            end(CUBERT_B200_K_HALF_TO_FLOAT, (int64_t) count * 6);
+            CUDA_CHECK(cudaMemcpyAsync(dst, float_staging_.get(), sizeof(float) * count, cudaMemcpyDeviceToHost,
+                                       stream_));
+        } else {
+            CUDA_CHECK(cudaMemcpyAsync(dst, src, sizeof(T) * count, cudaMemcpyDeviceToHost, stream_));
+        }
+    };
+    copy(out->logits, has_classifier_ ? logits_.template as<T>() : nullptr, B * num_labels);
+    copy(out->probs, has_classifier_ ? probs_.template as<T>() : nullptr, B * num_labels);
+    copy(out->pooled_output, pooled_.template as<T>(), B * H);
+    copy(out->sequence_output, sequence_output_, B * S * H);
+    copy(out->embedding_output, embedding_.template as<T>(), B * S * H);
+    CUDA_CHECK(cudaStreamSynchronize(stream_));
+}
+
+template <typename T>
+void Bert<T>::synchronize() {
+    CUDA_CHECK(cudaSetDevice(device_));
+    CUDA_CHECK(cudaStreamSynchronize(stream_));
+}
+
+template <typename T>
+cuBERT_Output Bert<T>::device_outputs() const {
+    cuBERT_Output o;
+    o.logits = has_classifier_ ? logits_.get() : nullptr;
+    o.probs = has_classifier_ ? probs_.get() : nullptr;
+    o.pooled_output = pooled_.get();
+    o.sequence_output = sequence_output_;
+    o.embedding_output = embedding_.get();
+    return o;
+}
+
+template class Bert<float>;
+template class Bert<__half>;
+
+}  // namespace cubert

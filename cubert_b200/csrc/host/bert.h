@@ -1,0 +1,117 @@
+// One BERT replica on one GPU: weights, activation buffers, a stream, and the forward pass.
+//
+// Mirrors the reference's Bert<T> (src/cuBERT/Bert.h:15-75, Bert.cpp) in interface and
+// results; the execution plan underneath is different:
+//   * every non-GEMM step is one of the fused kernels of include/cubert_kernels.h
+//     (K1 embeddings, K2 bias+residual+LayerNorm, K3 bias+GELU, K4 masked softmax, K5 heads);
+//   * GEMMs run with beta = 0: no replicated bias buffers, no bias refill after each request
+//     (src/cuBERT/op/Dense.cpp:22-25,41-45, Bert.cpp:88-96), no broadcast mask tensor and no
+//     per-layer device copy of it (op_att/AttentionSelf.cpp:99-101);
+//   * Q, K and V come from one [hidden, 3*hidden] projection;
+//   * activation buffers are shared by all layers instead of allocated per layer
+//     (op_att/Transformer.cpp:38-43), so memory is O(batch) and not O(layers * batch).
+#pragma once
+
+#include <array>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "blas.h"
+#include "cuBERT.h"
+#include "cubert_b200.h"
+#include "frozen_graph.h"
+#include "runtime.h"
+
+namespace cubert {
+
+template <typename T>
+class Bert {
+public:
+    // `var`: TensorFlow variable name -> host array in storage type T, as the loader yields it.
+    Bert(const std::unordered_map<std::string, const T *> &var, size_t max_batch_size, size_t seq_length,
+         size_t vocab_size, size_t type_vocab_size, size_t hidden_size, size_t num_hidden_layers,
+         size_t num_attention_heads, size_t intermediate_size, size_t num_labels, int device);
+    ~Bert();
+    Bert(const Bert &) = delete;
+    Bert &operator=(const Bert &) = delete;
+
+    // Host inputs -> device, then the forward pass; asynchronous on the replica's stream.
+    // Throws std::invalid_argument when batch_size > max_batch_size; batch_size == 0 is a no-op.
+    void compute(size_t batch_size, const int *input_ids, const int8_t *input_mask, const int8_t *segment_ids);
+
+    // Forward pass on inputs already in this replica's device memory.
+    void compute_device(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments);
+
+    // Copy the non-NULL outputs to the host and wait for them (src/cuBERT/Bert.cpp:185-208).
+    // With to_float, a binary16 model converts on the device first (Bert.cpp:218-259 does it on the host).
+    void output(size_t batch_size, cuBERT_Output *out, bool to_float);
+
+    void synchronize();
+    cuBERT_Output device_outputs() const;
+    cudaStream_t stream() const { return stream_; }
+    int device() const { return device_; }
+    bool has_classifier() const { return has_classifier_; }
+    bool has_pooler_dense() const { return has_pooler_dense_; }
+
+    void profile_enable(bool on);
+    void profile_read(cubert_b200_profile *out);
+
+    size_t max_batch_size, seq_length, vocab_size, type_vocab_size, hidden_size, num_hidden_layers,
+        num_attention_heads, intermediate_size, num_labels;
+
+private:
+    struct Layer {
+        DeviceBuffer qkv_kernel, qkv_bias;           // [hidden, 3*hidden], [3*hidden]
+        DeviceBuffer att_out_kernel, att_out_bias;   // [hidden, hidden], [hidden]
+        DeviceBuffer att_ln_gamma, att_ln_beta;
+        DeviceBuffer inter_kernel, inter_bias;       // [hidden, intermediate], [intermediate]
+        DeviceBuffer out_kernel, out_bias;           // [intermediate, hidden], [hidden]
+        DeviceBuffer out_ln_gamma, out_ln_beta;
+    };
+
+    void forward(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments);
+
+    // profiling: brackets one launch with events when enabled, always counts
+    struct Scope;
+    void begin(int family);
+    void end(int family, int64_t bytes);
+
+    int device_;
+    cudaStream_t stream_ = nullptr;
+    std::unique_ptr<Blas> blas_;
+    bool has_pooler_dense_ = false;
+    bool has_classifier_ = false;
+    bool has_classifier_bias_ = false;
+
+    // weights
+    DeviceBuffer word_emb_, type_emb_, pos_emb_, emb_ln_gamma_, emb_ln_beta_;
+    std::vector<Layer> layers_;
+    DeviceBuffer pooler_kernel_, pooler_bias_, output_weights_, output_bias_;
+
+    // inputs and activations (shared by all layers)
+    DeviceBuffer ids_, mask_, segments_, status_;
+    DeviceBuffer embedding_, hidden_[2], qkv_, scores_, context_, dense_out_, att_out_, inter_;
+    DeviceBuffer pooled_, logits_, probs_, pool_scratch_, float_staging_;
+    DeviceBuffer q_ptrs_, k_ptrs_, v_ptrs_, score_ptrs_, ctx_ptrs_;
+    T *sequence_output_ = nullptr;
+
+    int algo_attention_, algo_intermediate_, algo_output_, algo_pooler_, algo_qk_, algo_qkv_;
+
+    // profiling state
+    bool profiling_ = false;
+    std::array<int64_t, CUBERT_B200_K_COUNT> launches_{};
+    std::array<int64_t, CUBERT_B200_K_COUNT> bytes_{};
+    std::array<double, CUBERT_B200_K_COUNT> ms_{};
+    struct Timed {
+        int family;
+        cudaEvent_t start, stop;
+    };
+    std::vector<Timed> pending_;
+    std::vector<cudaEvent_t> event_pool_;
+    cudaEvent_t open_start_ = nullptr;
+    cudaEvent_t take_event();
+};
+
+}  // namespace cubert

@@ -1,0 +1,94 @@
+#include "bert_m.h"
+
+#include <chrono>
+#include <iostream>
+
+namespace cubert {
+
+template <typename T>
+BertM<T>::BertM(const char *model_file, size_t max_batch_size_, size_t seq_length_, size_t num_hidden_layers,
+                size_t num_attention_heads)
+    : seq_length(seq_length_), max_batch_size(max_batch_size_), graph(model_file), rr(0) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess) {
+        (void) cudaGetLastError();
+        count = 0;
+    }
+    if (count == 0) {
+        throw std::invalid_argument("No GPU device detected");
+    }
+    std::cerr << "Found GPU count: " << count << std::endl;
+    int per_gpu = env_int("CUBERT_NUM_MODELS_PER_GPU", 1);
+    if (per_gpu < 1) {
+        per_gpu = 1;
+    }
+
+    std::unordered_map<std::string, const T *> var;
+    for (auto &kv : graph.var) {
+        var[kv.first] = kv.second.data();
+    }
+    const size_t num_labels = graph.has("output_weights") ? graph.num_labels : 0;
+
+    for (int i = 0; i < count * per_gpu; ++i) {
+        const int device = i % count;  // replicas of one GPU are spread over the rotation
+        auto start = std::chrono::high_resolution_clock::now();
+        if (i < count) {
+            cudaDeviceProp prop;
+            CUDA_CHECK(cudaGetDeviceProperties(&prop, device));
+            std::cerr << "Found device " << device << " with properties:\n  name: " << prop.name
+                      << " major: " << prop.major << " minor: " << prop.minor << "\n  pciBusID: " << prop.pciBusID
+                      << "\n  totalMemory: " << prop.totalGlobalMem << std::endl;
+        }
+        bert_instances.emplace_back(new Bert<T>(var, max_batch_size, seq_length, graph.vocab_size,
+                                                graph.type_vocab_size, graph.hidden_size, num_hidden_layers,
+                                                num_attention_heads, graph.intermediate_size, num_labels,
+                                                device));
+        mutex_instances.emplace_back(new std::mutex());
+        auto finish = std::chrono::high_resolution_clock::now();
+        std::cerr << "device setup: " << device << ". Took "
+                  << std::chrono::duration_cast<std::chrono::milliseconds>(finish - start).count()
+                  << " milliseconds." << std::endl;
+    }
+}
+
+template <typename T>
+unsigned int BertM<T>::compute(size_t batch_size, int *input_ids, int8_t *input_mask, int8_t *segment_ids,
+                               void *output, cuBERT_OutputType output_type) {
+    cuBERT_Output out;
+    switch (output_type) {
+        case cuBERT_LOGITS:
+            out.logits = output;
+            break;
+        case cuBERT_PROBS:
+            out.probs = output;
+            break;
+        case cuBERT_POOLED_OUTPUT:
+            out.pooled_output = output;
+            break;
+        case cuBERT_EMBEDDING_OUTPUT:
+            out.embedding_output = output;
+            break;
+        case cuBERT_SEQUENCE_OUTPUT:
+            out.sequence_output = output;
+            break;
+        default:
+            throw std::invalid_argument("invalid output type");
+    }
+    return compute(batch_size, input_ids, input_mask, segment_ids, &out, false);
+}
+
+template <typename T>
+unsigned int BertM<T>::compute(size_t batch_size, int *input_ids, int8_t *input_mask, int8_t *segment_ids,
+                               cuBERT_Output *output, bool output_to_float) {
+    const unsigned int choice = (unsigned int) (rr.fetch_add(1) % bert_instances.size());
+    Bert<T> *bert = bert_instances[choice].get();
+    std::lock_guard<std::mutex> lg(*mutex_instances[choice]);
+    bert->compute(batch_size, input_ids, input_mask, segment_ids);
+    bert->output(batch_size, output, output_to_float);
+    return choice;
+}
+
+template class BertM<float>;
+template class BertM<__half>;
+
+}  // namespace cubert

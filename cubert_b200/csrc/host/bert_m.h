@@ -1,0 +1,46 @@
+// Replica manager: one Bert per GPU (times CUBERT_NUM_MODELS_PER_GPU), round-robin dispatch and
+// one mutex per replica, as the reference's BertM<T> (src/cuBERT/BertM.h:15-45, BertM.cpp:12-121).
+// The replicas share nothing on the device and never communicate: the batch dimension is the
+// only parallel axis, so there is no collective anywhere.
+#pragma once
+
+#include <atomic>
+#include <memory>
+#include <mutex>
+#include <vector>
+
+#include "bert.h"
+#include "frozen_graph.h"
+
+namespace cubert {
+
+template <typename T>
+class BertM {
+public:
+    BertM(const char *model_file, size_t max_batch_size, size_t seq_length, size_t num_hidden_layers,
+          size_t num_attention_heads);
+
+    // Single selected output (src/cuBERT/BertM.cpp:65-99). Returns the replica that served the call.
+    unsigned int compute(size_t batch_size, int *input_ids, int8_t *input_mask, int8_t *segment_ids, void *output,
+                         cuBERT_OutputType output_type);
+
+    // Every non-NULL field of `output` (src/cuBERT/BertM.cpp:101-121).
+    unsigned int compute(size_t batch_size, int *input_ids, int8_t *input_mask, int8_t *segment_ids,
+                         cuBERT_Output *output, bool output_to_float);
+
+    size_t replicas() const { return bert_instances.size(); }
+    Bert<T> *replica(size_t i) { return bert_instances.at(i).get(); }
+
+    size_t seq_length;
+    size_t max_batch_size;
+
+private:
+    FrozenGraph<T> graph;
+    std::vector<std::unique_ptr<Bert<T>>> bert_instances;
+    std::vector<std::unique_ptr<std::mutex>> mutex_instances;
+    // The reference counts in a uint8_t, which skews the rotation whenever 256 is not a multiple
+    // of the replica count (src/cuBERT/BertM.h:44); a wide counter keeps it even.
+    std::atomic<uint64_t> rr;
+};
+
+}  // namespace cubert

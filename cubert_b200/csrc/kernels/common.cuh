@@ -21,6 +21,40 @@ inline int check_launch() {
     return CUBK_OK;
 }
 
+// Blocks to launch for a persistent (grid-stride) kernel: every SM filled to the occupancy the
+// kernel really gets, so that all blocks are resident at once and none forms a ragged tail.
+// `cache` is a zero-initialised per-call-site table indexed by device; an entry is reused only
+// for the same dynamic shared-memory size (racing writers store equivalent values).
+constexpr int kMaxDevices = 64;
+
+struct OccupancyCache {
+    int blocks[kMaxDevices];
+    size_t smem[kMaxDevices];
+};
+
+template <typename Kernel>
+inline int resident_blocks(Kernel kernel, int block_threads, size_t dynamic_smem, OccupancyCache *cache) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
+        (void) cudaGetLastError();
+        return 148;
+    }
+    if (cache->blocks[device] > 0 && cache->smem[device] == dynamic_smem) {
+        return cache->blocks[device];
+    }
+    int sms = 0, per_sm = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, block_threads, dynamic_smem) !=
+            cudaSuccess ||
+        sms <= 0 || per_sm <= 0) {
+        (void) cudaGetLastError();
+        return 148;
+    }
+    cache->smem[device] = dynamic_smem;
+    cache->blocks[device] = sms * per_sm;
+    return sms * per_sm;
+}
+
 inline bool aligned16(const void *p) {
     return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
 }
@@ -67,6 +101,82 @@ struct Vec<__half> {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
+// ---------------------------------------------------------------- packed float32 pairs
+// Blackwell executes add/mul/fma on two float32 values with one instruction (.f32x2); the
+// kernels below are short of issue slots rather than of FP32 lanes, so halving the
+// instruction count of the arithmetic is what buys bandwidth.
+__device__ __forceinline__ uint64_t pack_f2(float2 a) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a.x), "f"(a.y));
+    return r;
+}
+
+__device__ __forceinline__ float2 unpack_f2(uint64_t r) {
+    float2 a;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a.x), "=f"(a.y) : "l"(r));
+    return a;
+}
+
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(pack_f2(a)), "l"(pack_f2(b)), "l"(pack_f2(c)));
+    return unpack_f2(d);
+}
+
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack_f2(a)), "l"(pack_f2(b)));
+    return unpack_f2(d);
+}
+
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack_f2(a)), "l"(pack_f2(b)));
+    return unpack_f2(d);
+}
+
+__device__ __forceinline__ float2 splat2(float a) {
+    return make_float2(a, a);
+}
+
+// A 16-byte vector as EPV/2 float pairs.
+template <typename T>
+struct Vec2;
+
+template <>
+struct Vec2<float> {
+    static constexpr int PAIRS = 2;
+    static __device__ __forceinline__ void unpack(const uint4 &raw, float2 (&v)[2]) {
+        v[0] = make_float2(__uint_as_float(raw.x), __uint_as_float(raw.y));
+        v[1] = make_float2(__uint_as_float(raw.z), __uint_as_float(raw.w));
+    }
+    static __device__ __forceinline__ uint4 pack(const float2 (&v)[2]) {
+        return make_uint4(__float_as_uint(v[0].x), __float_as_uint(v[0].y), __float_as_uint(v[1].x),
+                          __float_as_uint(v[1].y));
+    }
+};
+
+template <>
+struct Vec2<__half> {
+    static constexpr int PAIRS = 4;
+    static __device__ __forceinline__ void unpack(const uint4 &raw, float2 (&v)[4]) {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[i] = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+        }
+    }
+    static __device__ __forceinline__ uint4 pack(const float2 (&v)[4]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2 h = __float22half2_rn(v[i]);
             w[i] = *reinterpret_cast<uint32_t *>(&h);
         }
         return make_uint4(w[0], w[1], w[2], w[3]);

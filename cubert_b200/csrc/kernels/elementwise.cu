@@ -9,37 +9,56 @@
 namespace cubk {
 
 // ------------------------------------------------------------------ activations
-// Exact form used by the reference: x * 0.5 * (1 + erf(x * sqrt(0.5)))
-// (src/cuBERT/op/GELU.cpp:12-14, op/GELU.cu:16-18).
-struct GeluErf {
-    __device__ __forceinline__ float operator()(float x) const {
-        return x * 0.5f * (1.0f + erff(x * 0.70710678118654752440f));
+// Every activation maps a pair of float32 values, so that the arithmetic can be issued as
+// packed .f32x2 instructions.
+//
+// GELU = x * Phi(x), the reference's x * 0.5 * (1 + erf(x / sqrt(2))) (src/cuBERT/op/GELU.cpp:12-14,
+// op/GELU.cu:16-18), evaluated as  max(x, 0) - |x| * Q(|x|)  with the Gaussian tail
+// Q(z) = 0.5 * erfc(z / sqrt(2)) = 2^p(z). p is a minimax polynomial fit of log2 Q on [0, 5.6],
+// written in w = -z; beyond 5.6 the tail term is below 1e-7 * |x|. There is no cancellation
+// for negative x (the reference's 1 + erf loses all digits there) and no branch. Per element:
+// one MUFU.EX2, two FMNMX and (DEG + 2) / 2 packed FP32 operations.
+//   DEG = 6  : |error| <= 3.2e-5 relative, 15x below half an ulp of binary16 -- binary16 storage
+//   DEG = 10 : |error| <= 2.5e-7 relative for x >= 0, 6e-7 of max(|y|, 0.02 |x|) for x < 0 -- float32
+template <int DEG>
+struct GeluCoef;
+
+template <>
+struct GeluCoef<6> {
+    static __device__ __forceinline__ float c(int k) {
+        constexpr float t[7] = {-1.000034451e+00f, 1.150568843e+00f, -4.604086876e-01f, 5.188094452e-02f,
+                                7.448623423e-03f,  6.533698761e-04f, 2.562585178e-05f};
+        return t[k];
     }
 };
 
-// GELU for binary16 storage: x * Phi(x) written as max(x, 0) - |x| * Q(|x|) with the
-// Gaussian tail Q(z) = 0.5 * erfc(z / sqrt(2)) = 2^p(z). p is a degree-6 minimax fit of
-// log2 Q on [0, 5.6] (max |error| 4.3e-5, i.e. 3e-5 relative in Q, 16x below half an ulp
-// of binary16); beyond 5.6 the tail term is below 1e-7 * |x|. One MUFU.EX2 and 9 FP32
-// operations per element, no branches, no cancellation for negative x.
+template <>
+struct GeluCoef<10> {
+    static __device__ __forceinline__ float c(int k) {
+        constexpr float t[11] = {-9.999997616e-01f, 1.151114583e+00f,  -4.591476619e-01f, 5.263686553e-02f,
+                                 7.207410876e-03f,  1.954334439e-04f,  -1.920824725e-04f, -5.257620796e-05f,
+                                 -7.090403869e-06f, -5.148263540e-07f, -1.600383115e-08f};
+        return t[k];
+    }
+};
+
+template <int DEG>
 struct GeluTailFit {
-    __device__ __forceinline__ float operator()(float x) const {
-        const float z = fminf(fabsf(x), 5.6f);
-        float p = 2.5625851835872642e-05f;
-        p = fmaf(p, z, -0.0006533698916556955f);
-        p = fmaf(p, z, 0.00744862337644326f);
-        p = fmaf(p, z, -0.05188094273211438f);
-        p = fmaf(p, z, -0.46040868733330087f);
-        p = fmaf(p, z, -1.150568806242031f);
-        p = fmaf(p, z, -1.0000344064834001f);
-        const float q = fast_exp2(p);
-        return fmaf(-z, q, fmaxf(x, 0.f));
+    __device__ __forceinline__ float2 operator()(float2 x) const {
+        const float2 w = make_float2(fmaxf(-fabsf(x.x), -5.6f), fmaxf(-fabsf(x.y), -5.6f));
+        float2 p = splat2(GeluCoef<DEG>::c(DEG));
+#pragma unroll
+        for (int k = DEG - 1; k >= 0; --k) {
+            p = fma2(p, w, splat2(GeluCoef<DEG>::c(k)));
+        }
+        const float2 q = make_float2(fast_exp2(p.x), fast_exp2(p.y));
+        return fma2(w, q, make_float2(fmaxf(x.x, 0.f), fmaxf(x.y, 0.f)));
     }
 };
 
 struct Tanh {
-    __device__ __forceinline__ float operator()(float x) const {
-        return tanhf(x);
+    __device__ __forceinline__ float2 operator()(float2 x) const {
+        return make_float2(tanhf(x.x), tanhf(x.y));
     }
 };
 
@@ -48,18 +67,19 @@ template <typename T, int BX, int BY, int U, typename Act>
 __global__ void __launch_bounds__(BX *BY)
 bias_act_kernel(const T *x, const T *bias, T *out, int64_t rows, int channels, int nvec) {
     constexpr int EPV = Vec<T>::EPV;
+    constexpr int PAIRS = Vec2<T>::PAIRS;
     const int cv = blockIdx.x * BX + threadIdx.x;
     if (cv >= nvec) {
         return;
     }
     const Act act;
-    float b[EPV];
+    float2 b[PAIRS];
     if (bias != nullptr) {
-        Vec<T>::unpack(ld_param(bias + (size_t) cv * EPV), b);
+        Vec2<T>::unpack(ld_param(bias + (size_t) cv * EPV), b);
     } else {
 #pragma unroll
-        for (int e = 0; e < EPV; ++e) {
-            b[e] = 0.f;
+        for (int e = 0; e < PAIRS; ++e) {
+            b[e] = make_float2(0.f, 0.f);
         }
     }
     const int64_t col = (int64_t) cv * EPV;
@@ -77,13 +97,13 @@ bias_act_kernel(const T *x, const T *bias, T *out, int64_t rows, int channels, i
         for (int u = 0; u < U; ++u) {
             const int64_t r = r0 + (int64_t) u * BY;
             if (r < rows) {
-                float v[EPV];
-                Vec<T>::unpack(raw[u], v);
+                float2 v[PAIRS];
+                Vec2<T>::unpack(raw[u], v);
 #pragma unroll
-                for (int e = 0; e < EPV; ++e) {
-                    v[e] = act(v[e] + b[e]);
+                for (int e = 0; e < PAIRS; ++e) {
+                    v[e] = act(add2(v[e], b[e]));
                 }
-                st_vec(out + r * channels + col, Vec<T>::pack(v));
+                st_vec(out + r * channels + col, Vec2<T>::pack(v));
             }
         }
     }
@@ -100,11 +120,11 @@ bias_act_generic_kernel(const T *x, const T *bias, T *out, int64_t total, int ch
         if (bias != nullptr) {
             v += to_float<T>(bias[i % channels]);
         }
-        out[i] = from_float<T>(act(v));
+        out[i] = from_float<T>(act(make_float2(v, 0.f)).x);
     }
 }
 
-constexpr int kResidentBlocks = 148 * 8;  // enough 256-thread blocks to fill every SM of a B200
+constexpr int kResidentBlocks = 148 * 8;  // grid cap of the small helper kernels
 
 template <typename T, typename Act>
 int bias_act(const T *x, const T *bias, int64_t rows, int channels, T *out, cudaStream_t stream) {
@@ -120,15 +140,19 @@ int bias_act(const T *x, const T *bias, int64_t rows, int channels, T *out, cuda
                         (bias == nullptr || aligned16(bias));
     if (vec_ok) {
         const int nvec = channels / EPV;
+        // grid.x covers the columns; grid.y is as many row slices as stay resident together.
 #define LAUNCH(BX, BY)                                                                              \
     {                                                                                               \
+        static OccupancyCache cache;                                                                \
+        auto kernel = bias_act_kernel<T, BX, BY, U, Act>;                                           \
         const int gx = (nvec + BX - 1) / BX;                                                        \
         int64_t gy = (rows + BY * U - 1) / (BY * U);                                                \
-        const int64_t cap = (kResidentBlocks + gx - 1) / gx;                                        \
+        int64_t cap = resident_blocks(kernel, BX * BY, 0, &cache) / gx;                             \
+        if (cap < 1) cap = 1;                                                                       \
         if (gy > cap) gy = cap;                                                                     \
         if (gy > 65535) gy = 65535;                                                                 \
-        bias_act_kernel<T, BX, BY, U, Act><<<dim3((unsigned) gx, (unsigned) gy), dim3(BX, BY), 0,   \
-                                             stream>>>(x, bias, out, rows, channels, nvec);         \
+        kernel<<<dim3((unsigned) gx, (unsigned) gy), dim3(BX, BY), 0, stream>>>(x, bias, out, rows, \
+                                                                                channels, nvec);    \
     }
         if (nvec % 256 == 0) {
             LAUNCH(256, 1);
@@ -204,11 +228,11 @@ half_to_float_kernel(const __half *in, float *out, int64_t n, int vectorised) {
 extern "C" {
 
 int cubk_bias_gelu_f32(const float *x, const float *bias, int64_t rows, int channels, float *out, void *stream) {
-    return cubk::bias_act<float, cubk::GeluErf>(x, bias, rows, channels, out, (cudaStream_t) stream);
+    return cubk::bias_act<float, cubk::GeluTailFit<10>>(x, bias, rows, channels, out, (cudaStream_t) stream);
 }
 
 int cubk_bias_gelu_f16(const void *x, const void *bias, int64_t rows, int channels, void *out, void *stream) {
-    return cubk::bias_act<__half, cubk::GeluTailFit>((const __half *) x, (const __half *) bias, rows, channels,
+    return cubk::bias_act<__half, cubk::GeluTailFit<6>>((const __half *) x, (const __half *) bias, rows, channels,
                                                      (__half *) out, (cudaStream_t) stream);
 }
 

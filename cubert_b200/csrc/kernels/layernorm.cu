@@ -1,9 +1,15 @@
 // K1 (embedding lookup + add + LayerNorm) and K2 (bias + residual + LayerNorm).
 //
-// Both keep one row in registers: TPR threads share a row, each holding VPT 16-byte
-// vectors, so the row is read from HBM exactly once and written once. Mean and the
-// centred second moment are reduced with warp shuffles (plus one shared-memory hop when
-// a row spans a whole block). All arithmetic is float32.
+// Layout of the work
+//   * A row lives in registers: TPR threads share a row, each holding VPT 16-byte vectors, so a
+//     row is read from HBM exactly once and written once.
+//   * For rows that fit one warp, blocks are persistent: the grid is sized to what is resident
+//     on the GPU and every row group walks over rows with a grid stride, fetching the next row
+//     while it reduces the current one. gamma, beta and bias are converted to float32 once per
+//     block and kept in shared memory, laid out so that each 128-bit shared load is
+//     conflict-free ([quarter][vector] order). Wider rows take one 128-thread block per row.
+//   * Mean and the centred second moment are reduced with warp shuffles (plus one shared-memory
+//     hop when a row spans a whole block). Arithmetic is float32, issued as packed .f32x2.
 //
 // HBM traffic per row: K2 reads x and residual and writes out (3 * C * e bytes);
 // K1 reads one gathered word row and writes out (2 * H * e bytes) plus 5 index bytes.
@@ -14,113 +20,197 @@ namespace cubk {
 constexpr float kLayerNormEps = 1e-12f;  // src/cuBERT/op/LayerNorm.cpp:35, op/LayerNorm.cu:70
 
 template <int TPR, int BLOCK>
-__device__ __forceinline__ float row_sum(float v, float *smem) {
+__device__ __forceinline__ float row_sum(float v, float *red) {
     if (TPR <= 32) {
         return group_sum<TPR>(v);
     } else {
         static_assert(TPR <= 32 || TPR == BLOCK, "a row spans a sub-warp group or the whole block");
-        return block_sum<BLOCK / 32>(v, smem);
+        return block_sum<BLOCK / 32>(v, red);
     }
 }
 
-// Normalise the register-resident row `v` and store it.
-template <typename T, int TPR, int VPT, int BLOCK>
-__device__ __forceinline__ void normalise_store(float (&v)[VPT][Vec<T>::EPV], int lane, int nvec, int channels,
-                                                bool active, const T *gamma, const T *beta, T *out_row,
-                                                float *smem) {
+// float32 copy of a [channels] parameter in shared memory, as float4 [EPV/4][nvec]: the q-th
+// float4 of vector idx sits at [q * nvec + idx].
+template <typename T>
+__device__ __forceinline__ void stage_param(const T *src, float4 *dst, int nvec, int tid, int nthreads) {
     constexpr int EPV = Vec<T>::EPV;
-    float s = 0.f;
-#pragma unroll
-    for (int k = 0; k < VPT; ++k) {
-        if (lane + k * TPR < nvec) {
+    for (int idx = tid; idx < nvec; idx += nthreads) {
+        float v[EPV];
+        if (src != nullptr) {
+            Vec<T>::unpack(ld_param(src + (size_t) idx * EPV), v);
+        } else {
 #pragma unroll
             for (int e = 0; e < EPV; ++e) {
-                s += v[k][e];
+                v[e] = 0.f;
             }
         }
+#pragma unroll
+        for (int q = 0; q < EPV / 4; ++q) {
+            dst[q * nvec + idx] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        }
     }
-    const float mean = row_sum<TPR, BLOCK>(s, smem) / (float) channels;
+}
 
-    float q = 0.f;
+template <typename T>
+__device__ __forceinline__ void load_param(const float4 *src, int nvec, int idx, float2 (&p)[Vec2<T>::PAIRS]) {
+#pragma unroll
+    for (int q = 0; q < Vec<T>::EPV / 4; ++q) {
+        const float4 f = src[q * nvec + idx];
+        p[2 * q] = make_float2(f.x, f.y);
+        p[2 * q + 1] = make_float2(f.z, f.w);
+    }
+}
+
+// A [channels] parameter as seen by the row kernels: the float32 copy in shared memory (narrow
+// rows, persistent blocks) or the original in global memory through the read-only cache (wide
+// rows, where three float32 copies would cost too much occupancy).
+template <typename T, bool IN_SMEM>
+struct Param {
+    const float4 *smem;
+    const T *global;
+    __device__ __forceinline__ void load(int nvec, int idx, float2 (&p)[Vec2<T>::PAIRS]) const {
+        if (IN_SMEM) {
+            load_param<T>(smem, nvec, idx, p);
+        } else {
+            Vec2<T>::unpack(ld_param(global + (size_t) idx * Vec<T>::EPV), p);
+        }
+    }
+};
+
+// Normalise the register-resident row `v` and store it.
+template <typename T, int TPR, int VPT, int BLOCK, bool IN_SMEM>
+__device__ __forceinline__ void normalise_store(float2 (&v)[VPT][Vec2<T>::PAIRS], int lane, int nvec, int channels,
+                                                bool active, const Param<T, IN_SMEM> &p_gamma,
+                                                const Param<T, IN_SMEM> &p_beta, T *out_row, float *red) {
+    constexpr int EPV = Vec<T>::EPV;
+    constexpr int PAIRS = Vec2<T>::PAIRS;
+    float2 s2 = make_float2(0.f, 0.f);
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
         if (lane + k * TPR < nvec) {
 #pragma unroll
-            for (int e = 0; e < EPV; ++e) {
-                const float d = v[k][e] - mean;
-                q += d * d;
+            for (int e = 0; e < PAIRS; ++e) {
+                s2 = add2(s2, v[k][e]);
             }
         }
     }
-    const float var = row_sum<TPR, BLOCK>(q, smem) / (float) channels;
-    const float rstd = 1.f / sqrtf(var + kLayerNormEps);
+    const float mean = row_sum<TPR, BLOCK>(s2.x + s2.y, red) / (float) channels;
+    const float2 neg_mean = splat2(-mean);
+
+    float2 q2 = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        if (lane + k * TPR < nvec) {
+#pragma unroll
+            for (int e = 0; e < PAIRS; ++e) {
+                v[k][e] = add2(v[k][e], neg_mean);  // keep the centred value
+                q2 = fma2(v[k][e], v[k][e], q2);
+            }
+        }
+    }
+    const float var = row_sum<TPR, BLOCK>(q2.x + q2.y, red) / (float) channels;
+    const float2 rstd = splat2(1.f / sqrtf(var + kLayerNormEps));
 
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
         const int idx = lane + k * TPR;
         if (active && idx < nvec) {
-            float g[EPV], b[EPV], o[EPV];
-            Vec<T>::unpack(ld_param(gamma + (size_t) idx * EPV), g);
-            Vec<T>::unpack(ld_param(beta + (size_t) idx * EPV), b);
+            float2 g[PAIRS], b[PAIRS], o[PAIRS];
+            p_gamma.load(nvec, idx, g);
+            p_beta.load(nvec, idx, b);
 #pragma unroll
-            for (int e = 0; e < EPV; ++e) {
-                o[e] = b[e] + g[e] * rstd * (v[k][e] - mean);
+            for (int e = 0; e < PAIRS; ++e) {
+                o[e] = fma2(mul2(g[e], rstd), v[k][e], b[e]);  // beta + (gamma * rstd) * (t - mean)
             }
-            st_vec(out_row + (size_t) idx * EPV, Vec<T>::pack(o));
+            st_vec(out_row + (size_t) idx * EPV, Vec2<T>::pack(o));
         }
     }
 }
 
 // ------------------------------------------------------------------ K2
-template <typename T, int TPR, int VPT, int BLOCK>
+// PERSISTENT: blocks loop over rows with a grid stride, parameters staged in shared memory, and
+// the next row's loads are issued before the current row is reduced (twice the bytes in flight
+// per warp, which binary16 rows need to cover the HBM latency). Otherwise one row group per
+// block step and parameters straight from global memory.
+template <typename T, int TPR, int VPT, int BLOCK, bool PERSISTENT>
 __global__ void __launch_bounds__(BLOCK)
 bias_residual_ln_kernel(const T *x, const T *bias, const T *residual, const T *gamma, const T *beta,
                         T *out, int64_t rows, int channels, int nvec) {
     constexpr int EPV = Vec<T>::EPV;
-    constexpr int RPB = BLOCK / TPR;
-    __shared__ float smem[BLOCK / 32];
+    constexpr int PAIRS = Vec2<T>::PAIRS;
+    constexpr int GROUPS = BLOCK / TPR;
+    extern __shared__ float4 s_params[];
+    __shared__ float red[BLOCK / 32];
+    Param<T, PERSISTENT> p_gamma{s_params, gamma};
+    Param<T, PERSISTENT> p_beta{s_params + (EPV / 4) * nvec, beta};
+    Param<T, PERSISTENT> p_bias{s_params + 2 * (EPV / 4) * nvec, bias};
+    if (PERSISTENT) {
+        stage_param<T>(gamma, s_params, nvec, threadIdx.x, BLOCK);
+        stage_param<T>(beta, s_params + (EPV / 4) * nvec, nvec, threadIdx.x, BLOCK);
+        if (bias != nullptr) {
+            stage_param<T>(bias, s_params + 2 * (EPV / 4) * nvec, nvec, threadIdx.x, BLOCK);
+        }
+        __syncthreads();
+    }
 
     const int lane = threadIdx.x % TPR;
-    const int64_t row = (int64_t) blockIdx.x * RPB + threadIdx.x / TPR;
-    const bool active = row < rows;
-    const int64_t base = active ? row * (int64_t) channels : 0;
+    const int group = threadIdx.x / TPR;
+    const int64_t stride = (int64_t) gridDim.x * GROUPS;
 
-    // Issue every load of the row before the first use.
     uint4 rx[VPT], rr[VPT];
+    auto issue_loads = [&](int64_t row) {
+        const bool ok_row = row < rows;
+        const int64_t base = ok_row ? row * (int64_t) channels : 0;
 #pragma unroll
-    for (int k = 0; k < VPT; ++k) {
-        const int idx = lane + k * TPR;
-        const bool ok = active && idx < nvec;
-        rx[k] = ok ? ld_stream(x + base + (int64_t) idx * EPV) : make_uint4(0, 0, 0, 0);
-        if (residual != nullptr) {
-            rr[k] = ok ? ld_stream(residual + base + (int64_t) idx * EPV) : make_uint4(0, 0, 0, 0);
-        }
-    }
-
-    float v[VPT][EPV];
-#pragma unroll
-    for (int k = 0; k < VPT; ++k) {
-        const int idx = lane + k * TPR;
-        Vec<T>::unpack(rx[k], v[k]);
-        if (bias != nullptr && idx < nvec) {
-            float b[EPV];
-            Vec<T>::unpack(ld_param(bias + (size_t) idx * EPV), b);
-#pragma unroll
-            for (int e = 0; e < EPV; ++e) {
-                v[k][e] += b[e];
+        for (int k = 0; k < VPT; ++k) {
+            const int idx = lane + k * TPR;
+            const bool ok = ok_row && idx < nvec;
+            rx[k] = ok ? ld_stream(x + base + (int64_t) idx * EPV) : make_uint4(0, 0, 0, 0);
+            if (residual != nullptr) {
+                rr[k] = ok ? ld_stream(residual + base + (int64_t) idx * EPV) : make_uint4(0, 0, 0, 0);
             }
         }
-        if (residual != nullptr) {
-            float r[EPV];
-            Vec<T>::unpack(rr[k], r);
+    };
+
+    int64_t first = (int64_t) blockIdx.x * GROUPS;
+    if (first < rows) {
+        issue_loads(first + group);
+    }
+    for (; first < rows; first += stride) {
+        const int64_t row = first + group;
+        const bool active = row < rows;
+        const int64_t base = active ? row * (int64_t) channels : 0;
+
+        float2 v[VPT][PAIRS];
 #pragma unroll
-            for (int e = 0; e < EPV; ++e) {
-                v[k][e] += r[e];
+        for (int k = 0; k < VPT; ++k) {
+            const int idx = lane + k * TPR;
+            Vec2<T>::unpack(rx[k], v[k]);
+            if (bias != nullptr && idx < nvec) {
+                float2 b[PAIRS];
+                p_bias.load(nvec, idx, b);
+#pragma unroll
+                for (int e = 0; e < PAIRS; ++e) {
+                    v[k][e] = add2(v[k][e], b[e]);
+                }
+            }
+            if (residual != nullptr) {
+                float2 r[PAIRS];
+                Vec2<T>::unpack(rr[k], r);
+#pragma unroll
+                for (int e = 0; e < PAIRS; ++e) {
+                    v[k][e] = add2(v[k][e], r[e]);
+                }
             }
         }
-    }
+        // The raw registers are free again: fetch the next row while this one is reduced.
+        if (first + stride < rows) {
+            issue_loads(row + stride);
+        }
 
-    normalise_store<T, TPR, VPT, BLOCK>(v, lane, nvec, channels, active, gamma, beta, out + base, smem);
+        normalise_store<T, TPR, VPT, BLOCK, PERSISTENT>(v, lane, nvec, channels, active, p_gamma, p_beta,
+                                                        out + base, red);
+    }
 }
 
 // ------------------------------------------------------------------ K1
@@ -130,62 +220,73 @@ embed_ln_kernel(const int32_t *ids, const int8_t *segment_ids, const T *word, co
                 const T *gamma, const T *beta, T *out, uint32_t tokens, FastDiv seq_div, int hidden, int nvec,
                 int vocab, int type_vocab, uint32_t *status) {
     constexpr int EPV = Vec<T>::EPV;
-    constexpr int RPB = BLOCK / TPR;
-    __shared__ float smem[BLOCK / 32];
+    constexpr int PAIRS = Vec2<T>::PAIRS;
+    constexpr int GROUPS = BLOCK / TPR;
+    extern __shared__ float4 s_params[];
+    __shared__ float red[BLOCK / 32];
+    Param<T, true> p_gamma{s_params, gamma};
+    Param<T, true> p_beta{s_params + (EPV / 4) * nvec, beta};
+    stage_param<T>(gamma, s_params, nvec, threadIdx.x, BLOCK);
+    stage_param<T>(beta, s_params + (EPV / 4) * nvec, nvec, threadIdx.x, BLOCK);
+    __syncthreads();
 
     const int lane = threadIdx.x % TPR;
-    const uint32_t token = blockIdx.x * RPB + threadIdx.x / TPR;
-    const bool active = token < tokens;
+    const int group = threadIdx.x / TPR;
+    const uint32_t stride = gridDim.x * GROUPS;
+    for (uint32_t first = blockIdx.x * GROUPS; first < tokens; first += stride) {
+        const uint32_t token = first + group;
+        const bool active = token < tokens;
 
-    int id = 0, seg = 0;
-    uint32_t s = 0;
-    if (active) {
-        id = ids[token];
-        seg = segment_ids[token];
-        s = token - fast_div(token, seq_div) * seq_div.div;
-        uint32_t bad = 0;
-        if (id < 0 || id >= vocab) {
-            bad |= CUBK_STATUS_BAD_TOKEN_ID;
-            id = min(max(id, 0), vocab - 1);
+        int id = 0, seg = 0;
+        uint32_t s = 0;
+        if (active) {
+            id = ids[token];
+            seg = segment_ids[token];
+            s = token - fast_div(token, seq_div) * seq_div.div;
+            uint32_t bad = 0;
+            if (id < 0 || id >= vocab) {
+                bad |= CUBK_STATUS_BAD_TOKEN_ID;
+                id = min(max(id, 0), vocab - 1);
+            }
+            if (seg < 0 || seg >= type_vocab) {
+                bad |= CUBK_STATUS_BAD_SEGMENT_ID;
+                seg = min(max(seg, 0), type_vocab - 1);
+            }
+            if (bad != 0 && status != nullptr && lane == 0) {
+                atomicOr(status, bad);
+            }
         }
-        if (seg < 0 || seg >= type_vocab) {
-            bad |= CUBK_STATUS_BAD_SEGMENT_ID;
-            seg = min(max(seg, 0), type_vocab - 1);
-        }
-        if (bad != 0 && status != nullptr && lane == 0) {
-            atomicOr(status, bad);
-        }
-    }
 
-    const T *wrow = word + (size_t) id * hidden;
-    const T *prow = pos + (size_t) s * hidden;
-    const T *trow = type + (size_t) seg * hidden;
+        const T *wrow = word + (size_t) id * hidden;
+        const T *prow = pos + (size_t) s * hidden;
+        const T *trow = type + (size_t) seg * hidden;
 
-    uint4 rw[VPT], rp[VPT], rt[VPT];
+        uint4 rw[VPT], rp[VPT], rt[VPT];
 #pragma unroll
-    for (int k = 0; k < VPT; ++k) {
-        const int idx = lane + k * TPR;
-        const bool ok = active && idx < nvec;
-        rw[k] = ok ? ld_param(wrow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
-        rp[k] = ok ? ld_param(prow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
-        rt[k] = ok ? ld_param(trow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
-    }
-
-    float v[VPT][EPV];
-#pragma unroll
-    for (int k = 0; k < VPT; ++k) {
-        float p[EPV], t[EPV];
-        Vec<T>::unpack(rw[k], v[k]);
-        Vec<T>::unpack(rp[k], p);
-        Vec<T>::unpack(rt[k], t);
-#pragma unroll
-        for (int e = 0; e < EPV; ++e) {
-            v[k][e] = (v[k][e] + p[e]) + t[e];  // (word + pos) + type, the reference's order
+        for (int k = 0; k < VPT; ++k) {
+            const int idx = lane + k * TPR;
+            const bool ok = active && idx < nvec;
+            rw[k] = ok ? ld_param(wrow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
+            rp[k] = ok ? ld_param(prow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
+            rt[k] = ok ? ld_param(trow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
         }
-    }
 
-    normalise_store<T, TPR, VPT, BLOCK>(v, lane, nvec, hidden, active, gamma, beta,
-                                        out + (size_t) token * (active ? hidden : 0), smem);
+        float2 v[VPT][PAIRS];
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            float2 p[PAIRS], t[PAIRS];
+            Vec2<T>::unpack(rw[k], v[k]);
+            Vec2<T>::unpack(rp[k], p);
+            Vec2<T>::unpack(rt[k], t);
+#pragma unroll
+            for (int e = 0; e < PAIRS; ++e) {
+                v[k][e] = add2(add2(v[k][e], p[e]), t[e]);  // (word + pos) + type, the reference's order
+            }
+        }
+
+        normalise_store<T, TPR, VPT, BLOCK, true>(v, lane, nvec, hidden, active, p_gamma, p_beta,
+                                                  out + (size_t) token * (active ? hidden : 0), red);
+    }
 }
 
 // ------------------------------------------------------------------ generic rows (any width, any alignment)
@@ -262,21 +363,22 @@ generic_ln_kernel(Loader load, const T *gamma, const T *beta, T *out, int channe
 // ------------------------------------------------------------------ dispatch
 // Picks (threads per row, vectors per thread) for a row of `nvec` 16-byte vectors.
 // Rows up to 256 vectors stay inside one warp; up to 1024 vectors use one 128-thread block.
-#define CUBK_LN_DISPATCH(NVEC, LAUNCH)                      \
-    do {                                                    \
-        if ((NVEC) <= 32) { LAUNCH(32, 1, 128); }           \
-        else if ((NVEC) <= 64) { LAUNCH(32, 2, 128); }      \
-        else if ((NVEC) <= 96) { LAUNCH(32, 3, 128); }      \
-        else if ((NVEC) <= 128) { LAUNCH(32, 4, 128); }     \
-        else if ((NVEC) <= 192) { LAUNCH(32, 6, 128); }     \
-        else if ((NVEC) <= 256) { LAUNCH(32, 8, 128); }     \
-        else if ((NVEC) <= 384) { LAUNCH(128, 3, 128); }    \
-        else if ((NVEC) <= 512) { LAUNCH(128, 4, 128); }    \
-        else if ((NVEC) <= 768) { LAUNCH(128, 6, 128); }    \
-        else { LAUNCH(128, 8, 128); }                       \
+#define CUBK_LN_DISPATCH(NVEC, LAUNCH)                             \
+    do {                                                           \
+        if ((NVEC) <= 32) { LAUNCH(32, 1, 256, true); }            \
+        else if ((NVEC) <= 64) { LAUNCH(32, 2, 256, true); }       \
+        else if ((NVEC) <= 96) { LAUNCH(32, 3, 256, true); }       \
+        else if ((NVEC) <= 128) { LAUNCH(32, 4, 256, true); }      \
+        else if ((NVEC) <= 192) { LAUNCH(32, 6, 256, true); }      \
+        else if ((NVEC) <= 256) { LAUNCH(32, 8, 256, true); }      \
+        else if ((NVEC) <= 384) { LAUNCH(128, 3, 128, false); }    \
+        else if ((NVEC) <= 512) { LAUNCH(128, 4, 128, false); }    \
+        else if ((NVEC) <= 768) { LAUNCH(128, 6, 128, false); }    \
+        else { LAUNCH(128, 8, 128, false); }                       \
     } while (0)
 
 constexpr int kMaxRowVectors = 1024;
+constexpr size_t kMaxParamSmem = 47 * 1024;  // dynamic + static stay below the 48 KB that needs no opt-in
 
 template <typename T>
 int bias_residual_ln(const T *x, const T *bias, const T *residual, const T *gamma, const T *beta,
@@ -291,16 +393,22 @@ int bias_residual_ln(const T *x, const T *bias, const T *residual, const T *gamm
         return CUBK_ERR_UNSUPPORTED;
     }
     constexpr int EPV = Vec<T>::EPV;
-    const bool vec_ok = channels % EPV == 0 && channels / EPV <= kMaxRowVectors && aligned16(x) &&
-                        aligned16(out) && aligned16(gamma) && aligned16(beta) &&
+    const bool vec_ok = channels % EPV == 0 && channels / EPV <= kMaxRowVectors && aligned16(x) && aligned16(out) && aligned16(gamma) && aligned16(beta) &&
                         (bias == nullptr || aligned16(bias)) && (residual == nullptr || aligned16(residual));
     if (vec_ok) {
         const int nvec = channels / EPV;
-#define LAUNCH(TPR, VPT, BLOCK)                                                                       \
+#define LAUNCH(TPR, VPT, BLOCK, PERSISTENT)                                                           \
     {                                                                                                 \
-        const int64_t grid = (rows + (BLOCK / TPR) - 1) / (BLOCK / TPR);                              \
-        bias_residual_ln_kernel<T, TPR, VPT, BLOCK><<<(unsigned) grid, BLOCK, 0, stream>>>(           \
-            x, bias, residual, gamma, beta, out, rows, channels, nvec);                               \
+        static OccupancyCache cache;                                                                  \
+        auto kernel = bias_residual_ln_kernel<T, TPR, VPT, BLOCK, PERSISTENT>;                        \
+        const size_t smem = PERSISTENT ? sizeof(float) * 3 * (size_t) channels : 0;                   \
+        int64_t grid = (rows + (BLOCK / TPR) - 1) / (BLOCK / TPR);                                    \
+        if (PERSISTENT) {                                                                             \
+            const int resident = resident_blocks(kernel, BLOCK, smem, &cache);                        \
+            if (grid > resident) grid = resident;                                                     \
+        }                                                                                             \
+        kernel<<<(unsigned) grid, BLOCK, smem, stream>>>(x, bias, residual, gamma, beta, out, rows,   \
+                                                          channels, nvec);                            \
     }
         CUBK_LN_DISPATCH(nvec, LAUNCH);
 #undef LAUNCH
@@ -329,18 +437,23 @@ int embed_ln(const int32_t *ids, const int8_t *segment_ids, const T *word, const
         return CUBK_ERR_UNSUPPORTED;
     }
     constexpr int EPV = Vec<T>::EPV;
-    const bool vec_ok = hidden % EPV == 0 && hidden / EPV <= kMaxRowVectors && aligned16(word) &&
-                        aligned16(pos) && aligned16(type) && aligned16(gamma) && aligned16(beta) &&
-                        aligned16(out);
+    const size_t smem = sizeof(float) * 2 * (size_t) hidden;
+    const bool vec_ok = hidden % EPV == 0 && hidden / EPV <= kMaxRowVectors && smem <= kMaxParamSmem &&
+                        aligned16(word) && aligned16(pos) && aligned16(type) && aligned16(gamma) &&
+                        aligned16(beta) && aligned16(out);
     if (vec_ok) {
         const int nvec = hidden / EPV;
         const FastDiv seq_div = make_fastdiv((uint32_t) seq);
-#define LAUNCH(TPR, VPT, BLOCK)                                                                       \
+#define LAUNCH(TPR, VPT, BLOCK, PERSISTENT)                                                           \
     {                                                                                                 \
-        const int64_t grid = (tokens + (BLOCK / TPR) - 1) / (BLOCK / TPR);                            \
-        embed_ln_kernel<T, TPR, VPT, BLOCK><<<(unsigned) grid, BLOCK, 0, stream>>>(                   \
-            ids, segment_ids, word, pos, type, gamma, beta, out, (uint32_t) tokens, seq_div, hidden,  \
-            nvec, vocab, type_vocab, status);                                                         \
+        static OccupancyCache cache;                                                                  \
+        auto kernel = embed_ln_kernel<T, TPR, VPT, BLOCK>;                                            \
+        int64_t grid = (tokens + (BLOCK / TPR) - 1) / (BLOCK / TPR);                                  \
+        const int resident = resident_blocks(kernel, BLOCK, smem, &cache);                            \
+        if (grid > resident) grid = resident;                                                         \
+        kernel<<<(unsigned) grid, BLOCK, smem, stream>>>(ids, segment_ids, word, pos, type, gamma,    \
+                                                          beta, out, (uint32_t) tokens, seq_div,      \
+                                                          hidden, nvec, vocab, type_vocab, status);   \
     }
         CUBK_LN_DISPATCH(nvec, LAUNCH);
 #undef LAUNCH

@@ -5,10 +5,11 @@
 // A row lives in the registers of LPR adjacent lanes (LPR = 1..32, a power of two), VPT
 // 16-byte vectors per lane, and every lane group works on ROWS rows at once so that
 // ROWS * VPT independent 128-bit loads are in flight per thread. Short rows (seq 32 in
-// binary16 is 64 bytes) therefore still produce 512-byte contiguous warp accesses. The
-// int8 [batch, seq] mask is read directly (EPV bytes per vector, from L1/L2); the
-// reference's score-sized broadcast mask tensor never exists. HBM traffic: one read and
-// one write of the score matrix.
+// binary16 is 64 bytes) therefore still produce 512-byte contiguous warp accesses. Blocks
+// are bound to one batch entry: a thread reads its columns of the int8 [batch, seq] mask
+// once, keeps them as additive float terms in registers and reuses them for every row it
+// handles; the reference's score-sized broadcast mask tensor never exists. Arithmetic is
+// float32 issued as packed .f32x2. HBM traffic: one read and one write of the score matrix.
 #include "common.cuh"
 
 namespace cubk {
@@ -38,95 +39,126 @@ __device__ __forceinline__ void load_mask_add<__half>(const int8_t *mask_row, in
     }
 }
 
+// Work is cut into items of ROWS_PER_BLOCK consecutive rows of one batch entry (all of whose
+// rows share one mask row). Every block takes a contiguous range of items, so it changes batch
+// entry rarely; when it does, each thread converts its columns of the mask into additive terms,
+// which then stay in registers for all the rows that follow.
 template <typename T, int LPR, int VPT, int ROWS, int BLOCK>
 __global__ void __launch_bounds__(BLOCK)
-masked_softmax_kernel(const T *scores, const int8_t *mask, T *out, uint32_t rows, FastDiv rows_per_batch,
-                      int seq, int nvec, float scale) {
+masked_softmax_kernel(const T *scores, const int8_t *mask, T *out, uint32_t rows_per_batch, int seq, int nvec,
+                      float scale, uint32_t total_items, FastDiv items_per_batch) {
     constexpr int EPV = Vec<T>::EPV;
-    constexpr int GPW = 32 / LPR;  // row groups per warp
+    constexpr int PAIRS = Vec2<T>::PAIRS;
+    constexpr int GPW = 32 / LPR;                          // row groups per warp
+    constexpr int ROWS_PER_BLOCK = (BLOCK / 32) * GPW * ROWS;  // rows of one item
     const int lane = threadIdx.x & 31;
     const int sub = lane / LPR;
     const int l = lane % LPR;
-    const uint32_t warp = blockIdx.x * (BLOCK / 32) + (threadIdx.x >> 5);
-    const uint64_t first = (uint64_t) warp * (GPW * ROWS);
-    if (first >= rows) {
-        return;  // whole warp leaves together
-    }
+    const int warp = threadIdx.x >> 5;
 
-    uint4 raw[ROWS][VPT];
-    bool live[ROWS];
+    // items split as evenly as possible: the first `extra` blocks take one more
+    const uint32_t share = total_items / gridDim.x;
+    const uint32_t extra = total_items - share * gridDim.x;
+    const uint32_t item_begin = blockIdx.x * share + min(blockIdx.x, extra);
+    const uint32_t item_end = item_begin + share + (blockIdx.x < extra ? 1u : 0u);
+
+    float2 madd[VPT][PAIRS];
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-        const uint64_t row = first + (uint64_t) r * GPW + sub;
-        live[r] = row < rows;
-        const T *src = scores + row * (uint64_t) seq;
+    for (int k = 0; k < VPT; ++k) {
 #pragma unroll
-        for (int k = 0; k < VPT; ++k) {
-            const int idx = l + k * LPR;
-            raw[r][k] = (live[r] && idx < nvec) ? ld_stream(src + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
+        for (int e = 0; e < PAIRS; ++e) {
+            madd[k][e] = make_float2(0.f, 0.f);
         }
     }
+    uint32_t cur_b = 0xffffffffu;
+    const float2 scale2 = splat2(scale);
+    const float2 log2e2 = splat2(kLog2e);
 
+    for (uint32_t item = item_begin; item < item_end; ++item) {
+        const uint32_t b = fast_div(item, items_per_batch);
+        if (b != cur_b) {
+            cur_b = b;
+            if (mask != nullptr) {
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-        const uint64_t row = first + (uint64_t) r * GPW + sub;
-        float v[VPT][EPV];
-        float mx = -3.0e38f;
-        const int8_t *mask_row = nullptr;
-        if (mask != nullptr && live[r]) {
-            mask_row = mask + (size_t) fast_div((uint32_t) row, rows_per_batch) * seq;
-        }
+                for (int k = 0; k < VPT; ++k) {
+                    const int idx = l + k * LPR;
+                    if (idx < nvec) {
+                        float add[EPV];
+                        load_mask_add<T>(mask + (size_t) b * seq, idx, add);
 #pragma unroll
-        for (int k = 0; k < VPT; ++k) {
-            const int idx = l + k * LPR;
-            Vec<T>::unpack(raw[r][k], v[k]);
-            if (idx < nvec) {
-                if (mask_row != nullptr) {
-                    float add[EPV];
-                    load_mask_add<T>(mask_row, idx, add);
-#pragma unroll
-                    for (int e = 0; e < EPV; ++e) {
-                        v[k][e] = fmaf(scale, v[k][e], add[e]);
+                        for (int e = 0; e < PAIRS; ++e) {
+                            madd[k][e] = make_float2(add[2 * e], add[2 * e + 1]);
+                        }
                     }
-                } else {
-#pragma unroll
-                    for (int e = 0; e < EPV; ++e) {
-                        v[k][e] = scale * v[k][e];
-                    }
-                }
-#pragma unroll
-                for (int e = 0; e < EPV; ++e) {
-                    mx = fmaxf(mx, v[k][e]);
                 }
             }
         }
-        mx = group_max<LPR>(mx);
-
-        float sum = 0.f;
-#pragma unroll
-        for (int k = 0; k < VPT; ++k) {
-            if (l + k * LPR < nvec) {
-#pragma unroll
-                for (int e = 0; e < EPV; ++e) {
-                    v[k][e] = fast_exp2((v[k][e] - mx) * kLog2e);
-                    sum += v[k][e];
-                }
-            }
+        const uint64_t batch_row0 = (uint64_t) b * rows_per_batch;
+        const uint32_t r0 = (item - b * items_per_batch.div) * ROWS_PER_BLOCK + warp * (GPW * ROWS);
+        if (r0 >= rows_per_batch) {
+            continue;  // the whole warp skips together
         }
-        sum = group_sum<LPR>(sum);
-        const float inv = 1.f / sum;
-
-        if (live[r]) {
-            T *dst = out + row * (uint64_t) seq;
+        uint4 raw[ROWS][VPT];
+        bool live[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const uint32_t rb = r0 + r * GPW + sub;
+            live[r] = rb < rows_per_batch;
+            const T *src = scores + (batch_row0 + rb) * (uint64_t) seq;
 #pragma unroll
             for (int k = 0; k < VPT; ++k) {
                 const int idx = l + k * LPR;
-                if (idx < nvec) {
+                raw[r][k] = (live[r] && idx < nvec) ? ld_stream(src + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
+            }
+        }
+
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) {
-                        v[k][e] *= inv;
+        for (int r = 0; r < ROWS; ++r) {
+            float2 v[VPT][PAIRS];
+            float mx = -3.0e38f;
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                Vec2<T>::unpack(raw[r][k], v[k]);
+                if (l + k * LPR < nvec) {
+#pragma unroll
+                    for (int e = 0; e < PAIRS; ++e) {
+                        v[k][e] = fma2(scale2, v[k][e], madd[k][e]);
+                        mx = fmaxf(mx, fmaxf(v[k][e].x, v[k][e].y));
                     }
-                    st_vec(dst + (size_t) idx * EPV, Vec<T>::pack(v[k]));
+                }
+            }
+            mx = group_max<LPR>(mx);
+
+            // exp(v - mx) = 2^(v * log2e - mx * log2e): the product is exact inside the FMA and the
+            // rounding of mx * log2e is a factor common to the whole row, which the division removes.
+            const float2 neg_mx = splat2(-mx * kLog2e);
+            float2 sum2 = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                if (l + k * LPR < nvec) {
+#pragma unroll
+                    for (int e = 0; e < PAIRS; ++e) {
+                        const float2 t = fma2(v[k][e], log2e2, neg_mx);
+                        v[k][e] = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+                        sum2 = add2(sum2, v[k][e]);
+                    }
+                }
+            }
+            const float sum = group_sum<LPR>(sum2.x + sum2.y);
+            const float2 inv = splat2(1.f / sum);
+
+            if (live[r]) {
+                T *dst = out + (batch_row0 + r0 + r * GPW + sub) * (uint64_t) seq;
+#pragma unroll
+                for (int k = 0; k < VPT; ++k) {
+                    const int idx = l + k * LPR;
+                    if (idx < nvec) {
+#pragma unroll
+                        for (int e = 0; e < PAIRS; ++e) {
+                            v[k][e] = mul2(v[k][e], inv);
+                        }
+                        st_vec(dst + (size_t) idx * EPV, Vec2<T>::pack(v[k]));
+                    }
                 }
             }
         }
@@ -183,16 +215,23 @@ int masked_softmax(const T *scores, const int8_t *mask, int64_t rows, int64_t ro
     constexpr int EPV = Vec<T>::EPV;
     constexpr int BLOCK = 256;
     const int nvec = seq / EPV;
+    const int64_t batches = rows / rows_per_batch;
     const bool vec_ok = seq % EPV == 0 && nvec <= 256 && aligned16(scores) && aligned16(out) &&
-                        (mask == nullptr || aligned8(mask)) && rows_per_batch <= 0xffffffffLL;
+                        (mask == nullptr || aligned8(mask)) && rows_per_batch <= 0x7fffffffLL &&
+                        rows % rows_per_batch == 0;
     if (vec_ok) {
-        const FastDiv rpb = make_fastdiv((uint32_t) rows_per_batch);
 #define LAUNCH(LPR, VPT, ROWS)                                                                          \
     {                                                                                                   \
+        static OccupancyCache cache;                                                                    \
+        auto kernel = masked_softmax_kernel<T, LPR, VPT, ROWS, BLOCK>;                                  \
         const int64_t rows_per_block = (int64_t) (BLOCK / 32) * (32 / LPR) * ROWS;                      \
-        const int64_t grid = (rows + rows_per_block - 1) / rows_per_block;                              \
-        masked_softmax_kernel<T, LPR, VPT, ROWS, BLOCK><<<(unsigned) grid, BLOCK, 0, stream>>>(         \
-            scores, mask, out, (uint32_t) rows, rpb, seq, nvec, scale);                                 \
+        const int64_t per_batch = (rows_per_batch + rows_per_block - 1) / rows_per_block;               \
+        const int64_t items = per_batch * batches;                                                      \
+        int64_t grid = resident_blocks(kernel, BLOCK, 0, &cache);                                       \
+        if (grid > items) grid = items;                                                                 \
+        kernel<<<(unsigned) grid, BLOCK, 0, stream>>>(scores, mask, out, (uint32_t) rows_per_batch,     \
+                                                      seq, nvec, scale, (uint32_t) items,               \
+                                                      make_fastdiv((uint32_t) per_batch));              \
     }
         if (nvec <= 1) {
             LAUNCH(1, 1, 4);

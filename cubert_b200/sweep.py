@@ -38,19 +38,40 @@ def measured_peak_gbs():
     return 6650.0, "fallback"
 
 
+USE_GRAPH = True
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
 def _time(launch, nsets, iters, warmup=3):
-    stream = torch.cuda.current_stream()
+    """Seconds per launch. The `iters` launches are captured into one CUDA graph and replayed,
+    so that the host's launch cost (Python + ctypes) is not part of the device time."""
     for i in range(warmup):
         launch(i % nsets)
+    torch.cuda.synchronize()
     start = torch.cuda.Event(enable_timing=True)
     stop = torch.cuda.Event(enable_timing=True)
+    if USE_GRAPH:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(iters):
+                launch(i % nsets)
+        graph.replay()  # warm replay
+        torch.cuda.synchronize()
+        stream = torch.cuda.current_stream()
+        start.record(stream)
+        graph.replay()
+        stop.record(stream)
+    else:
+        stream = torch.cuda.current_stream()
+        start.record(stream)
+        for i in range(iters):
+            launch(i % nsets)
+        stop.record(stream)
     torch.cuda.synchronize()
-    start.record(stream)
-    for i in range(iters):
-        launch(i % nsets)
-    stop.record(stream)
-    torch.cuda.synchronize()
-    return start.elapsed_time(stop) / iters * 1e-3  # seconds per launch
+    return start.elapsed_time(stop) / iters * 1e-3
 
 
 def _nsets(bytes_per_set, budget=8 << 30):
@@ -79,12 +100,11 @@ def case_ln(t, rows, ch, iters):
     bias = torch.randn(ch, device="cuda").to(_dt(t))
     gamma = torch.ones(ch, device="cuda", dtype=_dt(t))
     beta = torch.zeros(ch, device="cuda", dtype=_dt(t))
-    s = torch.cuda.current_stream().cuda_stream
     f = _fn("bias_residual_ln", t)
 
     def launch(i):
         kernels.check(f(xs[i].data_ptr(), bias.data_ptr(), rs[i].data_ptr(), gamma.data_ptr(), beta.data_ptr(),
-                        rows, ch, outs[i].data_ptr(), s))
+                        rows, ch, outs[i].data_ptr(), _stream()))
 
     sec = _time(launch, n, iters)
     return dict(kernel="bias_residual_ln", dtype=t, shape=[rows, ch], bytes=per_set + 3 * ch * e, sec=sec, sets=n)
@@ -98,11 +118,10 @@ def case_gelu(t, rows, ch, iters):
     xs = [torch.randn((rows, ch), device="cuda", generator=g, dtype=torch.float32).to(_dt(t)) for _ in range(n)]
     outs = [torch.empty((rows, ch), device="cuda", dtype=_dt(t)) for _ in range(n)]
     bias = torch.randn(ch, device="cuda").to(_dt(t))
-    s = torch.cuda.current_stream().cuda_stream
     f = _fn("bias_gelu", t)
 
     def launch(i):
-        kernels.check(f(xs[i].data_ptr(), bias.data_ptr(), rows, ch, outs[i].data_ptr(), s))
+        kernels.check(f(xs[i].data_ptr(), bias.data_ptr(), rows, ch, outs[i].data_ptr(), _stream()))
 
     sec = _time(launch, n, iters)
     return dict(kernel="bias_gelu", dtype=t, shape=[rows, ch], bytes=per_set + ch * e, sec=sec, sets=n)
@@ -118,11 +137,10 @@ def case_softmax(t, batch, seq, iters, heads=12):
     outs = [torch.empty((rows, seq), device="cuda", dtype=_dt(t)) for _ in range(n)]
     lens = torch.randint(max(1, seq // 16), seq + 1, (batch,), device="cuda", generator=g)
     mask = (torch.arange(seq, device="cuda")[None, :] < lens[:, None]).to(torch.int8).contiguous()
-    s = torch.cuda.current_stream().cuda_stream
     f = _fn("masked_softmax", t)
 
     def launch(i):
-        kernels.check(f(xs[i].data_ptr(), mask.data_ptr(), rows, heads * seq, seq, 0.125, outs[i].data_ptr(), s))
+        kernels.check(f(xs[i].data_ptr(), mask.data_ptr(), rows, heads * seq, seq, 0.125, outs[i].data_ptr(), _stream()))
 
     sec = _time(launch, n, iters)
     return dict(kernel="masked_softmax", dtype=t, shape=[batch, heads, seq, seq], bytes=per_set + batch * seq,
@@ -142,13 +160,12 @@ def case_embed(t, batch, seq, iters, hidden=768, vocab=21128):
     ids = [torch.randint(0, vocab, (batch, seq), device="cuda", generator=g, dtype=torch.int32) for _ in range(n)]
     seg = torch.randint(0, 2, (batch, seq), device="cuda", generator=g).to(torch.int8)
     outs = [torch.empty((batch, seq, hidden), device="cuda", dtype=_dt(t)) for _ in range(n)]
-    s = torch.cuda.current_stream().cuda_stream
     f = _fn("embed_ln", t)
 
     def launch(i):
         kernels.check(f(ids[i].data_ptr(), seg.data_ptr(), word.data_ptr(), pos.data_ptr(), typ.data_ptr(),
                         gamma.data_ptr(), beta.data_ptr(), batch, seq, hidden, vocab, 2, outs[i].data_ptr(),
-                        None, s))
+                        None, _stream()))
 
     sec = _time(launch, n, iters)
     nbytes = per_set + 5 * batch * seq + seq * hidden * e + 2 * hidden * e + 2 * hidden * e
@@ -164,11 +181,10 @@ def case_pool(t, batch, seq, hidden, iters):
     out = torch.empty((batch, hidden), device="cuda", dtype=_dt(t))
     need = kernels.load().cubk_mean_pool_scratch_bytes(batch, seq, hidden)
     scratch = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
-    s = torch.cuda.current_stream().cuda_stream
     f = _fn("mean_pool", t)
 
     def launch(i):
-        kernels.check(f(xs[i].data_ptr(), batch, seq, hidden, out.data_ptr(), scratch.data_ptr(), need, s))
+        kernels.check(f(xs[i].data_ptr(), batch, seq, hidden, out.data_ptr(), scratch.data_ptr(), need, _stream()))
 
     sec = _time(launch, n, iters)
     return dict(kernel="mean_pool", dtype=t, shape=[batch, seq, hidden], bytes=per_set + batch * hidden * e,
@@ -221,7 +237,10 @@ def main():
     ap.add_argument("--dtype", default="f16,f32")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", default=None)
+    ap.add_argument("--no-graph", action="store_true", help="time plain stream launches instead of a graph replay")
     a = ap.parse_args()
+    global USE_GRAPH
+    USE_GRAPH = not a.no_graph
     if not torch.cuda.is_available():
         sys.exit("cubert_b200.sweep needs a CUDA device")
     results, peak, kind = run(a.only.split(",") if a.only else None, a.dtype.split(","), a.quick, a.iters)

@@ -117,6 +117,18 @@ def half_to_float(x):
     return out
 
 
+def copy_from_device(address, shape, dtype):
+    """numpy copy of a raw device allocation (cudaMemcpy device-to-host through the CUDA runtime)."""
+    import ctypes
+    out = np.empty(shape, dtype)
+    cudart = ctypes.CDLL("libcudart.so.12")
+    cudart.cudaMemcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+    torch.cuda.synchronize()
+    rc = cudart.cudaMemcpy(out.ctypes.data, address, out.nbytes, 2)
+    assert rc == 0, rc
+    return out
+
+
 def host(t):
     torch.cuda.synchronize()
     return t.detach().float().cpu().numpy()

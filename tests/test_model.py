@@ -1,0 +1,306 @@
+"""The host library (include/cuBERT.h, include/cubert_b200.h): model-file codec on CPU; whole
+forward pass, outputs, error behaviour, replica manager and device-resident entry points on GPU.
+
+Whole-model parity, float32: our result against the reference's own CPU output (golden
+fixtures written by tests/golden/make_reference_fixtures.py, plus oracle/_ref run live where
+it exists) and against the C oracle. The algorithm is identical; the GEMMs are summed in a
+different order by cuBLAS than by MKL, so the bar is 1e-5 relative to the tensor's scale
+(see `rel_err`). binary16: weights rounded to binary16, float32 oracle on the rounded weights;
+bar 1e-2 absolute on probs and pooled output.
+"""
+import os
+import threading
+
+import numpy as np
+import pytest
+
+from cubert_b200 import frozen_graph, model, synthetic
+from tests.golden.make_reference_fixtures import CASES, weight_checksum
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def rel_err(got, ref):
+    """max |got - ref| relative to the root-mean-square magnitude of the reference tensor."""
+    got = np.asarray(got, np.float64)
+    ref = np.asarray(ref, np.float64)
+    return float(np.max(np.abs(got - ref)) / (np.sqrt(np.mean(ref * ref)) + 1e-30))
+
+
+@pytest.fixture(scope="module")
+def model_files(tmp_path_factory):
+    """name -> (path, cfg, var) of frozen graphs holding the seeded fixture models."""
+    d = tmp_path_factory.mktemp("models")
+    out = {}
+    for name, (cfg_name, seed, batch, seq, lengths, segments) in CASES.items():
+        cfg = synthetic.config(cfg_name)
+        var = synthetic.random_weights(cfg, seed)
+        path = str(d / (name + ".pb"))
+        frozen_graph.write_frozen_graph(path, var, extra_nodes=["bert/encoder/Reshape", "loss/Softmax"])
+        out[name] = (path, cfg, var)
+    return out
+
+
+def golden(name):
+    return np.load(os.path.join(GOLDEN, "reference_forward_%s.npz" % name))
+
+
+# ============================================================================ CPU: model-file codec
+
+def test_frozen_graph_round_trip_python(model_files):
+    path, cfg, var = model_files["tiny"]
+    back = frozen_graph.read_frozen_graph(path)
+    assert set(back) == set(var)
+    for k in var:
+        assert back[k].dtype == np.float32 and np.array_equal(back[k], var[k])
+
+
+@pytest.mark.parametrize("ct,dtype", [(model.ComputeType.FLOAT, np.float32), (model.ComputeType.HALF, np.float16)])
+def test_frozen_graph_cpp_reader(model_files, ct, dtype):
+    """The C++ loader sees every tensor, converts with round-to-nearest and sniffs the geometry
+    (src/cuBERT/tensorflow/Graph.cpp:28-79)."""
+    for name in ("tiny", "tiny_mean"):
+        path, cfg, var = model_files[name]
+        g = model.FrozenGraph(path, ct)
+        assert g.info["vocab_size"] == cfg["vocab"] and g.info["hidden_size"] == cfg["hidden"]
+        assert g.info["type_vocab_size"] == cfg["type_vocab"] and g.info["intermediate_size"] == cfg["intermediate"]
+        assert g.info["num_labels"] == cfg["num_labels"] and g.info["has_pooler_dense"] == int(cfg["pooler"])
+        for k, v in var.items():
+            assert np.array_equal(g.tensor(k), v.astype(dtype).ravel()), k
+        with pytest.raises(ValueError):
+            g.tensor("no/such/tensor")
+        g.close()
+
+
+def test_frozen_graph_half_file_and_errors(tmp_path):
+    cfg = synthetic.config("tiny")
+    var = {k: v.astype(np.float16) for k, v in synthetic.random_weights(cfg, 3).items()}
+    path = str(tmp_path / "half.pb")
+    frozen_graph.write_frozen_graph(path, var)
+    g = model.FrozenGraph(path, model.ComputeType.FLOAT)  # DT_HALF file opened as a float32 model
+    assert np.array_equal(g.tensor("output_bias"), var["output_bias"].astype(np.float32))
+    g.close()
+    with pytest.raises(ValueError, match="model file not found"):
+        model.FrozenGraph(str(tmp_path / "missing.pb"))
+    (tmp_path / "empty.pb").write_bytes(b"")
+    with pytest.raises(ValueError, match="model file invalid"):
+        model.FrozenGraph(str(tmp_path / "empty.pb"))
+    (tmp_path / "garbage.pb").write_bytes(b"\x0a\xff\xff\xff\xff\x0f not a graph")
+    with pytest.raises(ValueError, match="model file invalid"):
+        model.FrozenGraph(str(tmp_path / "garbage.pb"))
+
+
+def test_golden_fixtures_match_the_weight_generator():
+    for name, (cfg_name, seed, batch, seq, lengths, segments) in CASES.items():
+        g = golden(name)
+        cfg = synthetic.config(cfg_name)
+        assert abs(float(g["weight_checksum"]) - weight_checksum(synthetic.random_weights(cfg, seed))) < 1e-9
+        ids, mask, seg, _ = synthetic.random_inputs(cfg, batch, seq, seed, lengths=lengths, segments=segments)
+        assert np.array_equal(g["ids"], ids) and np.array_equal(g["mask"], mask) and np.array_equal(g["seg"], seg)
+
+
+def test_oracle_reproduces_reference_fixtures(oracle):
+    """The C oracle against the reference's recorded outputs (runs without the reference tree)."""
+    for name, (cfg_name, seed, batch, seq, lengths, segments) in CASES.items():
+        g = golden(name)
+        cfg = synthetic.config(cfg_name)
+        out = oracle.bert_forward(synthetic.random_weights(cfg, seed), synthetic.model_geometry(cfg, seq),
+                                  g["ids"], g["mask"], g["seg"])
+        for k, v in out.items():
+            assert rel_err(v, g[k]) < 5e-6, (name, k)
+
+
+# ============================================================================ GPU: whole model
+
+def _run(m, ids, mask, seg, cfg, to_float=False):
+    b, s = ids.shape
+    h = cfg["hidden"]
+    dt = np.float32 if (to_float or m.dtype == np.float32) else np.float16
+    out = model.Output()
+    out.embedding_output = np.zeros((b, s, h), dt)
+    out.sequence_output = np.zeros((b, s, h), dt)
+    out.pooled_output = np.zeros((b, h), dt)
+    if m.info["num_labels"] > 0:
+        out.logits = np.zeros((b, m.info["num_labels"]), dt)
+        out.probs = np.zeros((b, m.info["num_labels"]), dt)
+    m.compute_m(ids, mask, seg, out, output_to_float=to_float)
+    return {f: getattr(out, f) for f in model.Output.FIELDS if getattr(out, f) is not None}
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", list(CASES))
+def test_forward_f32_matches_reference(model_files, oracle, name):
+    path, cfg, var = model_files[name]
+    g = golden(name)
+    ids, mask, seg = g["ids"], g["mask"], g["seg"]
+    m = model.Model(path, ids.shape[0] + 3, ids.shape[1], cfg["layers"], cfg["heads"], model.ComputeType.FLOAT)
+    assert m.info["hidden_size"] == cfg["hidden"] and m.info["num_labels"] == cfg["num_labels"]
+    got = _run(m, ids, mask, seg, cfg)
+    ref = oracle.bert_forward(var, synthetic.model_geometry(cfg, ids.shape[1]), ids, mask, seg)
+    assert set(got) == {k for k in g.files if k not in ("ids", "mask", "seg", "weight_checksum")}
+    # embeddings involve no GEMM: 1e-5 of the element itself (floor at the tensor scale * 1e-0)
+    assert rel_err(got["embedding_output"], g["embedding_output"]) < 1e-5
+    for k in got:
+        assert rel_err(got[k], g[k]) < 1e-5, (k, rel_err(got[k], g[k]))      # the reference's own output
+        assert rel_err(got[k], ref[k]) < 1e-5, (k, rel_err(got[k], ref[k]))  # the C oracle
+    m.close()
+
+
+@pytest.mark.gpu
+def test_forward_f32_matches_reference_live(model_files, reference_cpu):
+    """Same comparison with oracle/_ref executed now, on a batch the fixtures do not hold."""
+    path, cfg, var = model_files["small"]
+    ids, mask, seg, _ = synthetic.random_inputs(cfg, 7, 32, 123, lengths=(1, 32), segments="random")
+    m = model.Model(path, 8, 32, cfg["layers"], cfg["heads"], model.ComputeType.FLOAT)
+    got = _run(m, ids, mask, seg, cfg)
+    ref = reference_cpu.bert_forward(var, synthetic.model_geometry(cfg, 32), ids, mask, seg)
+    for k in got:
+        assert rel_err(got[k], ref[k]) < 1e-5, (k, rel_err(got[k], ref[k]))
+    m.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", list(CASES))
+def test_forward_f16_within_tolerance(model_files, oracle, name):
+    path, cfg, var = model_files[name]
+    g = golden(name)
+    ids, mask, seg = g["ids"], g["mask"], g["seg"]
+    var16 = {k: v.astype(np.float16).astype(np.float32) for k, v in var.items()}
+    ref = oracle.bert_forward(var16, synthetic.model_geometry(cfg, ids.shape[1]), ids, mask, seg)
+    m = model.Model(path, ids.shape[0], ids.shape[1], cfg["layers"], cfg["heads"], model.ComputeType.HALF)
+    raw = _run(m, ids, mask, seg, cfg)                      # binary16 outputs
+    conv = _run(m, ids, mask, seg, cfg, to_float=True)      # converted on the device
+    for k in raw:
+        assert raw[k].dtype == np.float16 and conv[k].dtype == np.float32
+        assert np.array_equal(raw[k].astype(np.float32), conv[k]), k
+    # embeddings: the reference accepts 3e-4 (test/cuBERT/BertTest.cpp:96-101); outputs are O(1)
+    assert np.max(np.abs(conv["embedding_output"] - ref["embedding_output"])) < 4e-3
+    # encoder output: the reference accepts up to 1e-2 after 2 layers (op_att/TransformerTest.cpp:330-341)
+    assert np.max(np.abs(conv["sequence_output"] - ref["sequence_output"])) < 3e-2
+    assert np.max(np.abs(conv["pooled_output"] - ref["pooled_output"])) < 1e-2
+    if "probs" in conv:
+        assert np.max(np.abs(conv["probs"] - ref["probs"])) < 1e-2
+        assert np.max(np.abs(conv["logits"] - ref["logits"])) < 1e-2
+    m.close()
+
+
+@pytest.mark.gpu
+def test_single_output_api_and_repeatability(model_files):
+    """cuBERT_compute with each cuBERT_OutputType; four consecutive calls give identical results
+    (test/cuBERT/BertMTest.cpp:5-38 checks that the round-robin and buffer reuse do not leak state)."""
+    path, cfg, var = model_files["tiny"]
+    g = golden("tiny")
+    ids, mask, seg = g["ids"], g["mask"], g["seg"]
+    b, s = ids.shape
+    m = model.Model(path, 8, s, cfg["layers"], cfg["heads"])
+    shapes = {model.OutputType.LOGITS: ("logits", (b, 3)), model.OutputType.PROBS: ("probs", (b, 3)),
+              model.OutputType.POOLED_OUTPUT: ("pooled_output", (b, 64)),
+              model.OutputType.SEQUENCE_OUTPUT: ("sequence_output", (b, s, 64)),
+              model.OutputType.EMBEDDING_OUTPUT: ("embedding_output", (b, s, 64))}
+    for ot, (key, shape) in shapes.items():
+        first = None
+        for _ in range(4):
+            out = np.zeros(shape, np.float32)
+            m.compute(ids, mask, seg, out, ot)
+            assert rel_err(out, g[key]) < 1e-5
+            if first is None:
+                first = out
+            assert np.array_equal(out, first)
+    # a smaller batch after a larger one must not see stale rows
+    out = np.zeros((2, 3), np.float32)
+    m.compute(ids[:2].copy(), mask[:2].copy(), seg[:2].copy(), out, model.OutputType.LOGITS)
+    assert rel_err(out, g["logits"][:2]) < 1e-5
+    m.close()
+
+
+@pytest.mark.gpu
+def test_error_behaviour(model_files, tmp_path):
+    """What the reference reports as std::invalid_argument (src/cuBERT/Bert.cpp:100-103,
+    BertM.cpp:95, tensorflow/Graph.cpp:18,84)."""
+    path, cfg, var = model_files["tiny"]
+    with pytest.raises(ValueError, match="model file not found"):
+        model.Model(str(tmp_path / "nope.pb"), 4, 16, 2, 4)
+    partial = {k: v for k, v in var.items() if "layer_1" not in k}
+    frozen_graph.write_frozen_graph(str(tmp_path / "partial.pb"), partial)
+    with pytest.raises(ValueError, match="layer_1"):
+        model.Model(str(tmp_path / "partial.pb"), 4, 16, 2, 4)
+    m = model.Model(path, 4, 16, cfg["layers"], cfg["heads"])
+    ids, mask, seg, _ = synthetic.random_inputs(cfg, 5, 16, 0)
+    out = np.zeros((5, 3), np.float32)
+    with pytest.raises(ValueError, match="batch_size > max_batch_size"):
+        m.compute(ids, mask, seg, out)
+    with pytest.raises(ValueError, match="invalid output type"):
+        m.compute(ids[:4].copy(), mask[:4].copy(), seg[:4].copy(), out, 17)
+    # batch 0 returns silently and writes nothing
+    sentinel = np.full((1, 3), 7.0, np.float32)
+    m.compute(ids[:0].copy(), mask[:0].copy(), seg[:0].copy(), sentinel)
+    assert np.all(sentinel == 7.0)
+    # the model is still usable after the errors
+    ok = np.zeros((4, 3), np.float32)
+    m.compute(ids[:4].copy(), mask[:4].copy(), seg[:4].copy(), ok)
+    assert np.all(np.isfinite(ok)) and np.any(ok != 0)
+    m.close()
+
+
+@pytest.mark.gpu
+def test_device_resident_forward_and_profile(model_files):
+    import torch
+    path, cfg, var = model_files["small"]
+    g = golden("small")
+    ids, mask, seg = g["ids"], g["mask"], g["seg"]
+    b, s = ids.shape
+    m = model.Model(path, b, s, cfg["layers"], cfg["heads"])
+    want = _run(m, ids, mask, seg, cfg)
+    m.profile_read()  # clear counters
+    m.profile_enable(True)
+    d_ids, d_mask, d_seg = (torch.from_numpy(a).cuda() for a in (ids, mask, seg))
+    torch.cuda.synchronize()
+    m.forward_device(0, b, d_ids.data_ptr(), d_mask.data_ptr(), d_seg.data_ptr())
+    m.synchronize(0)
+    prof = m.profile_read()
+    m.profile_enable(False)
+    L = cfg["layers"]
+    assert prof["embed_ln"]["launches"] == 1 and prof["bias_residual_ln"]["launches"] == 2 * L
+    assert prof["bias_gelu"]["launches"] == L and prof["masked_softmax"]["launches"] == L
+    assert prof["bias_tanh"]["launches"] == 1 and prof["logits_probs"]["launches"] == 1
+    assert prof["gemm"]["launches"] == 6 * L + 1
+    assert prof["bias_gelu"]["ms"] > 0 and prof["bias_gelu"]["bytes"] == 2 * b * s * cfg["intermediate"] * 4 + \
+        cfg["intermediate"] * 4
+    # the results stayed in the replica's device buffers
+    ptrs = m.device_outputs(0)
+    import gpu_harness as G
+    seq_out = G.copy_from_device(ptrs["sequence_output"], (b, s, cfg["hidden"]), np.float32)
+    assert np.array_equal(seq_out, want["sequence_output"])
+    probs = G.copy_from_device(ptrs["probs"], (b, cfg["num_labels"]), np.float32)
+    assert np.array_equal(probs, want["probs"])
+    m.close()
+
+
+@pytest.mark.gpu
+def test_concurrent_callers_are_serialised_per_replica(model_files):
+    """Several threads on one model: every call must return the right answer
+    (src/cuBERT/BertM.cpp:69-76 locks the chosen replica)."""
+    path, cfg, var = model_files["tiny"]
+    g = golden("tiny")
+    ids, mask, seg = g["ids"], g["mask"], g["seg"]
+    m = model.Model(path, 8, ids.shape[1], cfg["layers"], cfg["heads"])
+    errors = []
+
+    def worker(k):
+        try:
+            for _ in range(10):
+                n = 1 + (k % ids.shape[0])
+                out = np.zeros((n, 3), np.float32)
+                m.compute(ids[:n].copy(), mask[:n].copy(), seg[:n].copy(), out, model.OutputType.PROBS)
+                if rel_err(out, g["probs"][:n]) > 1e-5:
+                    errors.append((k, rel_err(out, g["probs"][:n])))
+        except Exception as e:  # pragma: no cover
+            errors.append((k, repr(e)))
+
+    threads = [threading.Thread(target=worker, args=(k,)) for k in range(6)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    m.close()

@@ -1,0 +1,377 @@
+#!/usr/bin/env python3
+"""Benchmark of the BERT forward pass through the cuBERT C API on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (BASELINE config 3): BERT-base, binary16 weight/activation storage with float32
+arithmetic, seq_length 128, batch 256 per GPU, per-sequence valid length uniform in [8, 128]
+(prefix mask), seeded random-init weights N(0, 0.02) and uniform token ids; outputs
+cuBERT_SEQUENCE_OUTPUT and cuBERT_POOLED_OUTPUT. One step = one forward pass over one batch.
+One process per GPU, each with its own model replica; the batch dimension is the only parallel
+axis, so there is no collective on the data path ("weak" scaling: per-GPU work is fixed).
+
+Printed by rank 0 as ONE JSON line:
+  value      sequences/s, whole job, inputs already resident in device memory, timed with CUDA
+             events on the replica's stream (max over ranks)
+  e2e        the same through cuBERT_compute_m with pinned HOST buffers: host-to-device copy of
+             ids/mask/segments and device-to-host copy of both outputs inside the timed region
+  roofline   the fused kernel with the largest share of the step: algorithmic bytes / its mean
+             launch duration (CUDA events around every launch, same timed region)
+  kernels    the same figures for every kernel family
+  cpu_baseline  the reference's own CPU code (oracle/_ref) or, failing that, its C restatement,
+             timed on this machine's host cores on a bounded sample (N = 1 only)
+
+--impl reference times only that CPU implementation, on the same workload definition.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+RANK = int(os.environ.get("RANK", "0"))
+LOCAL_RANK = int(os.environ.get("LOCAL_RANK", "0"))
+WORLD = int(os.environ.get("WORLD_SIZE", "1"))
+
+WORKLOAD = dict(model="base", seq=128, batch=256, lengths=(8, 128), seed=2)
+METRIC = "BERT-base seq128 seqs/s"
+UNIT = "sequences/s"
+L2_NOTE = ("no explicit L2 flush: one step streams 218 MB of weights and >1 GB of activations, "
+           "far more than the 126 MB L2")
+
+
+def physical_gpu_index():
+    vis = os.environ.get("CUBERT_BENCH_PARENT_VISIBLE", os.environ.get("CUDA_VISIBLE_DEVICES", ""))
+    ids = [v for v in vis.split(",") if v.strip() != ""]
+    if ids and LOCAL_RANK < len(ids) and ids[LOCAL_RANK].isdigit():
+        return int(ids[LOCAL_RANK])
+    return LOCAL_RANK
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed regions run."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.path = tempfile.mktemp(prefix="cubert_clocks_", suffix=".csv")
+        self.proc = None
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.out, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.out.close()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                p = [x.strip() for x in line.split(",")]
+                if len(p) < 9:
+                    continue
+                try:
+                    sm.append(float(p[1]))
+                    smax.append(float(p[2]))
+                    power.append(float(p[3]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, p[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        try:
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
+        # "under load": samples in the upper half of the power range seen
+        lo, hi = min(power), max(power)
+        loaded = [c for c, w in zip(sm, power) if w >= lo + 0.5 * (hi - lo)] or sm
+        return dict(sm_mhz=statistics.median(loaded), sm_max_mhz=max(smax), reasons=sorted(reasons),
+                    samples=len(sm), power_w_max=hi)
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# Per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the fused kernels on
+# this workload's shapes, from the ncu captures summarised under profiles/. None = not captured.
+NCU_TRAFFIC_BYTES = {
+    "bias_gelu": None,
+    "bias_residual_ln": None,
+    "masked_softmax": None,
+    "embed_ln": None,
+}
+
+
+def make_model_file(cfg, seed, half):
+    import numpy as np
+    from cubert_b200 import frozen_graph, synthetic
+    var = synthetic.random_weights(cfg, seed)
+    if half:
+        var = {k: v.astype(np.float16) for k, v in var.items()}
+    d = tempfile.mkdtemp(prefix="cubert_b200_bench_")
+    path = os.path.join(d, "model.pb")
+    frozen_graph.write_frozen_graph(path, var)
+    return path, var
+
+
+def cpu_reference_rate(cfg, var32, seq, sample_batch, lengths, seed, steps, warmup):
+    """sequences/s of the reference's CPU implementation (float32; it has no binary16 path) on
+    `sample_batch` sequences of the workload per step. Returns (rate, kind, cores, seconds/step)."""
+    import numpy as np
+    from cubert_b200 import synthetic
+    from oracle import bindings
+    geo = synthetic.model_geometry(cfg, seq)
+    ids, mask, seg, _ = synthetic.random_inputs(cfg, sample_batch, seq, seed, lengths=lengths)
+    cores = os.cpu_count() or 1
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    os.environ.setdefault("KMP_BLOCKTIME", "0")  # as the reference's README recommends
+    times = []
+    if os.path.exists(bindings.REF_CPU_SO):
+        kind = "reference"
+        ref = bindings.Reference()
+        h = ref.bert_open(var32, geo, sample_batch)
+        try:
+            for i in range(warmup + steps):
+                t0 = time.perf_counter()
+                ref.bert_compute(h, ids, mask, seg)
+                ref.bert_output(h, sample_batch, geo, "output_weights" in var32)
+                if i >= warmup:
+                    times.append(time.perf_counter() - t0)
+        finally:
+            ref.bert_close(h)
+    else:
+        kind = "port"
+        bindings.build()
+        orc = bindings.Oracle()
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            orc.bert_forward(var32, geo, ids, mask, seg)
+            if i >= warmup:
+                times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    return sample_batch / sec, kind, int(os.environ["OMP_NUM_THREADS"]), sec
+
+
+def run_reference_arm(args):
+    """--impl reference: the reference's own CPU implementation of the path, rank 0 only."""
+    if RANK != 0:
+        return
+    import numpy as np  # noqa: F401
+    from cubert_b200 import synthetic
+    cfg = synthetic.config(WORKLOAD["model"])
+    var32 = synthetic.random_weights(cfg, WORKLOAD["seed"])
+    sample = 32
+    rate, kind, cores, sec = cpu_reference_rate(cfg, var32, WORKLOAD["seq"], sample, WORKLOAD["lengths"],
+                                                WORKLOAD["seed"], args.steps, max(1, min(args.warmup, 3)))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": rate, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "BERT-base forward, seq_length 128, float32 on host cores (the reference's CPU "
+                               "build has no binary16), valid length U[8,128]",
+                   "sample_batch": sample, "full_batch": WORKLOAD["batch"], "seed": WORKLOAD["seed"]},
+        "cpu_baseline": {"value": rate, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": "%d sequences per step (of the 256-sequence batch), %d timed steps" %
+                                   (sample, args.steps)},
+        "e2e": {"value": rate, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    # one replica per process: restrict the library to this rank's GPU before CUDA starts
+    if WORLD > 1:
+        os.environ["CUBERT_BENCH_PARENT_VISIBLE"] = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+        os.environ["CUDA_VISIBLE_DEVICES"] = str(physical_gpu_index())
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from cubert_b200 import model, synthetic
+
+    if not torch.cuda.is_available():
+        sys.exit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(0)
+    if WORLD > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", 0))
+
+    def barrier():
+        if WORLD > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if WORLD == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(x):
+        if WORLD == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    cfg = synthetic.config(WORKLOAD["model"])
+    B, S, H = WORKLOAD["batch"], WORKLOAD["seq"], cfg["hidden"]
+    path, var16 = make_model_file(cfg, WORKLOAD["seed"], half=True)
+    m = model.Model(path, B, S, cfg["layers"], cfg["heads"], model.ComputeType.HALF)
+    os.unlink(path)
+    assert m.info["replicas"] == 1, "one replica per process expected, got %d" % m.info["replicas"]
+
+    # every rank works on its own batch of the seeded stream
+    ids, mask, seg, lens = synthetic.random_inputs(cfg, B, S, WORKLOAD["seed"] + 1000 * RANK,
+                                                   lengths=WORKLOAD["lengths"])
+    pin = lambda a: torch.from_numpy(a).pin_memory()  # noqa: E731
+    h_ids, h_mask, h_seg = pin(ids), pin(mask), pin(seg)
+    h_seq = torch.empty((B, S, H), dtype=torch.float16).pin_memory()
+    h_pool = torch.empty((B, H), dtype=torch.float16).pin_memory()
+    d_ids, d_mask, d_seg = h_ids.cuda(), h_mask.cuda(), h_seg.cuda()
+    out = model.Output()
+    out.sequence_output = h_seq.numpy()
+    out.pooled_output = h_pool.numpy()
+    np_ids, np_mask, np_seg = h_ids.numpy(), h_mask.numpy(), h_seg.numpy()
+    stream = torch.cuda.ExternalStream(m.replica_stream(0))
+
+    sampler = ClockSampler(physical_gpu_index()) if RANK == 0 else None
+
+    # ---- device-resident: `value` and the per-kernel figures
+    for _ in range(args.warmup):
+        m.forward_device(0, B, d_ids.data_ptr(), d_mask.data_ptr(), d_seg.data_ptr())
+    m.synchronize(0)
+    m.profile_read(0)
+    m.profile_enable(True, 0)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record(stream)
+    for _ in range(args.steps):
+        m.forward_device(0, B, d_ids.data_ptr(), d_mask.data_ptr(), d_seg.data_ptr())
+    stop.record(stream)
+    m.synchronize(0)
+    barrier()
+    dev_ms = max_over_ranks(start.elapsed_time(stop))
+    prof = m.profile_read(0)
+    m.profile_enable(False, 0)
+
+    # ---- end to end through the C API with pinned host buffers
+    for _ in range(args.warmup):
+        m.compute_m(np_ids, np_mask, np_seg, out)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        m.compute_m(np_ids, np_mask, np_seg, out)
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    e2e_s = max_over_ranks(e2e_s)
+    ok = bool(np.all(np.isfinite(out.pooled_output.astype(np.float32))))
+    clocks = sampler.stop() if sampler else None
+
+    launches = sum_over_ranks(sum(v["launches"] for k, v in prof.items() if k != "gemm"))
+    if RANK != 0:
+        m.close()
+        if WORLD > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peak()
+    kernels = {}
+    for k, v in prof.items():
+        if v["launches"] == 0:
+            continue
+        entry = dict(launches=int(v["launches"]), ms_total=v["ms"], us_per_launch=1e3 * v["ms"] / v["launches"],
+                     share_of_step=v["ms"] / (dev_ms if WORLD == 1 else start.elapsed_time(stop)))
+        if k != "gemm" and v["bytes"] > 0 and v["ms"] > 0:
+            entry["bytes_per_launch"] = int(v["bytes"] / v["launches"])
+            entry["gbs"] = v["bytes"] / (v["ms"] * 1e-3) / 1e9
+            entry["frac_of_%s_peak" % peak_kind] = entry["gbs"] / peak
+        kernels[k] = entry
+    ours = {k: v for k, v in kernels.items() if k != "gemm" and "gbs" in v}
+    top = max(ours, key=lambda k: ours[k]["ms_total"])
+    roofline = {"bound": "hbm", "kernel": top, "achieved": ours[top]["gbs"], "peak": peak, "peak_kind": peak_kind,
+                "unit": "GB/s", "frac": ours[top]["gbs"] / peak,
+                "bytes_per_launch": ours[top]["bytes_per_launch"], "us_per_launch": ours[top]["us_per_launch"],
+                "traffic": NCU_TRAFFIC_BYTES.get(top)}
+
+    total_seqs = B * args.steps * WORLD
+    line = {
+        "metric": METRIC, "value": total_seqs / (dev_ms * 1e-3), "unit": UNIT, "n_gpus": WORLD,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "BERT-base (12 layers, hidden 768, 12 heads, intermediate 3072, vocab 21128) "
+                               "forward, seq_length 128, batch 256 per GPU, valid length U[8,128], outputs "
+                               "sequence_output + pooled_output",
+                   "storage": "binary16 weights and activations", "arithmetic": "float32 accumulate",
+                   "global_batch": B * WORLD, "seq_len": S, "parallelism": "replica per GPU, no collective",
+                   "seed": WORKLOAD["seed"], "l2": L2_NOTE, "per_kernel_events": "on during the timed region"},
+        "e2e": {"value": total_seqs / e2e_s, "unit": UNIT, "ms_per_step": 1e3 * e2e_s / args.steps,
+                "h2d_bytes_per_step": int(B * S * 6), "d2h_bytes_per_step": int(B * S * H * 2 + B * H * 2),
+                "outputs_finite": ok},
+        "gpu_launches": int(launches),
+        "roofline": roofline,
+        "kernels": kernels,
+        "clocks": clocks,
+    }
+
+    # ---- CPU baseline beside it (N = 1 only): bounded sample on this machine's host cores
+    if WORLD == 1 and not args.no_cpu_baseline:
+        try:
+            var32 = {k: v.astype(np.float32) for k, v in var16.items()}
+            rate, kind, cores, sec = cpu_reference_rate(cfg, var32, S, 32, WORKLOAD["lengths"], WORKLOAD["seed"], 3, 1)
+            line["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": cores, "kind": kind,
+                                    "sample": "32 sequences of the batch per step, float32 (the reference's CPU "
+                                              "build has no binary16), 1 warm-up + 3 timed steps, %.2f s/step" % sec}
+        except Exception as e:  # the baseline must not take the benchmark down
+            line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "unavailable",
+                                    "sample": repr(e)}
+    print(json.dumps(line), flush=True)
+    m.close()
+    if WORLD > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

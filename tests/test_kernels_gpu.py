@@ -243,17 +243,31 @@ def test_masked_softmax(oracle, t, kind, batch, heads, seq):
     scale = 0.125 if kind != "none" else 1.0
     if seq > 512:
         # The reference sums a row sequentially in float32; for rows this long that sum is itself off
-        # by more than 1e-5 (n * eps / 2 systematic rounding). Judge long rows against float64.
+        # by more than 1e-5 (n * eps / 2 systematic rounding). Judge long rows against float64 (with
+        # the masked score rounded to float32 once, as the kernel's fused multiply-add does).
         v = scale * xh.astype(np.float64)
         if mask is not None:
             v = v + np.where(mask[:, None, None, :] == 0, -10000.0, 0.0)
+        v = v.astype(np.float32).astype(np.float64)
         ev = np.exp(v - v.max(axis=-1, keepdims=True))
         ref = ev / ev.sum(axis=-1, keepdims=True)
     else:
         ref = oracle.masked_softmax(xh, mask, scale)
     got = G.masked_softmax(x.view(-1, seq), None if mask is None else G.dev(mask), seq * heads, scale, t)
+    got4 = got.view(batch, seq, heads, seq)
+    first = 0
+    if kind == "empty_row":
+        # Sequence 0 has every key masked: all scores sit near -10000, where float32 resolves only
+        # 1e-3, so each probability carries a relative error of that order and whether the score was
+        # rounded once (fused multiply-add) or twice decides single elements. The reference's own
+        # backends differ from each other here; hold the degenerate sequence to 2e-3 instead.
+        r0 = G.host(got4[:1])
+        G.assert_close(r0, ref[:1], 2e-3, 1e-4, "softmax fully masked sequence")
+        assert np.allclose(r0.sum(-1), 1.0, atol=2e-3)
+        first = 1
     # probabilities: relative to max(|p|, 1e-4) -- a masked key is exactly 0 on both sides
-    _check(got.view(batch, seq, heads, seq), ref, t, 1e-4 if t == "f32" else 1e-1, "softmax " + kind)
+    if batch > first:
+        _check(got4[first:], ref[first:], t, 1e-4 if t == "f32" else 1e-1, "softmax " + kind)
     if kind == "prefix":
         p = G.host(got).reshape(batch, seq, heads, seq)
         assert np.all(p[np.broadcast_to(mask[:, None, None, :] == 0, p.shape)] == 0)
@@ -350,7 +364,14 @@ def test_logits_probs(oracle, t, batch, hidden, labels, bias):
     logits, probs = G.logits_probs(x, w, b, t)
     ref_logits, ref_probs = oracle.classifier(xh, wh, bh)
     _check(logits, ref_logits, t, 1.0, "logits")
-    _check(probs, ref_probs, t, 1e-3 if t == "f32" else 1e-1, "probs")
+    if t == "f32":
+        _check(probs, ref_probs, t, 1e-3, "probs")
+    else:
+        # As in the reference, the softmax reads the logits back in storage precision
+        # (src/cuBERT/op_out/AdditionalOutputLayer.cpp:61-64): probs must be the softmax of the
+        # binary16 logits we stored, and within the 1e-2 bar of the float32 oracle.
+        _check(probs, oracle.softmax_(G.host(logits)), t, 1e-1, "probs of stored logits")
+        assert np.max(np.abs(G.host(probs) - ref_probs)) <= G.F16_ATOL
 
 
 # ============================================================================ helpers and argument checking

@@ -186,6 +186,44 @@ int mean_pool(const T *x, int batch, int seq, int hidden, T *out, void *scratch,
     return check_launch();
 }
 
+// ------------------------------------------------------------------ K5b without any allocation
+// Some hosts of this library are not allowed to call cudaMalloc at all: code that runs inside a
+// region where the CUDA allocator is off limits (a real-time serving loop that forbids calls which
+// may take the driver's global lock, a plug-in whose host owns every byte of device memory, a
+// sandbox that filters allocation calls). For them the split-sequence mean pool is offered with its
+// float32 partial sums in a fixed array that is part of the library image: every GPU that loads the
+// library sets aside kStaticPoolScratchBytes until the process exits.
+constexpr size_t kStaticPoolScratchBytes = CUBK_STATIC_POOL_SCRATCH_BYTES;  // 512 KiB = 131072 partial sums
+static __device__ __align__(256) float g_static_pool_scratch[kStaticPoolScratchBytes / sizeof(float)];
+
+// In host code `g_static_pool_scratch` is only a handle for the runtime, not a device address;
+// the address a kernel can use comes from cudaGetSymbolAddress, asked once per device with that
+// device current. Entries are written once (racing threads store the same value).
+static void *g_static_pool_scratch_addr[kMaxDevices] = {nullptr};
+
+static int static_pool_scratch(void **addr) {
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) {
+        set_last_error(err);
+        return CUBK_ERR_LAUNCH;
+    }
+    if (device < 0 || device >= kMaxDevices) {
+        return CUBK_ERR_UNSUPPORTED;
+    }
+    if (g_static_pool_scratch_addr[device] == nullptr) {
+        void *p = nullptr;
+        err = cudaGetSymbolAddress(&p, g_static_pool_scratch);
+        if (err != cudaSuccess || p == nullptr) {
+            set_last_error(err);
+            return CUBK_ERR_LAUNCH;
+        }
+        g_static_pool_scratch_addr[device] = p;
+    }
+    *addr = g_static_pool_scratch_addr[device];
+    return CUBK_OK;
+}
+
 // ------------------------------------------------------------------ K5c classifier head
 // One 128-thread block per sequence. Warp w computes logits w, w+4, ... as dot products with
 // coalesced strided reads (the [labels, hidden] weights stay in L2 across blocks); logits
@@ -334,6 +372,31 @@ int cubk_mean_pool_f16(const void *x, int batch, int seq, int hidden, void *out,
                        size_t scratch_bytes, void *stream) {
     return cubk::mean_pool<__half>((const __half *) x, batch, seq, hidden, (__half *) out, scratch, scratch_bytes,
                                    (cudaStream_t) stream);
+}
+
+int cubk_mean_pool_static_scratch(const void *x, int elem_bytes, int batch, int seq, int hidden, void *out,
+                                  void *stream) {
+    if (elem_bytes != 2 && elem_bytes != 4) {
+        return CUBK_ERR_INVALID_ARG;
+    }
+    const size_t need = elem_bytes == 4 ? cubk::mean_pool_scratch_bytes<float>(batch, seq, hidden)
+                                        : cubk::mean_pool_scratch_bytes<__half>(batch, seq, hidden);
+    if (need > cubk::kStaticPoolScratchBytes) {
+        return CUBK_ERR_SCRATCH;  // the shape needs more partial sums than the built-in array holds
+    }
+    void *scratch = nullptr;
+    if (need > 0) {
+        const int rc = cubk::static_pool_scratch(&scratch);
+        if (rc != CUBK_OK) {
+            return rc;
+        }
+    }
+    if (elem_bytes == 4) {
+        return cubk::mean_pool<float>((const float *) x, batch, seq, hidden, (float *) out, scratch,
+                                      cubk::kStaticPoolScratchBytes, (cudaStream_t) stream);
+    }
+    return cubk::mean_pool<__half>((const __half *) x, batch, seq, hidden, (__half *) out, scratch,
+                                   cubk::kStaticPoolScratchBytes, (cudaStream_t) stream);
 }
 
 int cubk_logits_probs_f32(const float *pooled, const float *weights, const float *bias, int batch, int hidden,

@@ -18,6 +18,7 @@ CUBK_ERR_INVALID_ARG = -1
 CUBK_ERR_UNSUPPORTED = -2
 CUBK_ERR_LAUNCH = -3
 CUBK_ERR_SCRATCH = -4
+STATIC_POOL_SCRATCH_BYTES = 512 * 1024
 STATUS_BAD_TOKEN_ID = 1
 STATUS_BAD_SEGMENT_ID = 2
 
@@ -40,6 +41,7 @@ _SIGNATURES = {
     "cubk_bias_tanh_{t}": (_I, [_P, _P, _L, _I, _P, _P]),
     "cubk_mean_pool_scratch_bytes": (_Z, [_I, _I, _I]),
     "cubk_mean_pool_{t}": (_I, [_P, _I, _I, _I, _P, _P, _Z, _P]),
+    "cubk_mean_pool_static_scratch": (_I, [_P, _I, _I, _I, _I, _P, _P]),
     "cubk_logits_probs_{t}": (_I, [_P, _P, _P, _I, _I, _I, _P, _P, _P]),
     "cubk_not_{t}": (_I, [_P, _P, _L, _P]),
     "cubk_half_to_float": (_I, [_P, _P, _L, _P]),

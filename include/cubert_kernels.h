@@ -131,6 +131,25 @@ int cubk_mean_pool_f32(const float *x, int batch, int seq, int hidden, float *ou
 int cubk_mean_pool_f16(const void *x, int batch, int seq, int hidden, void *out,
                        void *scratch, size_t scratch_bytes, void *stream);
 
+/* Mean pooling for callers that must not allocate device memory. No counterpart in the reference.
+ * Same result as cubk_mean_pool_f32 / _f16 (elem_bytes 4 / 2), but the float32 partial sums of the
+ * split-sequence path live in a 512 KiB array built into the library (reserved on every GPU that loads
+ * it, until the process exits) instead of a caller-provided scratch buffer, and the call performs no
+ * cudaMalloc, cudaFree or other allocating call. For hosts where allocation is off limits on the
+ * calling path: latency-critical serving loops that ban calls which can take the driver's allocation
+ * lock, plug-ins whose host process owns all device memory, sandboxes that filter allocator calls.
+ *   - Shapes whose partial sums exceed the array (more than CUBK_STATIC_POOL_SCRATCH_BYTES; e.g.
+ *     binary16 [70, 512, 1024] needs 560 KiB) are refused with CUBK_ERR_SCRATCH before anything runs.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array. It keeps whatever the previous call left; that is
+ *     harmless because every partial sum is written before it is read, so nothing needs clearing.
+ *     Two calls whose kernels can overlap on the GPU (different streams, no ordering between them)
+ *     race on it: order them on one stream or with events. */
+#define CUBK_STATIC_POOL_SCRATCH_BYTES (512u * 1024u)
+int cubk_mean_pool_static_scratch(const void *x, int elem_bytes, int batch, int seq, int hidden, void *out,
+                                  void *stream);
+
 /* ---- K5c: classifier head ---------------------------------------------------------------------
  * logits[b,l] = sum_c pooled[b,c] * weights[l,c] (+ bias[l]);  probs[b,:] = softmax(logits[b,:])
  * Replaces ClassifierOutputLayer<T>::_pre_compute/_in_compute

@@ -74,6 +74,7 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
     CUDA_CHECK(cudaSetDevice(device_));
     CUDA_CHECK(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
     blas_.reset(new Blas(stream_));
+    use_graphs_ = env_int("CUBERT_CUDA_GRAPH", 1) != 0;
 
     const bool half = Storage<T>::is_half;
     algo_attention_ = gemm_algo_from_env("GEMM_ALGO_ATTENTION", half);
@@ -209,6 +210,11 @@ Bert<T>::~Bert() {
     if (stream_ != nullptr) {
         cudaStreamSynchronize(stream_);
     }
+    for (auto &kv : graphs_) {
+        if (kv.second.exec != nullptr) {
+            cudaGraphExecDestroy(kv.second.exec);
+        }
+    }
     for (cudaEvent_t e : event_pool_) {
         cudaEventDestroy(e);
     }
@@ -301,7 +307,7 @@ void Bert<T>::compute(size_t batch_size, const int *input_ids, const int8_t *inp
     CUDA_CHECK(cudaMemcpyAsync(ids_.get(), input_ids, sizeof(int32_t) * n, cudaMemcpyHostToDevice, stream_));
     CUDA_CHECK(cudaMemcpyAsync(mask_.get(), input_mask, sizeof(int8_t) * n, cudaMemcpyHostToDevice, stream_));
     CUDA_CHECK(cudaMemcpyAsync(segments_.get(), segment_ids, sizeof(int8_t) * n, cudaMemcpyHostToDevice, stream_));
-    forward(batch_size, ids_.template as<int32_t>(), mask_.template as<int8_t>(), segments_.template as<int8_t>());
+    run(batch_size, ids_.template as<int32_t>(), mask_.template as<int8_t>(), segments_.template as<int8_t>());
 }
 
 template <typename T>
@@ -316,7 +322,73 @@ void Bert<T>::compute_device(size_t batch_size, const int32_t *d_ids, const int8
         throw std::invalid_argument("null input");
     }
     CUDA_CHECK(cudaSetDevice(device_));
-    forward(batch_size, d_ids, d_mask, d_segments);
+    run(batch_size, d_ids, d_mask, d_segments);
+}
+
+constexpr size_t kMaxCachedGraphs = 64;
+
+template <typename T>
+void Bert<T>::run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments) {
+    if (!use_graphs_ || profiling_) {
+        forward(batch_size, d_ids, d_mask, d_segments);
+        return;
+    }
+    const GraphKey key{batch_size, d_ids, d_mask, d_segments};
+    auto it = graphs_.find(key);
+    if (it == graphs_.end()) {
+        if (graphs_.size() >= kMaxCachedGraphs) {
+            forward(batch_size, d_ids, d_mask, d_segments);
+            return;
+        }
+        it = graphs_.emplace(key, GraphEntry()).first;
+    }
+    GraphEntry &g = it->second;
+    if (g.exec != nullptr) {
+        // the launch counters keep counting what the graph replays
+        launches_[CUBERT_B200_K_EMBED_LN] += 1;
+        launches_[CUBERT_B200_K_BIAS_RESIDUAL_LN] += 2 * (int64_t) num_hidden_layers;
+        launches_[CUBERT_B200_K_BIAS_GELU] += (int64_t) num_hidden_layers;
+        launches_[CUBERT_B200_K_MASKED_SOFTMAX] += (int64_t) num_hidden_layers;
+        launches_[has_pooler_dense_ ? CUBERT_B200_K_BIAS_TANH : CUBERT_B200_K_MEAN_POOL] += 1;
+        if (has_classifier_) {
+            launches_[CUBERT_B200_K_LOGITS_PROBS] += 1;
+        }
+        launches_[CUBERT_B200_K_GEMM] += 6 * (int64_t) num_hidden_layers + (has_pooler_dense_ ? 1 : 0);
+        CUDA_CHECK(cudaGraphLaunch(g.exec, stream_));
+        return;
+    }
+    g.seen += 1;
+    if (g.seen == 1) {
+        // first call with this shape: run eagerly (cuBLASLt picks its algorithms, occupancy is queried)
+        forward(batch_size, d_ids, d_mask, d_segments);
+        return;
+    }
+    const auto saved_launches = launches_;
+    const auto saved_bytes = bytes_;
+    cudaGraph_t graph = nullptr;
+    CUDA_CHECK(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
+    try {
+        forward(batch_size, d_ids, d_mask, d_segments);
+    } catch (...) {
+        cudaStreamEndCapture(stream_, &graph);
+        if (graph != nullptr) {
+            cudaGraphDestroy(graph);
+        }
+        throw;
+    }
+    CUDA_CHECK(cudaStreamEndCapture(stream_, &graph));
+    launches_ = saved_launches;  // capturing launched nothing
+    bytes_ = saved_bytes;
+    cudaError_t err = cudaGraphInstantiate(&g.exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (err != cudaSuccess) {
+        g.exec = nullptr;
+        use_graphs_ = false;  // fall back to plain launches for good
+        (void) cudaGetLastError();
+        forward(batch_size, d_ids, d_mask, d_segments);
+        return;
+    }
+    run(batch_size, d_ids, d_mask, d_segments);
 }
 
 template <typename T>

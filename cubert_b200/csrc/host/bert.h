@@ -13,6 +13,8 @@
 #pragma once
 
 #include <array>
+#include <map>
+#include <tuple>
 #include <memory>
 #include <string>
 #include <unordered_map>
@@ -72,6 +74,25 @@ private:
     };
 
     void forward(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments);
+
+    // The forward pass as a CUDA graph, captured on first use per (batch size, input addresses) and
+    // replayed afterwards: about 125 kernel launches collapse into one graph launch, which removes
+    // the per-launch gaps that dominate small batches. Off while per-kernel timing is on, or with
+    // the environment variable CUBERT_CUDA_GRAPH=0.
+    void run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments);
+    struct GraphKey {
+        size_t batch;
+        const void *ids, *mask, *segments;
+        bool operator<(const GraphKey &o) const {
+            return std::tie(batch, ids, mask, segments) < std::tie(o.batch, o.ids, o.mask, o.segments);
+        }
+    };
+    struct GraphEntry {
+        cudaGraphExec_t exec = nullptr;
+        int seen = 0;  // calls with this key so far; the first runs eagerly, the second captures
+    };
+    std::map<GraphKey, GraphEntry> graphs_;
+    bool use_graphs_ = true;
 
     // profiling: brackets one launch with events when enabled, always counts
     struct Scope;

@@ -144,14 +144,6 @@ bias_residual_ln_kernel(const T *x, const T *bias, const T *residual, const T *g
     Param<T, PERSISTENT> p_gamma{s_params, gamma};
     Param<T, PERSISTENT> p_beta{s_params + (EPV / 4) * nvec, beta};
     Param<T, PERSISTENT> p_bias{s_params + 2 * (EPV / 4) * nvec, bias};
-    if (PERSISTENT) {
-        stage_param<T>(gamma, s_params, nvec, threadIdx.x, BLOCK);
-        stage_param<T>(beta, s_params + (EPV / 4) * nvec, nvec, threadIdx.x, BLOCK);
-        if (bias != nullptr) {
-            stage_param<T>(bias, s_params + 2 * (EPV / 4) * nvec, nvec, threadIdx.x, BLOCK);
-        }
-        __syncthreads();
-    }
 
     const int lane = threadIdx.x % TPR;
     const int group = threadIdx.x / TPR;
@@ -172,9 +164,18 @@ bias_residual_ln_kernel(const T *x, const T *bias, const T *residual, const T *g
         }
     };
 
+    // The first row's loads go out before the parameters are staged, so that the two latencies overlap.
     int64_t first = (int64_t) blockIdx.x * GROUPS;
     if (first < rows) {
         issue_loads(first + group);
+    }
+    if (PERSISTENT) {
+        stage_param<T>(gamma, s_params, nvec, threadIdx.x, BLOCK);
+        stage_param<T>(beta, s_params + (EPV / 4) * nvec, nvec, threadIdx.x, BLOCK);
+        if (bias != nullptr) {
+            stage_param<T>(bias, s_params + 2 * (EPV / 4) * nvec, nvec, threadIdx.x, BLOCK);
+        }
+        __syncthreads();
     }
     for (; first < rows; first += stride) {
         const int64_t row = first + group;
@@ -226,40 +227,53 @@ embed_ln_kernel(const int32_t *ids, const int8_t *segment_ids, const T *word, co
     __shared__ float red[BLOCK / 32];
     Param<T, true> p_gamma{s_params, gamma};
     Param<T, true> p_beta{s_params + (EPV / 4) * nvec, beta};
-    stage_param<T>(gamma, s_params, nvec, threadIdx.x, BLOCK);
-    stage_param<T>(beta, s_params + (EPV / 4) * nvec, nvec, threadIdx.x, BLOCK);
-    __syncthreads();
 
     const int lane = threadIdx.x % TPR;
     const int group = threadIdx.x / TPR;
     const uint32_t stride = gridDim.x * GROUPS;
-    for (uint32_t first = blockIdx.x * GROUPS; first < tokens; first += stride) {
-        const uint32_t token = first + group;
-        const bool active = token < tokens;
 
-        int id = 0, seg = 0;
-        uint32_t s = 0;
-        if (active) {
+    // The token's indices are fetched one step ahead of the row loads that depend on them, which
+    // takes one of the two serial memory latencies (index, then table rows) off every step. The row
+    // loads themselves are not prefetched: their registers would halve the number of resident warps,
+    // and this gather runs out of L2, where many warps hide latency better than a deeper pipeline.
+    int id = 0, seg = 0;
+    auto fetch_indices = [&](uint32_t token) {
+        id = 0;
+        seg = 0;
+        if (token < tokens) {
             id = ids[token];
             seg = segment_ids[token];
-            s = token - fast_div(token, seq_div) * seq_div.div;
+        }
+    };
+
+    uint32_t first = blockIdx.x * GROUPS;
+    fetch_indices(first + group);
+    stage_param<T>(gamma, s_params, nvec, threadIdx.x, BLOCK);
+    stage_param<T>(beta, s_params + (EPV / 4) * nvec, nvec, threadIdx.x, BLOCK);
+    __syncthreads();
+
+    for (; first < tokens; first += stride) {
+        const uint32_t token = first + group;
+        const bool active = token < tokens;
+        int wid = id, tid = seg;
+        if (active) {
             uint32_t bad = 0;
-            if (id < 0 || id >= vocab) {
+            if (wid < 0 || wid >= vocab) {
                 bad |= CUBK_STATUS_BAD_TOKEN_ID;
-                id = min(max(id, 0), vocab - 1);
+                wid = min(max(wid, 0), vocab - 1);
             }
-            if (seg < 0 || seg >= type_vocab) {
+            if (tid < 0 || tid >= type_vocab) {
                 bad |= CUBK_STATUS_BAD_SEGMENT_ID;
-                seg = min(max(seg, 0), type_vocab - 1);
+                tid = min(max(tid, 0), type_vocab - 1);
             }
             if (bad != 0 && status != nullptr && lane == 0) {
                 atomicOr(status, bad);
             }
         }
-
-        const T *wrow = word + (size_t) id * hidden;
+        const uint32_t s = active ? token - fast_div(token, seq_div) * seq_div.div : 0;
+        const T *wrow = word + (size_t) wid * hidden;
         const T *prow = pos + (size_t) s * hidden;
-        const T *trow = type + (size_t) seg * hidden;
+        const T *trow = type + (size_t) tid * hidden;
 
         uint4 rw[VPT], rp[VPT], rt[VPT];
 #pragma unroll
@@ -270,6 +284,7 @@ embed_ln_kernel(const int32_t *ids, const int8_t *segment_ids, const T *word, co
             rp[k] = ok ? ld_param(prow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
             rt[k] = ok ? ld_param(trow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
         }
+        fetch_indices(token + stride);  // for the next step
 
         float2 v[VPT][PAIRS];
 #pragma unroll

@@ -242,11 +242,11 @@ int masked_softmax(const T *scores, const int8_t *mask, int64_t rows, int64_t ro
         } else if (nvec <= 8) {
             LAUNCH(8, 1, 4);
         } else if (nvec <= 16) {
-            LAUNCH(16, 1, 4);
+            LAUNCH(4, 4, 1);  // fewer lanes per row: 2 shuffle steps per reduction instead of 4
         } else if (nvec <= 32) {
             LAUNCH(32, 1, 4);
         } else if (nvec <= 64) {
-            LAUNCH(32, 2, 2);
+            LAUNCH(16, 4, 1);
         } else if (nvec <= 128) {
             LAUNCH(32, 4, 1);
         } else {

@@ -194,7 +194,7 @@ def case_pool(t, batch, seq, hidden, iters):
 def run(only=None, dtypes=("f16", "f32"), quick=False, iters=20):
     kernels.load()
     peak, peak_kind = measured_peak_gbs()
-    rows_list = [4096, 65536] if quick else [4096, 65536, 1048576]
+    rows_list = [4096, 65536] if quick else [4096, 32768, 65536, 1048576]
     results = []
 
     def want(k):

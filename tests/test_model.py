@@ -282,7 +282,7 @@ def test_concurrent_callers_are_serialised_per_replica(model_files):
     (src/cuBERT/BertM.cpp:69-76 locks the chosen replica)."""
     path, cfg, var = model_files["tiny"]
     g = golden("tiny")
-    ids, mask, seg = g["ids"], g["mask"], g["seg"]
+    ids, mask, seg, want = g["ids"], g["mask"], g["seg"], g["probs"]  # read the archive before threading
     m = model.Model(path, 8, ids.shape[1], cfg["layers"], cfg["heads"])
     errors = []
 
@@ -292,8 +292,8 @@ def test_concurrent_callers_are_serialised_per_replica(model_files):
                 n = 1 + (k % ids.shape[0])
                 out = np.zeros((n, 3), np.float32)
                 m.compute(ids[:n].copy(), mask[:n].copy(), seg[:n].copy(), out, model.OutputType.PROBS)
-                if rel_err(out, g["probs"][:n]) > 1e-5:
-                    errors.append((k, rel_err(out, g["probs"][:n])))
+                if rel_err(out, want[:n]) > 1e-5:
+                    errors.append((k, rel_err(out, want[:n])))
         except Exception as e:  # pragma: no cover
             errors.append((k, repr(e)))
 

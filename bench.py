@@ -224,24 +224,18 @@ def run_ours(args):
     if WORLD > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", 0))
 
+    from cubert_b200 import replicas
+
     def barrier():
         if WORLD > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
     def max_over_ranks(x):
-        if WORLD == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return replicas.max_over_ranks(x, "cuda")
 
     def sum_over_ranks(x):
-        if WORLD == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        return float(t.item())
+        return replicas.sum_over_ranks(x, "cuda")
 
     cfg = synthetic.config(WORKLOAD["model"])
     B, S, H = WORKLOAD["batch"], WORKLOAD["seq"], cfg["hidden"]
@@ -251,7 +245,7 @@ def run_ours(args):
     assert m.info["replicas"] == 1, "one replica per process expected, got %d" % m.info["replicas"]
 
     # every rank works on its own batch of the seeded stream
-    ids, mask, seg, lens = synthetic.random_inputs(cfg, B, S, WORKLOAD["seed"] + 1000 * RANK,
+    ids, mask, seg, lens = synthetic.random_inputs(cfg, B, S, replicas.stream_seed(WORKLOAD["seed"], RANK),
                                                    lengths=WORKLOAD["lengths"])
     pin = lambda a: torch.from_numpy(a).pin_memory()  # noqa: E731
     h_ids, h_mask, h_seg = pin(ids), pin(mask), pin(seg)

@@ -151,9 +151,16 @@ def cpu_reference_rate(cfg, var32, seq, sample_batch, lengths, seed, steps, warm
     from oracle import bindings
     geo = synthetic.model_geometry(cfg, seq)
     ids, mask, seg, _ = synthetic.random_inputs(cfg, sample_batch, seq, seed, lengths=lengths)
-    cores = os.cpu_count() or 1
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    # All the host threads there are: launchers such as torchrun pin OMP_NUM_THREADS to 1 for their
+    # children, which would time a single-threaded reference. CUBERT_BENCH_CPU_THREADS overrides.
+    cores = int(os.environ.get("CUBERT_BENCH_CPU_THREADS", "0")) or len(os.sched_getaffinity(0)) or 1
+    os.environ["OMP_NUM_THREADS"] = str(cores)
     os.environ.setdefault("KMP_BLOCKTIME", "0")  # as the reference's README recommends
+    try:  # an OpenMP runtime that is already loaded has read the variable; tell it directly as well
+        import ctypes
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(cores)
+    except OSError:
+        pass
     times = []
     if os.path.exists(bindings.REF_CPU_SO):
         kind = "reference"

@@ -18,6 +18,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "liboracle.so")
 REF_CPU_SO = os.path.join(HERE, "_ref", "libcubert_ref_cpu.so")
+REF_GPU_SO = os.path.join(HERE, "_ref", "libcubert_ref_gpu.so")
 
 LAYER_TENSORS = [
     "attention/self/query/kernel", "attention/self/query/bias",
@@ -33,7 +34,7 @@ LAYER_TENSORS = [
 
 def build(ref=False):
     """Compile the checkers (idempotent; make decides what is stale)."""
-    targets = ["oracle"] + (["ref"] if ref else [])
+    targets = ["oracle"] + (["ref", "ref_gpu"] if ref else [])
     subprocess.run(["make", "-C", HERE] + targets, check=True, stdout=subprocess.DEVNULL)
 
 
@@ -400,3 +401,26 @@ class Reference:
             return self.bert_output(h, ids.shape[0], cfg, "output_weights" in var)
         finally:
             self.bert_close(h)
+
+
+class ReferenceGPU:
+    """The reference's own CUDA operator bodies compiled for sm_100a (oracle/_ref). Every pointer is a
+    raw device address; raises FileNotFoundError if the library was not built."""
+
+    def __init__(self):
+        if not os.path.exists(REF_GPU_SO):
+            raise FileNotFoundError(REF_GPU_SO)
+        self.lib = C.CDLL(REF_GPU_SO)
+        P, I, Z = C.c_void_p, C.c_int, C.c_size_t
+        for t in ("f32", "f16"):
+            getattr(self.lib, "refgpu_layer_norm_" + t).argtypes = [P, P, I, I, P, P, P, P, P]
+            getattr(self.lib, "refgpu_softmax_" + t).argtypes = [P, P, I, I, P, P]
+            getattr(self.lib, "refgpu_gelu_" + t).argtypes = [Z, P, P]
+            getattr(self.lib, "refgpu_embedding_i32_" + t).argtypes = [P, I, P, I, P, P]
+            getattr(self.lib, "refgpu_embedding_i8_" + t).argtypes = [P, I, P, I, P, P]
+            getattr(self.lib, "refgpu_not_" + t).argtypes = [P, P, I, P]
+            getattr(self.lib, "refgpu_tanh_" + t).argtypes = [P, I, P]
+            getattr(self.lib, "refgpu_reduce_mean_1_" + t).argtypes = [P, P, I, I, I, P]
+
+    def fn(self, name, t):
+        return getattr(self.lib, "refgpu_%s_%s" % (name, t))

@@ -1,0 +1,156 @@
+"""Our kernels against the reference's own CUDA kernels compiled for sm_100a (oracle/_ref), on the
+same device buffers: parity (this is the binary16 reference, the reference's CPU path has no half)
+and a side-by-side timing of the non-GEMM work of one encoder layer at the benchmark's shapes.
+
+The reference spreads that work over many launches and device copies; the comparison below runs
+the same sequence it does (op_att/AttentionSelf.cpp:96-111, op_att/Transformer.cpp:145-175,
+op/Dense.cpp:41-45): broadcast-mask copy + softmax, two LayerNorms, GELU, and the six bias refills.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import gpu_harness as G
+from cubert_b200 import kernels
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def refgpu():
+    from oracle import bindings
+    if not os.path.exists(bindings.REF_GPU_SO):
+        pytest.skip("oracle/_ref/libcubert_ref_gpu.so not built (reference tree absent at build time)")
+    return bindings.ReferenceGPU()
+
+
+def S():
+    return torch.cuda.current_stream().cuda_stream
+
+
+@pytest.mark.parametrize("t,tol", [("f32", 2e-5), ("f16", 1e-2)])
+def test_parity_with_reference_gpu_kernels(refgpu, t, tol):
+    dt = G.TORCH_DTYPE[t]
+    g = torch.Generator(device="cuda").manual_seed(3)
+    rows, ch = 512, 768
+    x = torch.randn((rows, ch), device="cuda", generator=g).to(dt)
+    r = torch.randn((rows, ch), device="cuda", generator=g).to(dt)
+    gamma = (1 + 0.1 * torch.randn(ch, device="cuda", generator=g)).to(dt)
+    beta = (0.1 * torch.randn(ch, device="cuda", generator=g)).to(dt)
+    # LayerNorm(in = r, inout = x)
+    ref = x.clone()
+    mean = torch.empty(rows, device="cuda", dtype=dt)
+    var = torch.empty(rows, device="cuda", dtype=dt)
+    refgpu.fn("layer_norm", t)(r.data_ptr(), ref.data_ptr(), rows, ch, mean.data_ptr(), var.data_ptr(),
+                               beta.data_ptr(), gamma.data_ptr(), S())
+    ours = G.bias_residual_ln(x, None, r, gamma, beta, t)
+    assert (ours.float() - ref.float()).abs().max().item() <= tol * 4  # outputs are O(4)
+    # GELU
+    ref = (x * 2).clone()
+    refgpu.fn("gelu", t)(ref.numel(), ref.data_ptr(), S())
+    ours = G.bias_gelu((x * 2).contiguous(), None, t)
+    assert (ours.float() - ref.float()).abs().max().item() <= tol * 4
+    # softmax over rows of 128 (no mask: the reference kernel has none)
+    sc = (torch.randn((1536, 128), device="cuda", generator=g) * 3).to(dt)
+    ref = torch.empty_like(sc)
+    ssum = torch.empty(1536, device="cuda", dtype=dt)
+    refgpu.fn("softmax", t)(sc.clone().data_ptr(), ref.data_ptr(), 1536, 128, ssum.data_ptr(), S())
+    ours = G.masked_softmax(sc, None, 1536, 1.0, t)
+    assert (ours.float() - ref.float()).abs().max().item() <= tol
+    # gather: bit-exact
+    table = torch.randn((1000, ch), device="cuda", generator=g).to(dt)
+    ids = torch.randint(0, 1000, (777,), device="cuda", generator=g, dtype=torch.int32)
+    ref = torch.empty((777, ch), device="cuda", dtype=dt)
+    refgpu.fn("embedding_i32", t)(ids.data_ptr(), 777, table.data_ptr(), ch, ref.data_ptr(), S())
+    assert torch.equal(G.embed_gather(ids, table), ref)
+    # tanh, mean pool, not
+    ref = x[:64].clone()
+    refgpu.fn("tanh", t)(ref.data_ptr(), ref.numel(), S())
+    assert (G.bias_tanh(x[:64].contiguous(), None, t).float() - ref.float()).abs().max().item() <= tol
+    x3 = torch.randn((8, 128, ch), device="cuda", generator=g).to(dt)
+    ref = torch.empty((8, ch), device="cuda", dtype=dt)
+    refgpu.fn("reduce_mean_1", t)(x3.data_ptr(), ref.data_ptr(), 8, 128, ch, S())
+    assert (G.mean_pool(x3, t).float() - ref.float()).abs().max().item() <= tol
+    m = torch.randint(0, 2, (4096,), device="cuda", generator=g).to(torch.int8)
+    ref = torch.empty(4096, device="cuda", dtype=dt)
+    refgpu.fn("not", t)(m.data_ptr(), ref.data_ptr(), 4096, S())
+    assert torch.equal(G.logical_not(m, t), ref)
+    torch.cuda.synchronize()
+
+
+def _time(fn, iters=20, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters * 1e3  # microseconds
+
+
+@pytest.mark.parametrize("t", ["f16", "f32"])
+def test_one_layer_of_non_gemm_work_against_the_reference_kernels(refgpu, t):
+    """BERT-base, batch 256, seq 128: time per encoder layer spent outside the GEMMs."""
+    dt = G.TORCH_DTYPE[t]
+    B, Sq, H, I, heads = 256, 128, 768, 3072, 12
+    R = B * Sq
+    g = torch.Generator(device="cuda").manual_seed(4)
+    lib = kernels.load()
+    scores = (torch.randn((R * heads, Sq), device="cuda", generator=g) * 3).to(dt)
+    negmask = torch.zeros((R * heads, Sq), device="cuda", dtype=dt)       # the reference's broadcast mask tensor
+    mask = torch.ones((B, Sq), device="cuda", dtype=torch.int8)
+    hid = torch.randn((R, H), device="cuda", generator=g).to(dt)
+    res = torch.randn((R, H), device="cuda", generator=g).to(dt)
+    inter = torch.randn((R, I), device="cuda", generator=g).to(dt)
+    bias_h = torch.randn(H, device="cuda", generator=g).to(dt)
+    bias_i = torch.randn(I, device="cuda", generator=g).to(dt)
+    gamma, beta = torch.ones(H, device="cuda", dtype=dt), torch.zeros(H, device="cuda", dtype=dt)
+    rep_h = bias_h.repeat(R, 1).contiguous()                               # replicated bias buffers (op/Dense.cpp:22-25)
+    rep_i = bias_i.repeat(R, 1).contiguous()
+    q = torch.empty((R, H), device="cuda", dtype=dt)
+    mean, var = torch.empty(R, device="cuda", dtype=dt), torch.empty(R, device="cuda", dtype=dt)
+    ssum = torch.empty(R * heads, device="cuda", dtype=dt)
+    out_h = torch.empty((R, H), device="cuda", dtype=dt)
+
+    def reference_layer():
+        s = S()
+        scores.copy_(negmask)                                             # AttentionSelf.cpp:99-101
+        refgpu.fn("softmax", t)(scores.data_ptr(), scores.data_ptr(), R * heads, Sq, ssum.data_ptr(), s)
+        refgpu.fn("layer_norm", t)(res.data_ptr(), hid.data_ptr(), R, H, mean.data_ptr(), var.data_ptr(),
+                                   beta.data_ptr(), gamma.data_ptr(), s)
+        refgpu.fn("gelu", t)(inter.numel(), inter.data_ptr(), s)
+        refgpu.fn("layer_norm", t)(res.data_ptr(), hid.data_ptr(), R, H, mean.data_ptr(), var.data_ptr(),
+                                   beta.data_ptr(), gamma.data_ptr(), s)
+        for _ in range(3):                                                # Q, K, V bias refill (Dense::_pre_compute)
+            q.copy_(rep_h)
+        out_h.copy_(rep_h)                                                # attention-output bias refill
+        inter.copy_(rep_i)                                                # intermediate bias refill
+        out_h.copy_(rep_h)                                                # output bias refill
+
+    def our_layer():
+        s = S()
+        kernels.check(G.fn("masked_softmax", t)(scores.data_ptr(), mask.data_ptr(), R * heads, Sq * heads, Sq, 1.0,
+                                                scores.data_ptr(), s))
+        kernels.check(G.fn("bias_residual_ln", t)(hid.data_ptr(), bias_h.data_ptr(), res.data_ptr(), gamma.data_ptr(),
+                                                  beta.data_ptr(), R, H, out_h.data_ptr(), s))
+        kernels.check(G.fn("bias_gelu", t)(inter.data_ptr(), bias_i.data_ptr(), R, I, inter.data_ptr(), s))
+        kernels.check(G.fn("bias_residual_ln", t)(hid.data_ptr(), bias_h.data_ptr(), res.data_ptr(), gamma.data_ptr(),
+                                                  beta.data_ptr(), R, H, out_h.data_ptr(), s))
+
+    ref_us = _time(reference_layer)
+    inter.normal_(generator=g)  # GELU applied 23 times in place has flattened it; refresh
+    our_us = _time(our_layer)
+    line = dict(dtype=t, shape="BERT-base B=256 S=128", reference_us_per_layer=ref_us, ours_us_per_layer=our_us,
+                speedup=ref_us / our_us)
+    print("\\nnon-GEMM work per encoder layer:", json.dumps(line))
+    out_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
+    if os.path.isdir(out_dir):
+        with open(os.path.join(out_dir, "vs_reference_kernels_%s.json" % t), "w") as f:
+            json.dump(line, f)
+    assert lib is not None and our_us < ref_us, line

@@ -112,7 +112,7 @@ private:
     DeviceBuffer pooler_kernel_, pooler_bias_, output_weights_, output_bias_;
 
     // inputs and activations (shared by all layers)
-    DeviceBuffer ids_, mask_, segments_, status_;
+    DeviceBuffer ids_, mask_, segments_, status_, calibration_;
     DeviceBuffer embedding_, hidden_[2], qkv_, scores_, context_, dense_out_, att_out_, inter_;
     DeviceBuffer pooled_, logits_, probs_, pool_scratch_, float_staging_;
     DeviceBuffer q_ptrs_, k_ptrs_, v_ptrs_, score_ptrs_, ctx_ptrs_;

@@ -215,11 +215,16 @@ bias_residual_ln_kernel(const T *x, const T *bias, const T *residual, const T *g
 }
 
 // ------------------------------------------------------------------ K1
+// Tokens are walked position-major (j = s * batch + b): every row group takes a contiguous run of j,
+// so the position s it works on changes at most a few times and the position row stays in registers
+// as float32 across the run. Per token that leaves one gathered word row (from L2: the table is a
+// few tens of MB), one token-type row (L1) and the output row. Token indices are fetched one step
+// ahead of the row loads that depend on them.
 template <typename T, int TPR, int VPT, int BLOCK>
 __global__ void __launch_bounds__(BLOCK)
 embed_ln_kernel(const int32_t *ids, const int8_t *segment_ids, const T *word, const T *pos, const T *type,
-                const T *gamma, const T *beta, T *out, uint32_t tokens, FastDiv seq_div, int hidden, int nvec,
-                int vocab, int type_vocab, uint32_t *status) {
+                const T *gamma, const T *beta, T *out, uint32_t tokens, FastDiv batch_div, int seq, int hidden,
+                int nvec, int vocab, int type_vocab, uint32_t *status) {
     constexpr int EPV = Vec<T>::EPV;
     constexpr int PAIRS = Vec2<T>::PAIRS;
     constexpr int GROUPS = BLOCK / TPR;
@@ -230,31 +235,46 @@ embed_ln_kernel(const int32_t *ids, const int8_t *segment_ids, const T *word, co
 
     const int lane = threadIdx.x % TPR;
     const int group = threadIdx.x / TPR;
-    const uint32_t stride = gridDim.x * GROUPS;
 
-    // The token's indices are fetched one step ahead of the row loads that depend on them, which
-    // takes one of the two serial memory latencies (index, then table rows) off every step. The row
-    // loads themselves are not prefetched: their registers would halve the number of resident warps,
-    // and this gather runs out of L2, where many warps hide latency better than a deeper pipeline.
+    // even split of the position-major index range over all row groups of the grid
+    const uint32_t total_groups = gridDim.x * GROUPS;
+    const uint32_t g = blockIdx.x * GROUPS + group;
+    const uint32_t share = tokens / total_groups;
+    const uint32_t extra = tokens - share * total_groups;
+    const uint32_t j_begin = g * share + min(g, extra);
+    const uint32_t j_count = share + (g < extra ? 1u : 0u);
+    // a row that spans the block needs every thread in every step: iterate to the longest run
+    const uint32_t steps = TPR == BLOCK ? share + (extra > 0 ? 1u : 0u) : j_count;
+
+    auto token_of = [&](uint32_t j, uint32_t &s) {
+        s = fast_div(j, batch_div);
+        return (j - s * batch_div.div) * (uint32_t) seq + s;
+    };
+
     int id = 0, seg = 0;
-    auto fetch_indices = [&](uint32_t token) {
+    auto fetch_indices = [&](uint32_t step) {
         id = 0;
         seg = 0;
-        if (token < tokens) {
+        if (step < j_count) {
+            uint32_t s;
+            const uint32_t token = token_of(j_begin + step, s);
             id = ids[token];
             seg = segment_ids[token];
         }
     };
 
-    uint32_t first = blockIdx.x * GROUPS;
-    fetch_indices(first + group);
+    fetch_indices(0);
     stage_param<T>(gamma, s_params, nvec, threadIdx.x, BLOCK);
     stage_param<T>(beta, s_params + (EPV / 4) * nvec, nvec, threadIdx.x, BLOCK);
     __syncthreads();
 
-    for (; first < tokens; first += stride) {
-        const uint32_t token = first + group;
-        const bool active = token < tokens;
+    float2 pos_row[VPT][PAIRS];
+    uint32_t cur_s = 0xffffffffu;
+
+    for (uint32_t step = 0; step < steps; ++step) {
+        const bool active = step < j_count;
+        uint32_t s = 0;
+        const uint32_t token = active ? token_of(j_begin + step, s) : 0;
         int wid = id, tid = seg;
         if (active) {
             uint32_t bad = 0;
@@ -270,37 +290,43 @@ embed_ln_kernel(const int32_t *ids, const int8_t *segment_ids, const T *word, co
                 atomicOr(status, bad);
             }
         }
-        const uint32_t s = active ? token - fast_div(token, seq_div) * seq_div.div : 0;
         const T *wrow = word + (size_t) wid * hidden;
-        const T *prow = pos + (size_t) s * hidden;
         const T *trow = type + (size_t) tid * hidden;
 
-        uint4 rw[VPT], rp[VPT], rt[VPT];
+        uint4 rw[VPT], rt[VPT];
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
             const int idx = lane + k * TPR;
             const bool ok = active && idx < nvec;
             rw[k] = ok ? ld_param(wrow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
-            rp[k] = ok ? ld_param(prow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
             rt[k] = ok ? ld_param(trow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
         }
-        fetch_indices(token + stride);  // for the next step
+        if (active && s != cur_s) {  // uniform within a row group
+            cur_s = s;
+            const T *prow = pos + (size_t) s * hidden;
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                const int idx = lane + k * TPR;
+                const uint4 raw = idx < nvec ? ld_param(prow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
+                Vec2<T>::unpack(raw, pos_row[k]);
+            }
+        }
+        fetch_indices(step + 1);
 
         float2 v[VPT][PAIRS];
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
-            float2 p[PAIRS], t[PAIRS];
+            float2 t[PAIRS];
             Vec2<T>::unpack(rw[k], v[k]);
-            Vec2<T>::unpack(rp[k], p);
             Vec2<T>::unpack(rt[k], t);
 #pragma unroll
             for (int e = 0; e < PAIRS; ++e) {
-                v[k][e] = add2(add2(v[k][e], p[e]), t[e]);  // (word + pos) + type, the reference's order
+                v[k][e] = add2(add2(v[k][e], pos_row[k][e]), t[e]);  // (word + pos) + type, the reference's order
             }
         }
 
         normalise_store<T, TPR, VPT, BLOCK, true>(v, lane, nvec, hidden, active, p_gamma, p_beta,
-                                                  out + (size_t) token * (active ? hidden : 0), red);
+                                                  out + (size_t) token * hidden, red);
     }
 }
 
@@ -458,7 +484,7 @@ int embed_ln(const int32_t *ids, const int8_t *segment_ids, const T *word, const
                         aligned16(beta) && aligned16(out);
     if (vec_ok) {
         const int nvec = hidden / EPV;
-        const FastDiv seq_div = make_fastdiv((uint32_t) seq);
+        const FastDiv batch_div = make_fastdiv((uint32_t) batch);
 #define LAUNCH(TPR, VPT, BLOCK, PERSISTENT)                                                           \
     {                                                                                                 \
         static OccupancyCache cache;                                                                  \
@@ -467,8 +493,9 @@ int embed_ln(const int32_t *ids, const int8_t *segment_ids, const T *word, const
         const int resident = resident_blocks(kernel, BLOCK, smem, &cache);                            \
         if (grid > resident) grid = resident;                                                         \
         kernel<<<(unsigned) grid, BLOCK, smem, stream>>>(ids, segment_ids, word, pos, type, gamma,    \
-                                                          beta, out, (uint32_t) tokens, seq_div,      \
-                                                          hidden, nvec, vocab, type_vocab, status);   \
+                                                          beta, out, (uint32_t) tokens, batch_div,    \
+                                                          seq, hidden, nvec, vocab, type_vocab,       \
+                                                          status);                                    \
     }
         CUBK_LN_DISPATCH(nvec, LAUNCH);
 #undef LAUNCH

@@ -20,7 +20,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 HOST_LIB = os.path.join(HERE, "lib", "libcuBERT.so")
 
 K_NAMES = ["embed_ln", "bias_residual_ln", "bias_gelu", "masked_softmax", "bias_tanh", "mean_pool",
-           "logits_probs", "half_to_float", "gemm"]
+           "logits_probs", "half_to_float", "gemm", "event_overhead"]
 
 
 class ComputeType:

@@ -32,10 +32,18 @@ LAYER_TENSORS = [
 ]
 
 
+# Where the reference's sources are looked for (the same default as oracle/Makefile's REF).
+REFERENCE_SRC = os.environ.get("CUBERT_REFERENCE_SRC", os.path.join(os.sep, "root", "reference", "src"))
+
+
+def reference_tree_present():
+    return os.path.isdir(os.path.join(REFERENCE_SRC, "cuBERT"))
+
+
 def build(ref=False):
     """Compile the checkers (idempotent; make decides what is stale)."""
     targets = ["oracle"] + (["ref", "ref_gpu"] if ref else [])
-    subprocess.run(["make", "-C", HERE] + targets, check=True, stdout=subprocess.DEVNULL)
+    subprocess.run(["make", "-C", HERE, "REF=" + REFERENCE_SRC] + targets, check=True, stdout=subprocess.DEVNULL)
 
 
 def _f32(a):

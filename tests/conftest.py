@@ -49,7 +49,7 @@ def reference_cpu():
     """The reference's own CPU code, where oracle/_ref could be built."""
     from oracle import bindings
     if not os.path.exists(bindings.REF_CPU_SO):
-        if os.path.isdir("/root/reference/src"):
+        if bindings.reference_tree_present():
             bindings.build(ref=True)
         else:
             pytest.skip("oracle/_ref not built (reference tree absent)")

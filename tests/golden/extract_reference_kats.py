@@ -6,7 +6,7 @@ or run) and writes tests/golden/reference_kats.json:
 
     { "<file>::<test name>": {
           "arrays": {name: [numbers...]},          # every initialised array in the test
-          "expect": [[out_index, value, tol|null]] # EXPECT_NEAR / EXPECT_FLOAT_EQ on out[i]
+          "expect": [[array, index, value, tol|null]] # EXPECT_NEAR / EXPECT_FLOAT_EQ on array[index]
       }, ...,
       "<file>::<globals>": {"arrays": {...}}       # file-scope arrays (TransformerTest weights)
     }
@@ -14,7 +14,7 @@ or run) and writes tests/golden/reference_kats.json:
 The reference tree is only present in the build container, so the JSON is committed
 and the tests read the JSON, never the reference.
 
-Usage: python tests/golden/extract_reference_kats.py [/root/reference]
+Usage: python tests/golden/extract_reference_kats.py [<reference checkout>]
 """
 import json
 import math
@@ -97,7 +97,7 @@ def parse_block(text):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.sep, "root", "reference")
     root = os.path.join(ref, "test", "cuBERT")
     out = {}
     for rel in FILES:

@@ -149,8 +149,8 @@ def test_one_layer_of_non_gemm_work_against_the_reference_kernels(refgpu, t):
     line = dict(dtype=t, shape="BERT-base B=256 S=128", reference_us_per_layer=ref_us, ours_us_per_layer=our_us,
                 speedup=ref_us / our_us)
     print("\\nnon-GEMM work per encoder layer:", json.dumps(line))
-    out_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
-    if os.path.isdir(out_dir):
+    out_dir = os.environ.get("CUBERT_TEST_ARTIFACTS", "")  # optional folder for the timing record
+    if out_dir and os.path.isdir(out_dir):
         with open(os.path.join(out_dir, "vs_reference_kernels_%s.json" % t), "w") as f:
             json.dump(line, f)
     assert lib is not None and our_us < ref_us, line

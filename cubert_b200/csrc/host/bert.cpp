@@ -179,6 +179,19 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
     if (half) {
         float_staging_.allocate(sizeof(float) * R * H);
     }
+    // Rows of the [batch, seq] buffers that a padding-skipping pass never writes must still hold
+    // finite numbers (the attention products multiply them by an exact 0).
+    CUDA_CHECK(cudaMemset(qkv_.get(), 0, qkv_.bytes()));
+    CUDA_CHECK(cudaMemset(context_.get(), 0, context_.bytes()));
+    skip_padding_ = has_pooler_dense_ && env_int("CUBERT_SKIP_PADDING", 1) != 0;
+    if (skip_padding_) {
+        CUDA_CHECK(cudaMallocHost(reinterpret_cast<void **>(&h_token_index_), sizeof(int32_t) * (R + B)));
+        token_index_.allocate(sizeof(int32_t) * R);
+        first_index_.allocate(sizeof(int32_t) * B);
+        qkv_packed_.allocate(sizeof(T) * R * 3 * H);
+        ctx_packed_.allocate(sizeof(T) * R * H);
+        first_rows_.allocate(sizeof(T) * B * H);
+    }
 
     // ---- pointer arrays of the batched attention products, one entry per (sequence, head).
     // Layouts follow src/cuBERT/op_att/BatchMatMul.h:10-14: Q/K/V [B, S, heads, d] (here the three
@@ -224,6 +237,9 @@ Bert<T>::~Bert() {
         cudaEventDestroy(t.stop);
     }
     blas_.reset();
+    if (h_token_index_ != nullptr) {
+        cudaFreeHost(h_token_index_);
+    }
     if (stream_ != nullptr) {
         cudaStreamDestroy(stream_);
     }
@@ -292,9 +308,40 @@ void Bert<T>::profile_read(cubert_b200_profile *out) {
 }
 
 // ------------------------------------------------------------------ forward pass
+// Packed list of the tokens a padding-skipping pass works on; returns its (rounded) length, or 0
+// when skipping would not pay (less than a fifth of the positions is padding).
+template <typename T>
+size_t Bert<T>::build_token_index(size_t batch_size, const int8_t *input_mask) {
+    const size_t S = seq_length, R = batch_size * S;
+    int32_t *list = h_token_index_;
+    int32_t *first = h_token_index_ + max_batch_size * S;
+    size_t n = 0;
+    for (size_t b = 0; b < batch_size; ++b) {
+        first[b] = (int32_t) n;  // position 0 is always kept: the pooler reads it
+        list[n++] = (int32_t) (b * S);
+        const int8_t *m = input_mask + b * S;
+        for (size_t s = 1; s < S; ++s) {
+            if (m[s] != 0) {
+                list[n++] = (int32_t) (b * S + s);
+            }
+        }
+    }
+    size_t padded = (n + 63) / 64 * 64;
+    if (padded > R) {
+        padded = R;
+    }
+    if (padded * 5 > R * 4) {
+        return 0;
+    }
+    for (size_t i = n; i < padded; ++i) {
+        list[i] = list[n - 1];
+    }
+    return padded;
+}
+
 template <typename T>
 void Bert<T>::compute(size_t batch_size, const int *input_ids, const int8_t *input_mask,
-                      const int8_t *segment_ids) {
+                      const int8_t *segment_ids, bool all_positions) {
     if (batch_size > max_batch_size) {
         throw std::invalid_argument("batch_size > max_batch_size");
     } else if (batch_size == 0) {
@@ -308,7 +355,17 @@ void Bert<T>::compute(size_t batch_size, const int *input_ids, const int8_t *inp
     CUDA_CHECK(cudaMemcpyAsync(ids_.get(), input_ids, sizeof(int32_t) * n, cudaMemcpyHostToDevice, stream_));
     CUDA_CHECK(cudaMemcpyAsync(mask_.get(), input_mask, sizeof(int8_t) * n, cudaMemcpyHostToDevice, stream_));
     CUDA_CHECK(cudaMemcpyAsync(segments_.get(), segment_ids, sizeof(int8_t) * n, cudaMemcpyHostToDevice, stream_));
-    run(batch_size, ids_.template as<int32_t>(), mask_.template as<int8_t>(), segments_.template as<int8_t>());
+    size_t packed = 0;
+    if (!all_positions && skip_padding_) {
+        packed = build_token_index(batch_size, input_mask);
+        if (packed > 0) {
+            CUDA_CHECK(cudaMemcpyAsync(token_index_.get(), h_token_index_, sizeof(int32_t) * packed,
+                                       cudaMemcpyHostToDevice, stream_));
+            CUDA_CHECK(cudaMemcpyAsync(first_index_.get(), h_token_index_ + max_batch_size * seq_length,
+                                       sizeof(int32_t) * batch_size, cudaMemcpyHostToDevice, stream_));
+        }
+    }
+    run(batch_size, ids_.template as<int32_t>(), mask_.template as<int8_t>(), segments_.template as<int8_t>(), packed);
 }
 
 template <typename T>
@@ -323,22 +380,23 @@ void Bert<T>::compute_device(size_t batch_size, const int32_t *d_ids, const int8
         throw std::invalid_argument("null input");
     }
     CUDA_CHECK(cudaSetDevice(device_));
-    run(batch_size, d_ids, d_mask, d_segments);
+    run(batch_size, d_ids, d_mask, d_segments, 0);
 }
 
-constexpr size_t kMaxCachedGraphs = 64;
+constexpr size_t kMaxCachedGraphs = 256;
 
 template <typename T>
-void Bert<T>::run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments) {
+void Bert<T>::run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments,
+                  size_t packed) {
     if (!use_graphs_ || profiling_) {
-        forward(batch_size, d_ids, d_mask, d_segments);
+        forward(batch_size, d_ids, d_mask, d_segments, packed);
         return;
     }
-    const GraphKey key{batch_size, d_ids, d_mask, d_segments};
+    const GraphKey key{batch_size, packed, d_ids, d_mask, d_segments};
     auto it = graphs_.find(key);
     if (it == graphs_.end()) {
         if (graphs_.size() >= kMaxCachedGraphs) {
-            forward(batch_size, d_ids, d_mask, d_segments);
+            forward(batch_size, d_ids, d_mask, d_segments, packed);
             return;
         }
         it = graphs_.emplace(key, GraphEntry()).first;
@@ -361,7 +419,7 @@ void Bert<T>::run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask,
     g.seen += 1;
     if (g.seen == 1) {
         // first call with this shape: run eagerly (cuBLASLt picks its algorithms, occupancy is queried)
-        forward(batch_size, d_ids, d_mask, d_segments);
+        forward(batch_size, d_ids, d_mask, d_segments, packed);
         return;
     }
     const auto saved_launches = launches_;
@@ -369,7 +427,7 @@ void Bert<T>::run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask,
     cudaGraph_t graph = nullptr;
     CUDA_CHECK(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
     try {
-        forward(batch_size, d_ids, d_mask, d_segments);
+        forward(batch_size, d_ids, d_mask, d_segments, packed);
     } catch (...) {
         cudaStreamEndCapture(stream_, &graph);
         if (graph != nullptr) {
@@ -386,19 +444,22 @@ void Bert<T>::run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask,
         g.exec = nullptr;
         use_graphs_ = false;  // fall back to plain launches for good
         (void) cudaGetLastError();
-        forward(batch_size, d_ids, d_mask, d_segments);
+        forward(batch_size, d_ids, d_mask, d_segments, packed);
         return;
     }
-    run(batch_size, d_ids, d_mask, d_segments);
+    run(batch_size, d_ids, d_mask, d_segments, packed);
 }
 
 template <typename T>
-void Bert<T>::forward(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments) {
+void Bert<T>::forward(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments,
+                      size_t packed) {
     const int B = (int) batch_size, S = (int) seq_length, H = (int) hidden_size, I = (int) intermediate_size;
     const int heads = (int) num_attention_heads, d = H / heads;
-    const int64_t R = (int64_t) B * S;
+    const int64_t R = (int64_t) B * S;      // rows of the [batch, seq] layout
+    const int64_t N = packed > 0 ? (int64_t) packed : R;  // rows the token-wise steps work on
     const int64_t e = sizeof(T);
     void *st = stream_;
+    const int32_t *tok = token_index_.template as<int32_t>();
 
     // K1: embeddings (src/cuBERT/op_bert/BertEmbeddings.cpp:50-66)
     begin(CUBERT_B200_K_EMBED_LN);
@@ -411,15 +472,25 @@ void Bert<T>::forward(size_t batch_size, const int32_t *d_ids, const int8_t *d_m
     // encoder (src/cuBERT/op_att/Transformer.cpp:145-175, op_att/AttentionSelf.cpp:96-111)
     const float att_scale = (float) (1.0 / std::sqrt((double) d));  // op_att/AttentionSelf.cpp:58-60
     const T *x = embedding_.template as<T>();
+    if (packed > 0) {
+        // gather the kept tokens' embedding rows; layer 0 writes hidden_[0], so they go to hidden_[1]
+        KERNEL_CHECK(cubk_embed_gather_i32(tok, N, embedding_.get(), (int) R, H, (int) e, hidden_[1].get(), nullptr, st));
+        x = hidden_[1].template as<T>();
+    }
     for (size_t l = 0; l < num_hidden_layers; ++l) {
         Layer &L = layers_[l];
         T *y = hidden_[l % 2].template as<T>();
 
         // Q, K, V in one projection with the bias in the GEMM epilogue
+        T *qkv_out = packed > 0 ? qkv_packed_.template as<T>() : qkv_.template as<T>();
         begin(CUBERT_B200_K_GEMM);
-        blas_->gemm_bias<T>(3 * H, (int) R, H, L.qkv_kernel.template as<T>(), 3 * H, x, H, L.qkv_bias.template as<T>(), qkv_.template as<T>(),
+        blas_->gemm_bias<T>(3 * H, (int) N, H, L.qkv_kernel.template as<T>(), 3 * H, x, H, L.qkv_bias.template as<T>(), qkv_out,
                             3 * H);
         end(CUBERT_B200_K_GEMM, 0);
+        if (packed > 0) {
+            // back to [batch, seq] places for the attention products (padding rows keep old, finite values)
+            KERNEL_CHECK(cubk_scatter_rows(tok, N, qkv_out, 3 * H, (int) e, qkv_.get(), (int) R, st));
+        }
 
         // scores[b, i, h, j] = (1/sqrt(d)) * sum_c K[b,j,h,c] * Q[b,i,h,c]   (op_att/BatchMatMul.cpp:57-68)
         begin(CUBERT_B200_K_GEMM);
@@ -442,41 +513,54 @@ void Bert<T>::forward(size_t batch_size, const int32_t *d_ids, const int8_t *d_m
         end(CUBERT_B200_K_GEMM, 0);
 
         // attention output projection, then K2: LayerNorm(dense + bias + layer input)
+        const T *ctx = context_.template as<T>();
+        if (packed > 0) {
+            KERNEL_CHECK(cubk_embed_gather_i32(tok, N, context_.get(), (int) R, H, (int) e, ctx_packed_.get(), nullptr, st));
+            ctx = ctx_packed_.template as<T>();
+        }
         begin(CUBERT_B200_K_GEMM);
-        blas_->gemm<T>(false, false, H, (int) R, H, 1.f, L.att_out_kernel.template as<T>(), H, context_.template as<T>(), H, 0.f,
+        blas_->gemm<T>(false, false, H, (int) N, H, 1.f, L.att_out_kernel.template as<T>(), H, ctx, H, 0.f,
                        dense_out_.template as<T>(), H, algo_attention_);
         end(CUBERT_B200_K_GEMM, 0);
         begin(CUBERT_B200_K_BIAS_RESIDUAL_LN);
         KERNEL_CHECK(K<T>::bias_residual_ln(dense_out_.template as<T>(), L.att_out_bias.template as<T>(), x, L.att_ln_gamma.template as<T>(),
-                                            L.att_ln_beta.template as<T>(), R, H, att_out_.template as<T>(), st));
-        end(CUBERT_B200_K_BIAS_RESIDUAL_LN, 3 * R * H * e + 3 * H * e);
+                                            L.att_ln_beta.template as<T>(), N, H, att_out_.template as<T>(), st));
+        end(CUBERT_B200_K_BIAS_RESIDUAL_LN, 3 * N * H * e + 3 * H * e);
 
         // intermediate projection, then K3: bias + GELU in place
         begin(CUBERT_B200_K_GEMM);
-        blas_->gemm<T>(false, false, I, (int) R, H, 1.f, L.inter_kernel.template as<T>(), I, att_out_.template as<T>(), H, 0.f,
+        blas_->gemm<T>(false, false, I, (int) N, H, 1.f, L.inter_kernel.template as<T>(), I, att_out_.template as<T>(), H, 0.f,
                        inter_.template as<T>(), I, algo_intermediate_);
         end(CUBERT_B200_K_GEMM, 0);
         begin(CUBERT_B200_K_BIAS_GELU);
-        KERNEL_CHECK(K<T>::bias_gelu(inter_.template as<T>(), L.inter_bias.template as<T>(), R, I, inter_.template as<T>(), st));
-        end(CUBERT_B200_K_BIAS_GELU, 2 * R * I * e + I * e);
+        KERNEL_CHECK(K<T>::bias_gelu(inter_.template as<T>(), L.inter_bias.template as<T>(), N, I, inter_.template as<T>(), st));
+        end(CUBERT_B200_K_BIAS_GELU, 2 * N * I * e + I * e);
 
         // output projection, then K2: LayerNorm(dense + bias + attention output)
         begin(CUBERT_B200_K_GEMM);
-        blas_->gemm<T>(false, false, H, (int) R, I, 1.f, L.out_kernel.template as<T>(), H, inter_.template as<T>(), I, 0.f,
+        blas_->gemm<T>(false, false, H, (int) N, I, 1.f, L.out_kernel.template as<T>(), H, inter_.template as<T>(), I, 0.f,
                        dense_out_.template as<T>(), H, algo_output_);
         end(CUBERT_B200_K_GEMM, 0);
         begin(CUBERT_B200_K_BIAS_RESIDUAL_LN);
         KERNEL_CHECK(K<T>::bias_residual_ln(dense_out_.template as<T>(), L.out_bias.template as<T>(), att_out_.template as<T>(),
-                                            L.out_ln_gamma.template as<T>(), L.out_ln_beta.template as<T>(), R, H, y, st));
-        end(CUBERT_B200_K_BIAS_RESIDUAL_LN, 3 * R * H * e + 3 * H * e);
+                                            L.out_ln_gamma.template as<T>(), L.out_ln_beta.template as<T>(), N, H, y, st));
+        end(CUBERT_B200_K_BIAS_RESIDUAL_LN, 3 * N * H * e + 3 * H * e);
 
         x = y;
     }
 
     // pooler (src/cuBERT/op_bert/BertPooler.cpp:62-77,93-96)
     if (has_pooler_dense_) {
+        const T *first = x;       // first token of every sequence: rows S apart, or gathered when packed
+        int first_ld = H * S;
+        if (packed > 0) {
+            KERNEL_CHECK(cubk_embed_gather_i32(first_index_.template as<int32_t>(), B, x, (int) N, H, (int) e,
+                                               first_rows_.get(), nullptr, st));
+            first = first_rows_.template as<T>();
+            first_ld = H;
+        }
         begin(CUBERT_B200_K_GEMM);
-        blas_->gemm<T>(false, false, H, B, H, 1.f, pooler_kernel_.template as<T>(), H, x, H * S, 0.f, pooled_.template as<T>(), H,
+        blas_->gemm<T>(false, false, H, B, H, 1.f, pooler_kernel_.template as<T>(), H, first, first_ld, 0.f, pooled_.template as<T>(), H,
                        algo_pooler_);
         end(CUBERT_B200_K_GEMM, 0);
         begin(CUBERT_B200_K_BIAS_TANH);

@@ -41,7 +41,11 @@ public:
 
     // Host inputs -> device, then the forward pass; asynchronous on the replica's stream.
     // Throws std::invalid_argument when batch_size > max_batch_size; batch_size == 0 is a no-op.
-    void compute(size_t batch_size, const int *input_ids, const int8_t *input_mask, const int8_t *segment_ids);
+    // all_positions = false promises that only pooled_output / logits / probs will be read
+    // afterwards; with the first-token pooler the replica may then skip padding tokens (see
+    // `forward`), which leaves sequence_output and embedding_output undefined for this call.
+    void compute(size_t batch_size, const int *input_ids, const int8_t *input_mask, const int8_t *segment_ids,
+                 bool all_positions = true);
 
     // Forward pass on inputs already in this replica's device memory.
     void compute_device(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments);
@@ -73,18 +77,27 @@ private:
         DeviceBuffer out_ln_gamma, out_ln_beta;
     };
 
-    void forward(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments);
+    // `packed` > 0: padding is skipped. The token-wise GEMMs, LayerNorms and GELU run on a packed list
+    // of `packed` tokens (the positions whose mask is non-zero, plus position 0 of every sequence for
+    // the pooler; rounded up to a multiple of 64 by repeating the last one); only the attention
+    // products and the softmax keep the [batch, seq] layout, with rows scattered in and gathered out.
+    // A masked position never influences an unmasked one (its keys get probability exactly 0), so
+    // pooled_output, logits and probs are the same as in the full computation.
+    void forward(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments,
+                 size_t packed);
 
     // The forward pass as a CUDA graph, captured on first use per (batch size, input addresses) and
     // replayed afterwards: about 125 kernel launches collapse into one graph launch, which removes
     // the per-launch gaps that dominate small batches. Off while per-kernel timing is on, or with
     // the environment variable CUBERT_CUDA_GRAPH=0.
-    void run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments);
+    void run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments,
+             size_t packed);
     struct GraphKey {
-        size_t batch;
+        size_t batch, packed;
         const void *ids, *mask, *segments;
         bool operator<(const GraphKey &o) const {
-            return std::tie(batch, ids, mask, segments) < std::tie(o.batch, o.ids, o.mask, o.segments);
+            return std::tie(batch, packed, ids, mask, segments) <
+                   std::tie(o.batch, o.packed, o.ids, o.mask, o.segments);
         }
     };
     struct GraphEntry {
@@ -116,6 +129,12 @@ private:
     DeviceBuffer embedding_, hidden_[2], qkv_, scores_, context_, dense_out_, att_out_, inter_;
     DeviceBuffer pooled_, logits_, probs_, pool_scratch_, float_staging_;
     DeviceBuffer q_ptrs_, k_ptrs_, v_ptrs_, score_ptrs_, ctx_ptrs_;
+
+    // padding skipping: packed-token index lists (host staging is pinned) and packed buffers
+    bool skip_padding_ = true;
+    int32_t *h_token_index_ = nullptr;   // [max_batch * seq + max_batch]: packed list, then first-token slots
+    DeviceBuffer token_index_, first_index_, qkv_packed_, ctx_packed_, first_rows_;
+    size_t build_token_index(size_t batch_size, const int8_t *input_mask);
     T *sequence_output_ = nullptr;
 
     int algo_attention_, algo_intermediate_, algo_output_, algo_pooler_, algo_qk_, algo_qkv_;

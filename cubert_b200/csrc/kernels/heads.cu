@@ -352,9 +352,57 @@ int embed_gather(const IdT *ids, int64_t n, const void *table, int vocab, int wi
     return check_launch();
 }
 
+// out[idx[i], :] = in[i, :] as a bit copy: the inverse of the gather, used to put the packed rows of
+// the non-padding tokens back into their [batch, seq] places. Rows of `out` that no index names are
+// left as they are. Duplicate indices must carry identical rows.
+__global__ void __launch_bounds__(128)
+scatter_rows_kernel(const int32_t *idx, int64_t n, const unsigned char *in, int row_bytes, unsigned char *out,
+                    int rows_out, int vectorised) {
+    const int lane = threadIdx.x & 31;
+    const int64_t i = (int64_t) blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (i >= n) {
+        return;
+    }
+    const int row = idx[i];
+    if (row < 0 || row >= rows_out) {
+        return;  // never write outside the destination
+    }
+    const unsigned char *src = in + (size_t) i * row_bytes;
+    unsigned char *dst = out + (size_t) row * row_bytes;
+    if (vectorised) {
+        for (int o = lane * 16; o < row_bytes; o += 32 * 16) {
+            st_vec(dst + o, ld_stream(src + o));
+        }
+    } else {
+        for (int o = lane; o < row_bytes; o += 32) {
+            dst[o] = src[o];
+        }
+    }
+}
+
 }  // namespace cubk
 
 extern "C" {
+
+int cubk_scatter_rows(const int32_t *idx, int64_t n, const void *in, int width, int elem_bytes, void *out,
+                      int rows_out, void *stream) {
+    if (idx == nullptr || in == nullptr || out == nullptr || n < 0 || width <= 0 || rows_out <= 0 ||
+        (elem_bytes != 2 && elem_bytes != 4)) {
+        return CUBK_ERR_INVALID_ARG;
+    }
+    if (n == 0) {
+        return CUBK_OK;
+    }
+    const int64_t grid = (n + 3) / 4;
+    if (grid > 0x7fffffffLL) {
+        return CUBK_ERR_UNSUPPORTED;
+    }
+    const int row_bytes = width * elem_bytes;
+    const int vectorised = row_bytes % 16 == 0 && cubk::aligned16(in) && cubk::aligned16(out);
+    cubk::scatter_rows_kernel<<<(unsigned) grid, 128, 0, (cudaStream_t) stream>>>(
+        idx, n, (const unsigned char *) in, row_bytes, (unsigned char *) out, rows_out, vectorised);
+    return cubk::check_launch();
+}
 
 size_t cubk_mean_pool_scratch_bytes(int batch, int seq, int hidden) {
     // The float32 and binary16 kernels split alike for hidden % 8 == 0; take the larger otherwise.

@@ -35,6 +35,7 @@ _SIGNATURES = {
     "cubk_embed_ln_{t}": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P]),
     "cubk_embed_gather_i32": (_I, [_P, _L, _P, _I, _I, _I, _P, _P, _P]),
     "cubk_embed_gather_i8": (_I, [_P, _L, _P, _I, _I, _I, _P, _P, _P]),
+    "cubk_scatter_rows": (_I, [_P, _L, _P, _I, _I, _P, _I, _P]),
     "cubk_bias_residual_ln_{t}": (_I, [_P, _P, _P, _P, _P, _L, _I, _P, _P]),
     "cubk_bias_gelu_{t}": (_I, [_P, _P, _L, _I, _P, _P]),
     "cubk_masked_softmax_{t}": (_I, [_P, _P, _L, _L, _I, _F, _P, _P]),

@@ -73,6 +73,15 @@ int cubk_embed_gather_i32(const int32_t *ids, int64_t n, const void *table, int 
 int cubk_embed_gather_i8(const int8_t *ids, int64_t n, const void *table, int vocab, int width,
                          int elem_bytes, void *out, uint32_t *status, void *stream);
 
+/* Row scatter out[idx[i],:] = in[i,:], bit-exact; the inverse of cubk_embed_gather_i32 (which doubles as
+ * the general row gather out[i,:] = in[idx[i],:]). No counterpart in the reference: the pair moves
+ * activations between the [batch*seq, width] layout and a packed list of the non-padding tokens, so that
+ * the token-wise GEMMs and kernels can skip padding. in [n, width], out [rows_out, width]; rows of out
+ * that no index names keep their contents; out-of-range indices are skipped; duplicate indices must
+ * carry identical rows. elem_bytes is 4 or 2. */
+int cubk_scatter_rows(const int32_t *idx, int64_t n, const void *in, int width, int elem_bytes, void *out,
+                      int rows_out, void *stream);
+
 /* ---- K2: bias + residual + LayerNorm -------------------------------------------------------
  * t = x (+ bias) (+ residual);  out = beta + gamma * (t - mean(t)) / sqrt(var(t) + 1e-12)
  * Replaces layer_norm_<T> (src/cuBERT/op/LayerNorm.h:6-15, op/LayerNorm.cu:11-100) together

@@ -304,3 +304,56 @@ def test_concurrent_callers_are_serialised_per_replica(model_files):
         t.join()
     assert not errors, errors
     m.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ct", [model.ComputeType.FLOAT, model.ComputeType.HALF])
+def test_padding_is_skipped_without_changing_the_results(model_files, oracle, ct):
+    """When only pooled_output / logits / probs are asked for, the library works on the non-padding
+    tokens only. A masked position never influences an unmasked one, so the answers must be those of
+    the full computation -- including masks that are not prefixes and a masked first position."""
+    path, cfg, var = model_files["small"]
+    B, S = 8, 32
+    rng = np.random.default_rng(17)
+    ids, _, seg, _ = synthetic.random_inputs(cfg, B, S, 17, segments="random")
+    mask = np.zeros((B, S), np.int8)
+    for b in range(B):
+        keep = rng.choice(S, size=rng.integers(2, 12), replace=False)
+        mask[b, keep] = rng.integers(1, 5, size=keep.size)      # scattered, any non-zero value
+    mask[3, 0] = 0                                               # first token masked as a key, still pooled
+    mask[5, :] = 0
+    mask[5, 7] = 1
+    dt = np.float32 if ct == model.ComputeType.FLOAT else np.float16
+    m = model.Model(path, B, S, cfg["layers"], cfg["heads"], ct)
+
+    def heads_only():
+        out = model.Output()
+        out.pooled_output = np.zeros((B, cfg["hidden"]), dt)
+        out.logits = np.zeros((B, 2), dt)
+        out.probs = np.zeros((B, 2), dt)
+        m.compute_m(ids, mask, seg, out)
+        return out
+
+    m.profile_read()
+    m.profile_enable(True)
+    packed = heads_only()
+    prof = m.profile_read()
+    m.profile_enable(False)
+    kept = int(np.count_nonzero(mask[:, 1:])) + B
+    rows = (kept + 63) // 64 * 64
+    assert rows < B * S
+    e = 4 if ct == model.ComputeType.FLOAT else 2
+    assert prof["bias_gelu"]["bytes"] == cfg["layers"] * (2 * rows * cfg["intermediate"] * e + cfg["intermediate"] * e)
+
+    full = _run(m, ids, mask, seg, cfg)                         # asks for sequence_output: no skipping
+    tol = 1e-5 if ct == model.ComputeType.FLOAT else 4e-3
+    for k in ("pooled_output", "logits", "probs"):
+        assert rel_err(getattr(packed, k), full[k]) < tol, k
+    again = heads_only()                                         # replayed from the captured graph
+    for k in ("pooled_output", "logits", "probs"):
+        assert np.array_equal(getattr(again, k), getattr(packed, k))
+    if ct == model.ComputeType.FLOAT:
+        ref = oracle.bert_forward(var, synthetic.model_geometry(cfg, S), ids, mask, seg)
+        for k in ("pooled_output", "logits", "probs"):
+            assert rel_err(getattr(packed, k), ref[k]) < 1e-5, k
+    m.close()

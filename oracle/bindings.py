@@ -46,6 +46,21 @@ def build(ref=False):
     subprocess.run(["make", "-C", HERE, "REF=" + REFERENCE_SRC] + targets, check=True, stdout=subprocess.DEVNULL)
 
 
+PYWRAP_DIR = os.path.join(HERE, "_ref", "pywrap")
+
+
+def build_pywrap():
+    """Compile the reference's own Cython wrapper against our libcuBERT.so (needs the reference tree and
+    the native libraries). Returns the folder to put on sys.path, or None where it cannot be built."""
+    import glob
+    if not glob.glob(os.path.join(PYWRAP_DIR, "cuBERT*.so")):
+        if not reference_tree_present():
+            return None
+        subprocess.run(["make", "-C", HERE, "REF=" + REFERENCE_SRC, "ref_pywrap"], check=True,
+                       stdout=subprocess.DEVNULL)
+    return PYWRAP_DIR
+
+
 def _f32(a):
     return np.ascontiguousarray(a, dtype=np.float32)
 

@@ -57,6 +57,21 @@ def reference_cpu():
 
 
 @pytest.fixture(scope="session")
+def reference_python_wrapper():
+    """The reference's own Cython module (python/cuBERT.pyx, unmodified) linked against OUR library."""
+    from cubert_b200 import build as native
+    from oracle import bindings
+    native.build_all(verbose=False)
+    folder = bindings.build_pywrap()
+    if folder is None:
+        pytest.skip("reference wrapper not built (reference tree absent)")
+    if folder not in sys.path:
+        sys.path.insert(0, folder)
+    import cuBERT
+    return cuBERT
+
+
+@pytest.fixture(scope="session")
 def kats():
     with open(os.path.join(ROOT, "tests", "golden", "reference_kats.json")) as f:
         return json.load(f)

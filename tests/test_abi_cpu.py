@@ -4,7 +4,9 @@ import ctypes
 import os
 import re
 
-from cubert_b200 import build, kernels
+import pytest
+
+from cubert_b200 import build, kernels, model
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -35,3 +37,26 @@ def test_kernel_binding_fails_loudly_without_the_library(monkeypatch):
         assert "no CPU fallback" in str(e)
     else:
         raise AssertionError("load() must raise when the CUDA library is missing")
+
+
+def test_host_library_exports_the_reference_api_and_the_additions():
+    build.build_all(verbose=False)
+    lib = ctypes.CDLL(model.HOST_LIB)
+    declared = _declared("cuBERT.h", "cuBERT_") + _declared("cubert_b200.h", "cubert_b200_")
+    assert {"cuBERT_open", "cuBERT_compute", "cuBERT_compute_m", "cuBERT_close", "cuBERT_get_gpu_count",
+            "cuBERT_tokenize_compute"} <= set(declared)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert sorted(model.exported_symbols()) == sorted(set(declared))
+
+
+def test_reference_cython_wrapper_binds_to_this_library(reference_python_wrapper):
+    """python/cuBERT.pyx + python/_cuBERT.pxd + the reference's src/cuBERT.h, compiled unchanged, link
+    and load against our libcuBERT.so; enum values and exception translation come through."""
+    cuBERT = reference_python_wrapper
+    assert cuBERT.get_gpu_count() == model.get_gpu_count()
+    assert (cuBERT.ComputeType.FLOAT, cuBERT.ComputeType.HALF) == (0, 1)
+    assert (cuBERT.OutputType.LOGITS, cuBERT.OutputType.POOLED_OUTPUT, cuBERT.OutputType.SEQUENCE_OUTPUT,
+            cuBERT.OutputType.EMBEDDING_OUTPUT, cuBERT.OutputType.PROBS) == (0, 1, 2, 3, 4)
+    with pytest.raises(ValueError, match="model file not found"):   # std::invalid_argument through `except +`
+        cuBERT.Model("/no/such/model.pb", 8, 32, 12, 12)

@@ -313,7 +313,7 @@ def test_padding_is_skipped_without_changing_the_results(model_files, oracle, ct
     tokens only. A masked position never influences an unmasked one, so the answers must be those of
     the full computation -- including masks that are not prefixes and a masked first position."""
     path, cfg, var = model_files["small"]
-    B, S = 8, 32
+    B, S = 64, 32       # 2048 positions: the smallest request the library packs
     rng = np.random.default_rng(17)
     ids, _, seg, _ = synthetic.random_inputs(cfg, B, S, 17, segments="random")
     mask = np.zeros((B, S), np.int8)
@@ -357,3 +357,25 @@ def test_padding_is_skipped_without_changing_the_results(model_files, oracle, ct
         for k in ("pooled_output", "logits", "probs"):
             assert rel_err(getattr(packed, k), ref[k]) < 1e-5, k
     m.close()
+
+
+@pytest.mark.gpu
+def test_through_the_references_own_python_wrapper(model_files, reference_python_wrapper):
+    """The calls of the reference's python/cuBERT_test.py:35-51, made through its unmodified Cython
+    wrapper, served by this library; checked against the reference CPU build's recorded outputs."""
+    cuBERT = reference_python_wrapper
+    path, cfg, var = model_files["tiny"]
+    g = golden("tiny")
+    ids, mask, seg = g["ids"], g["mask"], g["seg"]
+    b, s = ids.shape
+    m = cuBERT.Model(path, 8, s, cfg["layers"], cfg["heads"], compute_type=cuBERT.ComputeType.FLOAT)
+    output = np.zeros((b, 3), dtype=np.float32, order="C")
+    m.compute(ids, mask, seg, output, output_type=cuBERT.OutputType.LOGITS)
+    assert rel_err(output, g["logits"]) < 1e-5
+    new_output = cuBERT.Output()
+    new_output.logits = np.zeros((b, 3), dtype=np.float32, order="C")
+    new_output.sequence_output = np.zeros((b, s, 64), dtype=np.float32, order="C")
+    m.compute_m(ids, mask, seg, new_output)
+    assert rel_err(new_output.logits, g["logits"]) < 1e-5
+    assert rel_err(new_output.sequence_output, g["sequence_output"]) < 1e-5
+    del m

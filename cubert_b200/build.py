@@ -40,7 +40,7 @@ def _sources(sub):
         return [], []
     files = sorted(os.listdir(d))
     srcs = [os.path.join(d, f) for f in files if f.endswith((".cu", ".cpp"))]
-    hdrs = [os.path.join(d, f) for f in files if f.endswith((".cuh", ".h", ".hpp"))]
+    hdrs = [os.path.join(d, f) for f in files if f.endswith((".cuh", ".h", ".hpp", ".inc"))]
     return srcs, hdrs
 
 

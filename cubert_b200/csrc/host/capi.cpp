@@ -3,10 +3,12 @@
 #include <cstring>
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 #include "bert_m.h"
 #include "cuBERT.h"
 #include "cubert_b200.h"
+#include "tokenizer.h"
 
 using cubert::BertM;
 
@@ -61,6 +63,49 @@ void with_graph(void *graph, int compute_type, F f) {
     }
 }
 
+// Rows of ids / mask / segment ids for a batch of texts (src/cuBERT.cpp:210-243; heap buffers instead
+// of the reference's variable-length stack arrays).
+void encode_batch(void *model, void *tokenizer, int batch_size, const char **text_a, const char **text_b,
+                  int compute_type, std::vector<int> *ids, std::vector<int8_t> *mask, std::vector<int8_t> *seg) {
+    if (tokenizer == nullptr || text_a == nullptr || batch_size < 0) {
+        throw std::invalid_argument("invalid tokenizer arguments");
+    }
+    size_t seq = 0;
+    with_model(model, compute_type, [&](auto *m) { seq = m->seq_length; });
+    const auto *tok = static_cast<const cubert::FullTokenizer *>(tokenizer);
+    ids->assign((size_t) batch_size * seq, 0);
+    mask->assign((size_t) batch_size * seq, 0);
+    seg->assign((size_t) batch_size * seq, 0);
+    for (int b = 0; b < batch_size; ++b) {
+        tok->encode(seq, text_a[b], text_b == nullptr ? nullptr : text_b[b], ids->data() + b * seq,
+                    mask->data() + b * seq, seg->data() + b * seq);
+    }
+}
+
+// Joins tokens with '\n' into a caller buffer; returns false if it does not fit.
+bool join_tokens(const std::vector<std::string> &tokens, char *buffer, size_t buffer_size, int *count) {
+    size_t need = 1;
+    for (const std::string &t : tokens) {
+        need += t.size() + 1;
+    }
+    if (buffer == nullptr || need > buffer_size) {
+        return false;
+    }
+    char *p = buffer;
+    for (size_t i = 0; i < tokens.size(); ++i) {
+        std::memcpy(p, tokens[i].data(), tokens[i].size());
+        p += tokens[i].size();
+        *p++ = i + 1 < tokens.size() ? '\n' : '\0';
+    }
+    if (tokens.empty()) {
+        *p = '\0';
+    }
+    if (count != nullptr) {
+        *count = (int) tokens.size();
+    }
+    return true;
+}
+
 }  // namespace
 
 extern "C" {
@@ -109,23 +154,30 @@ void cuBERT_close(void *model, cuBERT_ComputeType compute_type) {
     with_model(model, compute_type, [&](auto *m) { delete m; });
 }
 
-// The tokenizer (src/cuBERT/tokenization.cpp) is CPU text preprocessing outside this library's
-// path. The symbols exist so that wrappers written against the reference still link; they
-// report that no tokenizer is built in.
-void *cuBERT_open_tokenizer(const char *, int) {
-    throw std::invalid_argument("this build of cuBERT has no tokenizer; pass token ids to cuBERT_compute");
+// Text API (src/cuBERT.cpp:104-280): tokenize on the calling thread, then the ordinary compute.
+void *cuBERT_open_tokenizer(const char *vocab_file, int do_lower_case) {
+    return new cubert::FullTokenizer(vocab_file, do_lower_case != 0);
 }
 
-void cuBERT_close_tokenizer(void *) {}
-
-void cuBERT_tokenize_compute(void *, void *, int, const char **, const char **, void *, cuBERT_OutputType,
-                             cuBERT_ComputeType) {
-    throw std::invalid_argument("this build of cuBERT has no tokenizer; pass token ids to cuBERT_compute");
+void cuBERT_close_tokenizer(void *tokenizer) {
+    delete static_cast<cubert::FullTokenizer *>(tokenizer);
 }
 
-void cuBERT_tokenize_compute_m(void *, void *, int, const char **, const char **, cuBERT_Output *,
-                               cuBERT_ComputeType, int) {
-    throw std::invalid_argument("this build of cuBERT has no tokenizer; pass token ids to cuBERT_compute");
+void cuBERT_tokenize_compute(void *model, void *tokenizer, int batch_size, const char **text_a, const char **text_b,
+                             void *output, cuBERT_OutputType output_type, cuBERT_ComputeType compute_type) {
+    std::vector<int> ids;
+    std::vector<int8_t> mask, seg;
+    encode_batch(model, tokenizer, batch_size, text_a, text_b, compute_type, &ids, &mask, &seg);
+    cuBERT_compute(model, batch_size, ids.data(), mask.data(), seg.data(), output, output_type, compute_type);
+}
+
+void cuBERT_tokenize_compute_m(void *model, void *tokenizer, int batch_size, const char **text_a,
+                               const char **text_b, cuBERT_Output *output, cuBERT_ComputeType compute_type,
+                               int output_to_float) {
+    std::vector<int> ids;
+    std::vector<int8_t> mask, seg;
+    encode_batch(model, tokenizer, batch_size, text_a, text_b, compute_type, &ids, &mask, &seg);
+    cuBERT_compute_m(model, batch_size, ids.data(), mask.data(), seg.data(), output, compute_type, output_to_float);
 }
 
 // ---------------------------------------------------------------- additions (include/cubert_b200.h)
@@ -245,6 +297,58 @@ int cubert_b200_graph_tensor(void *graph, int compute_type, const char *name, co
 
 int cubert_b200_graph_close(void *graph, int compute_type) {
     return guarded([&] { with_graph(graph, compute_type, [&](auto *g) { delete g; }); });
+}
+
+int cubert_b200_open_tokenizer(const char *vocab_file, int do_lower_case, void **tokenizer) {
+    return guarded([&] {
+        if (vocab_file == nullptr || tokenizer == nullptr) {
+            throw std::invalid_argument("null argument");
+        }
+        *tokenizer = cuBERT_open_tokenizer(vocab_file, do_lower_case);
+    });
+}
+
+int cubert_b200_close_tokenizer(void *tokenizer) {
+    return guarded([&] { cuBERT_close_tokenizer(tokenizer); });
+}
+
+int cubert_b200_encode(void *tokenizer, int max_seq_length, const char *text_a, const char *text_b,
+                       int32_t *input_ids, int8_t *input_mask, int8_t *segment_ids) {
+    return guarded([&] {
+        if (tokenizer == nullptr || text_a == nullptr || input_ids == nullptr || input_mask == nullptr ||
+            segment_ids == nullptr || max_seq_length <= 0) {
+            throw std::invalid_argument("invalid argument");
+        }
+        static_cast<const cubert::FullTokenizer *>(tokenizer)->encode((size_t) max_seq_length, text_a, text_b,
+                                                                     input_ids, input_mask, segment_ids);
+    });
+}
+
+int cubert_b200_tokenize(void *tokenizer, const char *text, int do_lower_case, int max_tokens, char *buffer,
+                         size_t buffer_size, int *count) {
+    return guarded([&] {
+        if (text == nullptr || max_tokens <= 0) {
+            throw std::invalid_argument("invalid argument");
+        }
+        std::vector<std::string> tokens;
+        if (tokenizer != nullptr) {
+            static_cast<const cubert::FullTokenizer *>(tokenizer)->tokenize(text, &tokens, (size_t) max_tokens);
+        } else {
+            cubert::BasicTokenizer(do_lower_case != 0).tokenize(text, &tokens, (size_t) max_tokens);
+        }
+        if (!join_tokens(tokens, buffer, buffer_size, count)) {
+            throw std::invalid_argument("token buffer too small");
+        }
+    });
+}
+
+int cubert_b200_tokenize_compute_m(void *model, void *tokenizer, int batch_size, const char **text_a,
+                                   const char **text_b, cuBERT_Output *output, int compute_type,
+                                   int output_to_float) {
+    return guarded([&] {
+        cuBERT_tokenize_compute_m(model, tokenizer, batch_size, text_a, text_b, output,
+                                  (cuBERT_ComputeType) compute_type, output_to_float);
+    });
 }
 
 int cubert_b200_replica_device(void *model, int compute_type, int replica, int *device) {

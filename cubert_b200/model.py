@@ -59,6 +59,8 @@ _REFERENCE_API = ["cuBERT_initialize", "cuBERT_finalize", "cuBERT_get_gpu_count"
 _EXTENSION_API = ["cubert_b200_last_error", "cubert_b200_open", "cubert_b200_compute", "cubert_b200_compute_m",
                   "cubert_b200_close", "cubert_b200_model_info", "cubert_b200_graph_open",
                   "cubert_b200_graph_info", "cubert_b200_graph_tensor", "cubert_b200_graph_close",
+                  "cubert_b200_open_tokenizer", "cubert_b200_close_tokenizer", "cubert_b200_encode",
+                  "cubert_b200_tokenize", "cubert_b200_tokenize_compute_m",
                   "cubert_b200_replica_device",
                   "cubert_b200_replica_stream", "cubert_b200_forward_device", "cubert_b200_device_outputs",
                   "cubert_b200_synchronize", "cubert_b200_profile_enable", "cubert_b200_profile_read"]
@@ -94,6 +96,13 @@ def load():
     lib.cubert_b200_graph_tensor.argtypes = [C.c_void_p, C.c_int, C.c_char_p, C.POINTER(C.c_void_p),
                                              C.POINTER(C.c_int64)]
     lib.cubert_b200_graph_close.argtypes = [C.c_void_p, C.c_int]
+    lib.cubert_b200_open_tokenizer.argtypes = [C.c_char_p, C.c_int, C.POINTER(C.c_void_p)]
+    lib.cubert_b200_close_tokenizer.argtypes = [C.c_void_p]
+    lib.cubert_b200_encode.argtypes = [C.c_void_p, C.c_int, C.c_char_p, C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.cubert_b200_tokenize.argtypes = [C.c_void_p, C.c_char_p, C.c_int, C.c_int, C.c_char_p, C.c_size_t,
+                                         C.POINTER(C.c_int)]
+    lib.cubert_b200_tokenize_compute_m.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_char_p),
+                                                   C.POINTER(C.c_char_p), C.POINTER(_COutput), C.c_int, C.c_int]
     lib.cubert_b200_replica_device.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int)]
     lib.cubert_b200_replica_stream.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]
     lib.cubert_b200_forward_device.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
@@ -144,6 +153,52 @@ class FrozenGraph:
         if self._handle:
             _check(self._lib.cubert_b200_graph_close(self._handle, self._compute_type))
             self._handle = C.c_void_p()
+
+
+def _utf8(text):
+    return text if isinstance(text, bytes) else text.encode("utf8")
+
+
+class Tokenizer:
+    """BERT basic + WordPiece tokenizer of the library (CPU only)."""
+
+    def __init__(self, vocab_file, do_lower_case=True):
+        self._lib = load()
+        self._handle = C.c_void_p()
+        _check(self._lib.cubert_b200_open_tokenizer(_utf8(vocab_file), 1 if do_lower_case else 0,
+                                                    C.byref(self._handle)))
+
+    def close(self):
+        if self._handle:
+            _check(self._lib.cubert_b200_close_tokenizer(self._handle))
+            self._handle = C.c_void_p()
+
+    def tokenize(self, text, max_tokens=1 << 20):
+        return _tokenize(self._handle, text, True, max_tokens)
+
+    def encode(self, text_a, text_b, max_seq_length):
+        ids = np.zeros(max_seq_length, np.int32)
+        mask = np.zeros(max_seq_length, np.int8)
+        seg = np.zeros(max_seq_length, np.int8)
+        _check(self._lib.cubert_b200_encode(self._handle, max_seq_length, _utf8(text_a),
+                                            None if text_b is None else _utf8(text_b),
+                                            ids.ctypes.data, mask.ctypes.data, seg.ctypes.data))
+        return ids, mask, seg
+
+
+def _tokenize(handle, text, do_lower_case, max_tokens):
+    lib = load()
+    raw = _utf8(text)
+    size = 8 * len(raw) + 64
+    buf = C.create_string_buffer(size)
+    count = C.c_int()
+    _check(lib.cubert_b200_tokenize(handle, raw, 1 if do_lower_case else 0, max_tokens, buf, size, C.byref(count)))
+    return buf.value.decode("utf8").split("\n") if count.value else []
+
+
+def basic_tokenize(text, do_lower_case=True, max_tokens=1 << 20):
+    """The basic tokenizer alone (clean-up, lower-casing, punctuation and CJK splitting)."""
+    return _tokenize(None, text, do_lower_case, max_tokens)
 
 
 class Output:
@@ -222,6 +277,15 @@ class Model:
                                                _input(input_mask, np.int8, "input_mask"),
                                                _input(segment_ids, np.int8, "segment_ids"), C.byref(c),
                                                self._compute_type, 1 if output_to_float else 0))
+
+    def tokenize_compute_m(self, tokenizer, text_a, text_b, output, output_to_float=False):
+        """python/cuBERT.pyx:214-257: tokenise the texts, then compute_m."""
+        n = len(text_a)
+        a = (C.c_char_p * n)(*[_utf8(t) for t in text_a])
+        b = (C.c_char_p * n)(*[_utf8(t) for t in text_b]) if text_b else None
+        c = output._c()
+        _check(self._lib.cubert_b200_tokenize_compute_m(self._handle, tokenizer._handle, n, a, b, C.byref(c),
+                                                        self._compute_type, 1 if output_to_float else 0))
 
     # ---- additions of include/cubert_b200.h -------------------------------------------------
     def forward_device(self, replica, batch, d_ids, d_mask, d_segments):

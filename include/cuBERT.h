@@ -23,8 +23,7 @@
  *
  * Differences: replicas per GPU can be raised with the environment variable
  * CUBERT_NUM_MODELS_PER_GPU (default 1; the GPU twin of the reference's CUBERT_NUM_CPU_MODELS).
- * The tokenizer entry points exist so that wrappers link, but no tokenizer is built in:
- * cuBERT_open_tokenizer and the cuBERT_tokenize_compute* calls throw std::invalid_argument.
+ * The tokenizer needs no utf8proc: its Unicode tables are built in.
  */
 #ifndef CUBERT_LIBRARY_H
 #define CUBERT_LIBRARY_H
@@ -106,7 +105,8 @@ void cuBERT_compute_m(void *model,
                       cuBERT_ComputeType compute_type CUBERT_DEFAULT(cuBERT_COMPUTE_FLOAT),
                       int output_to_float CUBERT_DEFAULT(0));
 
-/* Text API of the reference (src/cuBERT.h:46-60,80-94). Declared for link compatibility only. */
+/* Text API (src/cuBERT.h:46-60,80-94): BERT basic + WordPiece tokenization on the calling thread,
+ * then the forward pass. text_b may be NULL (single sentences). */
 void *cuBERT_open_tokenizer(const char *vocab_file, int do_lower_case CUBERT_DEFAULT(1));
 void cuBERT_close_tokenizer(void *tokenizer);
 void cuBERT_tokenize_compute(void *model, void *tokenizer, int batch_size, const char **text_a,

@@ -62,6 +62,23 @@ int cubert_b200_graph_info(void *graph, int compute_type, struct cubert_b200_inf
 int cubert_b200_graph_tensor(void *graph, int compute_type, const char *name, const void **data, int64_t *count);
 int cubert_b200_graph_close(void *graph, int compute_type);
 
+/* The text front end on its own (CPU only). cubert_b200_open_tokenizer / _close_tokenizer /
+ * _tokenize_compute_m are the status-returning twins of the cuBERT_* tokenizer calls.
+ * cubert_b200_encode turns one text (or a pair, text_b may be NULL) into one row of
+ * input_ids / input_mask / segment_ids of length max_seq_length ([CLS] a [SEP] b [SEP], zero padded).
+ * cubert_b200_tokenize writes the tokens of `text`, separated by '\n' and NUL-terminated, into
+ * `buffer`: WordPiece tokens when `tokenizer` is given, the basic tokenizer's words (with
+ * `do_lower_case`) when it is NULL. */
+int cubert_b200_open_tokenizer(const char *vocab_file, int do_lower_case, void **tokenizer);
+int cubert_b200_close_tokenizer(void *tokenizer);
+int cubert_b200_encode(void *tokenizer, int max_seq_length, const char *text_a, const char *text_b,
+                       int32_t *input_ids, int8_t *input_mask, int8_t *segment_ids);
+int cubert_b200_tokenize(void *tokenizer, const char *text, int do_lower_case, int max_tokens, char *buffer,
+                         size_t buffer_size, int *count);
+int cubert_b200_tokenize_compute_m(void *model, void *tokenizer, int batch_size, const char **text_a,
+                                   const char **text_b, struct cuBERT_Output *output, int compute_type,
+                                   int output_to_float);
+
 /* Device of a replica and the CUDA stream (cudaStream_t) all of its work is enqueued on. */
 int cubert_b200_replica_device(void *model, int compute_type, int replica, int *device);
 int cubert_b200_replica_stream(void *model, int compute_type, int replica, void **stream);

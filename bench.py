@@ -25,6 +25,10 @@ Printed by rank 0 as ONE JSON line:
              timed on this machine's host cores on a bounded sample (N = 1 only)
 
 --impl reference times only that CPU implementation, on the same workload definition.
+
+--workload large_seq512 runs the second full-model case instead (BASELINE config 4): BERT-large,
+binary16 storage, seq_length 512, ONE batch of 512 sequences split evenly over the GPUs ("strong"
+scaling), full masks, mean pooler, output cuBERT_POOLED_OUTPUT, seed 3.
 """
 import argparse
 import json
@@ -42,10 +46,31 @@ RANK = int(os.environ.get("RANK", "0"))
 LOCAL_RANK = int(os.environ.get("LOCAL_RANK", "0"))
 WORLD = int(os.environ.get("WORLD_SIZE", "1"))
 
-WORKLOAD = dict(model="base", seq=128, batch=256, lengths=(8, 128), seed=2)
-METRIC = "BERT-base seq128 seqs/s"
+# base_seq128 is the workload the headline metric is quoted on (per-GPU batch fixed: weak scaling);
+# large_seq512 is the second full-model case: one 512-sequence batch split evenly over the GPUs
+# (strong scaling), mean pooler, pooled_output only.
+WORKLOADS = {
+    # the reference's own published case (README: batch 128, seq 32, float32), BASELINE config 1
+    "base_seq32_f32": dict(model="base", seq=32, batch=128, lengths=None, seed=0, scaling="weak", dtype="f32",
+                           segments="half", outputs=("logits", "probs"), cpu_sample=128,
+                           metric="BERT-base seq32 float32 seqs/s",
+                           text="BERT-base (12 layers, hidden 768, 12 heads, intermediate 3072, vocab 21128, 2 labels) "
+                                "forward, float32, seq_length 32, batch 128 per GPU, full masks, segment 0 for the "
+                                "first 16 positions and 1 after, outputs logits + probs"),
+    "base_seq128": dict(model="base", seq=128, batch=256, lengths=(8, 128), seed=2, scaling="weak",
+                        outputs=("sequence_output", "pooled_output"), metric="BERT-base seq128 seqs/s",
+                        text="BERT-base (12 layers, hidden 768, 12 heads, intermediate 3072, vocab 21128) forward, "
+                             "seq_length 128, batch 256 per GPU, valid length U[8,128], outputs sequence_output + "
+                             "pooled_output"),
+    "large_seq512": dict(model="large", seq=512, batch=512, lengths=None, seed=3, scaling="strong", cpu_sample=4,
+                         outputs=("pooled_output",), metric="BERT-large seq512 seqs/s",
+                         text="BERT-large (24 layers, hidden 1024, 16 heads, intermediate 4096, vocab 30522) forward, "
+                              "seq_length 512, one batch of 512 split evenly over the GPUs, full masks, mean pooler, "
+                              "output pooled_output"),
+}
+WORKLOAD = WORKLOADS["base_seq128"]
 UNIT = "sequences/s"
-L2_NOTE = ("no explicit L2 flush: one step streams 218 MB of weights and >1 GB of activations, "
+L2_NOTE = ("no explicit L2 flush: one step streams the model's weights (218 MB or more) and >1 GB of activations, "
            "far more than the 126 MB L2")
 
 
@@ -196,19 +221,19 @@ def run_reference_arm(args):
     from cubert_b200 import synthetic
     cfg = synthetic.config(WORKLOAD["model"])
     var32 = synthetic.random_weights(cfg, WORKLOAD["seed"])
-    sample = 32
-    rate, kind, cores, sec = cpu_reference_rate(cfg, var32, WORKLOAD["seq"], sample, WORKLOAD["lengths"],
+    sample = WORKLOAD.get("cpu_sample", 32)
+    rate, kind, cores, sec = cpu_reference_rate(cfg, var32, WORKLOAD["seq"], sample, WORKLOAD["lengths"] or "full",
                                                 WORKLOAD["seed"], args.steps, max(1, min(args.warmup, 3)))
     line = {
-        "impl": "reference", "metric": METRIC, "value": rate, "unit": UNIT, "n_gpus": args.gpus,
+        "impl": "reference", "metric": WORKLOAD["metric"], "value": rate, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "BERT-base forward, seq_length 128, float32 on host cores (the reference's CPU "
-                               "build has no binary16), valid length U[8,128]",
+        "scaling": WORKLOAD["scaling"], "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD["text"] + "; float32 on host cores (the reference's CPU build has no "
+                               "binary16)",
                    "sample_batch": sample, "full_batch": WORKLOAD["batch"], "seed": WORKLOAD["seed"]},
         "cpu_baseline": {"value": rate, "unit": UNIT, "cores": cores, "kind": kind,
-                         "sample": "%d sequences per step (of the 256-sequence batch), %d timed steps" %
-                                   (sample, args.steps)},
+                         "sample": "%d sequences per step (of the %d-sequence batch), %d timed steps" %
+                                   (sample, WORKLOAD["batch"], args.steps)},
         "e2e": {"value": rate, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -221,9 +246,10 @@ def run_ours(args):
         os.environ["CUBERT_BENCH_PARENT_VISIBLE"] = os.environ.get("CUDA_VISIBLE_DEVICES", "")
         os.environ["CUDA_VISIBLE_DEVICES"] = str(physical_gpu_index())
     import numpy as np
+    from cubert_b200 import model, synthetic
+    model.load()  # before torch: the process then binds the toolkit's cuBLAS, not the older one torch bundles
     import torch
     import torch.distributed as dist
-    from cubert_b200 import model, synthetic
 
     if not torch.cuda.is_available():
         sys.exit("bench.py needs a CUDA device (there is no CPU fallback)")
@@ -245,23 +271,33 @@ def run_ours(args):
         return replicas.sum_over_ranks(x, "cuda")
 
     cfg = synthetic.config(WORKLOAD["model"])
-    B, S, H = WORKLOAD["batch"], WORKLOAD["seq"], cfg["hidden"]
-    path, var16 = make_model_file(cfg, WORKLOAD["seed"], half=True)
-    m = model.Model(path, B, S, cfg["layers"], cfg["heads"], model.ComputeType.HALF)
+    weak = WORKLOAD["scaling"] == "weak"
+    if not weak and WORKLOAD["batch"] % WORLD != 0:
+        sys.exit("the %d-sequence batch does not split evenly over %d GPUs" % (WORKLOAD["batch"], WORLD))
+    B = WORKLOAD["batch"] if weak else WORKLOAD["batch"] // WORLD   # sequences per GPU and step
+    S, H = WORKLOAD["seq"], cfg["hidden"]
+    half = WORKLOAD.get("dtype", "f16") == "f16"
+    elem = 2 if half else 4
+    path, var16 = make_model_file(cfg, WORKLOAD["seed"], half=half)
+    m = model.Model(path, B, S, cfg["layers"], cfg["heads"],
+                    model.ComputeType.HALF if half else model.ComputeType.FLOAT)
     os.unlink(path)
     assert m.info["replicas"] == 1, "one replica per process expected, got %d" % m.info["replicas"]
 
     # every rank works on its own batch of the seeded stream
     ids, mask, seg, lens = synthetic.random_inputs(cfg, B, S, replicas.stream_seed(WORKLOAD["seed"], RANK),
-                                                   lengths=WORKLOAD["lengths"])
+                                                   lengths=WORKLOAD["lengths"] or "full")
     pin = lambda a: torch.from_numpy(a).pin_memory()  # noqa: E731
     h_ids, h_mask, h_seg = pin(ids), pin(mask), pin(seg)
-    h_seq = torch.empty((B, S, H), dtype=torch.float16).pin_memory()
-    h_pool = torch.empty((B, H), dtype=torch.float16).pin_memory()
     d_ids, d_mask, d_seg = h_ids.cuda(), h_mask.cuda(), h_seg.cuda()
     out = model.Output()
-    out.sequence_output = h_seq.numpy()
-    out.pooled_output = h_pool.numpy()
+    d2h_bytes = 0
+    h_out = {}
+    for name in WORKLOAD["outputs"]:
+        shape = {"sequence_output": (B, S, H), "pooled_output": (B, H)}.get(name, (B, cfg["num_labels"]))
+        h_out[name] = torch.empty(shape, dtype=torch.float16 if half else torch.float32).pin_memory()
+        setattr(out, name, h_out[name].numpy())
+        d2h_bytes += h_out[name].numel() * elem
     np_ids, np_mask, np_seg = h_ids.numpy(), h_mask.numpy(), h_seg.numpy()
     stream = torch.cuda.ExternalStream(m.replica_stream(0))
 
@@ -309,7 +345,7 @@ def run_ours(args):
     e2e_s = time.perf_counter() - t0
     barrier()
     e2e_s = max_over_ranks(e2e_s)
-    ok = bool(np.all(np.isfinite(out.pooled_output.astype(np.float32))))
+    ok = all(bool(np.all(np.isfinite(h.numpy().astype(np.float32)))) for h in h_out.values())
     clocks = sampler.stop() if sampler else None
 
     launches = sum_over_ranks(sum(v["launches"] for k, v in counted.items() if k not in ("gemm", "event_overhead")))
@@ -338,7 +374,8 @@ def run_ours(args):
     roofline = {"bound": "hbm", "kernel": top, "achieved": ours[top]["gbs"], "peak": peak, "peak_kind": peak_kind,
                 "unit": "GB/s", "frac": ours[top]["gbs"] / peak,
                 "bytes_per_launch": ours[top]["bytes_per_launch"], "us_per_launch": ours[top]["us_per_launch"],
-                "traffic": NCU_TRAFFIC_BYTES.get(top), "event_bracket_overhead_us": overhead_us}
+                "traffic": NCU_TRAFFIC_BYTES.get(top) if WORKLOAD is WORKLOADS["base_seq128"] else None,
+                "event_bracket_overhead_us": overhead_us}
     if overhead_us:
         for k, v in ours.items():
             net = v["us_per_launch"] - overhead_us
@@ -348,18 +385,19 @@ def run_ours(args):
 
     total_seqs = B * args.steps * WORLD
     line = {
-        "metric": METRIC, "value": total_seqs / (dev_ms * 1e-3), "unit": UNIT, "n_gpus": WORLD,
+        "metric": WORKLOAD["metric"], "value": total_seqs / (dev_ms * 1e-3), "unit": UNIT, "n_gpus": WORLD,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "BERT-base (12 layers, hidden 768, 12 heads, intermediate 3072, vocab 21128) "
-                               "forward, seq_length 128, batch 256 per GPU, valid length U[8,128], outputs "
-                               "sequence_output + pooled_output",
-                   "storage": "binary16 weights and activations", "arithmetic": "float32 accumulate",
-                   "global_batch": B * WORLD, "seq_len": S, "parallelism": "replica per GPU, no collective",
+        "higher_is_better": True, "scaling": WORKLOAD["scaling"], "vs_baseline": None,
+        "dtype": "f16" if half else "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD["text"],
+                   "storage": ("binary16" if half else "float32") + " weights and activations",
+                   "arithmetic": "float32 accumulate",
+                   "global_batch": B * WORLD, "batch_per_gpu": B, "seq_len": S,
+                   "parallelism": "replica per GPU, no collective",
                    "seed": WORKLOAD["seed"], "l2": L2_NOTE, "per_kernel_events": "second timed region of the same K steps, CUDA events around every "
                                         "launch, graph replay off; ms_per_step there = %.3f" % (prof_ms / args.steps)},
         "e2e": {"value": total_seqs / e2e_s, "unit": UNIT, "ms_per_step": 1e3 * e2e_s / args.steps,
-                "h2d_bytes_per_step": int(B * S * 6), "d2h_bytes_per_step": int(B * S * H * 2 + B * H * 2),
+                "h2d_bytes_per_step": int(B * S * 6), "d2h_bytes_per_step": int(d2h_bytes),
                 "outputs_finite": ok},
         "gpu_launches": int(launches),
         "roofline": roofline,
@@ -371,10 +409,13 @@ def run_ours(args):
     if WORLD == 1 and not args.no_cpu_baseline:
         try:
             var32 = {k: v.astype(np.float32) for k, v in var16.items()}
-            rate, kind, cores, sec = cpu_reference_rate(cfg, var32, S, 32, WORKLOAD["lengths"], WORKLOAD["seed"], 3, 1)
+            sample = WORKLOAD.get("cpu_sample", 32)
+            rate, kind, cores, sec = cpu_reference_rate(cfg, var32, S, sample, WORKLOAD["lengths"] or "full",
+                                                        WORKLOAD["seed"], 3, 1)
             line["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": cores, "kind": kind,
-                                    "sample": "32 sequences of the batch per step, float32 (the reference's CPU "
-                                              "build has no binary16), 1 warm-up + 3 timed steps, %.2f s/step" % sec}
+                                    "sample": "%d sequences of the batch per step, float32 (the reference's CPU "
+                                              "build has no binary16), 1 warm-up + 3 timed steps, %.2f s/step"
+                                              % (sample, sec)}
         except Exception as e:  # the baseline must not take the benchmark down
             line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "unavailable",
                                     "sample": repr(e)}
@@ -391,7 +432,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="base_seq128", choices=sorted(WORKLOADS))
     args = ap.parse_args()
+    global WORKLOAD
+    WORKLOAD = WORKLOADS[args.workload]
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference_arm(args)

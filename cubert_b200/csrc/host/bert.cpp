@@ -73,7 +73,18 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
     }
     CUDA_CHECK(cudaSetDevice(device_));
     CUDA_CHECK(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
-    blas_.reset(new Blas(stream_));
+    {
+        // float32 models: room for the largest product's operands split into three bfloat16 parts each
+        // (weights [hidden x intermediate], activations [max tokens x intermediate]), capped at 4 GB
+        size_t emulation_ws = 0;
+        if (!Storage<T>::is_half) {
+            const size_t widest = intermediate_size > 3 * hidden_size ? intermediate_size : 3 * hidden_size;
+            emulation_ws = 8 * widest * (hidden_size + max_batch_size * seq_length) + (32u << 20);
+            const size_t cap = (size_t) 4 << 30;
+            emulation_ws = emulation_ws > cap ? cap : emulation_ws;
+        }
+        blas_.reset(new Blas(stream_, emulation_ws));
+    }
     use_graphs_ = env_int("CUBERT_CUDA_GRAPH", 1) != 0;
 
     const bool half = Storage<T>::is_half;

@@ -60,6 +60,7 @@ public:
     int device() const { return device_; }
     bool has_classifier() const { return has_classifier_; }
     bool has_pooler_dense() const { return has_pooler_dense_; }
+    bool fp32_gemm_emulation() const { return blas_ && blas_->fp32_emulation(); }
 
     void profile_enable(bool on);
     void profile_read(cubert_b200_profile *out);

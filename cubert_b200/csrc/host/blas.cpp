@@ -16,14 +16,26 @@ int gemm_algo_from_env(const char *env, bool half) {
     return std::atoi(val);
 }
 
-Blas::Blas(cudaStream_t stream) : stream_(stream) {
+Blas::Blas(cudaStream_t stream, size_t fp32_emulation_workspace) : stream_(stream) {
     CUBLAS_CHECK(cublasCreate(&handle_));
     CUBLAS_CHECK(cublasSetStream(handle_, stream_));
     CUBLAS_CHECK(cublasLtCreate(&lt_));
-    workspace_.allocate(kWorkspaceBytes);
-    CUBLAS_CHECK(cublasSetWorkspace(handle_, workspace_.get(), workspace_.bytes()));
     // float32 storage must not be demoted to TF32
     CUBLAS_CHECK(cublasSetMathMode(handle_, CUBLAS_DEFAULT_MATH));
+    size_t bytes = kWorkspaceBytes;
+    if (fp32_emulation_workspace > 0 && env_int("CUBERT_FP32_EMULATION", 1) != 0) {
+        // A cuBLAS older than 12.9 refuses the mode and the products stay on the float32 pipes.
+        fp32_emulation_ = cublasSetMathMode(handle_, CUBLAS_FP32_EMULATED_BF16X9_MATH) == CUBLAS_STATUS_SUCCESS;
+        if (fp32_emulation_ && fp32_emulation_workspace > bytes) {
+            bytes = fp32_emulation_workspace;
+        }
+    }
+    const int ws_mb = env_int("CUBERT_BLAS_WORKSPACE_MB", 0);
+    if (ws_mb > 0) {
+        bytes = (size_t) ws_mb << 20;
+    }
+    workspace_.allocate(bytes);
+    CUBLAS_CHECK(cublasSetWorkspace(handle_, workspace_.get(), workspace_.bytes()));
 }
 
 Blas::~Blas() {
@@ -76,28 +88,45 @@ void Blas::gemm_bias(int m, int n, int k, const T *A, int lda, const T *B, int l
     auto it = plans_.find(key);
     if (it == plans_.end()) {
         LtPlan p;
-        CUBLAS_CHECK(cublasLtMatmulDescCreate(&p.desc, CUBLAS_COMPUTE_32F, CUDA_R_32F));
-        const cublasOperation_t op_n = CUBLAS_OP_N;
-        CUBLAS_CHECK(cublasLtMatmulDescSetAttribute(p.desc, CUBLASLT_MATMUL_DESC_TRANSA, &op_n, sizeof(op_n)));
-        CUBLAS_CHECK(cublasLtMatmulDescSetAttribute(p.desc, CUBLASLT_MATMUL_DESC_TRANSB, &op_n, sizeof(op_n)));
-        const cublasLtEpilogue_t epilogue = CUBLASLT_EPILOGUE_BIAS;
-        CUBLAS_CHECK(
-            cublasLtMatmulDescSetAttribute(p.desc, CUBLASLT_MATMUL_DESC_EPILOGUE, &epilogue, sizeof(epilogue)));
-        CUBLAS_CHECK(cublasLtMatmulDescSetAttribute(p.desc, CUBLASLT_MATMUL_DESC_BIAS_POINTER, &bias, sizeof(bias)));
         CUBLAS_CHECK(cublasLtMatrixLayoutCreate(&p.a, dt, m, k, lda));
         CUBLAS_CHECK(cublasLtMatrixLayoutCreate(&p.b, dt, k, n, ldb));
         CUBLAS_CHECK(cublasLtMatrixLayoutCreate(&p.c, dt, m, n, ldc));
-        cublasLtMatmulPreference_t pref = nullptr;
-        CUBLAS_CHECK(cublasLtMatmulPreferenceCreate(&pref));
-        const size_t ws = workspace_.bytes();
-        CUBLAS_CHECK(
-            cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &ws, sizeof(ws)));
         cublasLtMatmulHeuristicResult_t result;
-        int found = 0;
-        cublasStatus_t st = cublasLtMatmulAlgoGetHeuristic(lt_, p.desc, p.a, p.b, p.c, p.c, pref, 1, &result, &found);
-        cublasLtMatmulPreferenceDestroy(pref);
-        CUBLAS_CHECK(st);
-        if (found == 0) {
+        // the emulated float32 compute type first where it was asked for, plain float32 otherwise or after it
+        const bool try_emulated = fp32_emulation_ && !Storage<T>::is_half;
+        for (int attempt = try_emulated ? 0 : 1; attempt < 2; ++attempt) {
+            const cublasComputeType_t compute = attempt == 0 ? CUBLAS_COMPUTE_32F_EMULATED_16BFX9 : CUBLAS_COMPUTE_32F;
+            if (cublasLtMatmulDescCreate(&p.desc, compute, CUDA_R_32F) != CUBLAS_STATUS_SUCCESS) {
+                p.desc = nullptr;
+                continue;
+            }
+            const cublasOperation_t op_n = CUBLAS_OP_N;
+            CUBLAS_CHECK(cublasLtMatmulDescSetAttribute(p.desc, CUBLASLT_MATMUL_DESC_TRANSA, &op_n, sizeof(op_n)));
+            CUBLAS_CHECK(cublasLtMatmulDescSetAttribute(p.desc, CUBLASLT_MATMUL_DESC_TRANSB, &op_n, sizeof(op_n)));
+            const cublasLtEpilogue_t epilogue = CUBLASLT_EPILOGUE_BIAS;
+            CUBLAS_CHECK(
+                cublasLtMatmulDescSetAttribute(p.desc, CUBLASLT_MATMUL_DESC_EPILOGUE, &epilogue, sizeof(epilogue)));
+            CUBLAS_CHECK(
+                cublasLtMatmulDescSetAttribute(p.desc, CUBLASLT_MATMUL_DESC_BIAS_POINTER, &bias, sizeof(bias)));
+            cublasLtMatmulPreference_t pref = nullptr;
+            CUBLAS_CHECK(cublasLtMatmulPreferenceCreate(&pref));
+            const size_t ws = workspace_.bytes();
+            CUBLAS_CHECK(cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &ws,
+                                                              sizeof(ws)));
+            int found = 0;
+            cublasStatus_t st =
+                cublasLtMatmulAlgoGetHeuristic(lt_, p.desc, p.a, p.b, p.c, p.c, pref, 1, &result, &found);
+            cublasLtMatmulPreferenceDestroy(pref);
+            if (st == CUBLAS_STATUS_SUCCESS && found > 0) {
+                break;
+            }
+            cublasLtMatmulDescDestroy(p.desc);
+            p.desc = nullptr;
+        }
+        if (p.desc == nullptr) {
+            cublasLtMatrixLayoutDestroy(p.a);
+            cublasLtMatrixLayoutDestroy(p.b);
+            cublasLtMatrixLayoutDestroy(p.c);
             throw RuntimeError("cuBLASLt found no algorithm for the biased projection");
         }
         p.algo = result.algo;

@@ -2,8 +2,10 @@
 // not part of the product; this wrapper only fixes conventions:
 //   * column-major BLAS semantics exactly as the reference passes them
 //     (src/cuBERT/common.cpp:224-419), so the layouts documented there carry over;
-//   * float32 accumulation for both storage types; float32 storage computes in true float32
-//     (CUBLAS_COMPUTE_32F, no TF32), as the reference does (CUDA_R_32F compute type);
+//   * float32 accumulation for both storage types; float32 storage computes to float32 accuracy
+//     (CUBLAS_COMPUTE_32F, never TF32), as the reference does (CUDA_R_32F compute type): on the
+//     float32 pipes or, where cuBLAS offers it, as error-free three-way bfloat16 splits on the
+//     tensor cores;
 //   * a fixed workspace, so that no call allocates and all of them can be captured in a graph;
 //   * the reference's GEMM_ALGO_* environment variables still select a cublasGemmAlgo_t
 //     (src/cuBERT/common.cpp:443-469).
@@ -20,7 +22,12 @@ int gemm_algo_from_env(const char *env, bool half);
 
 class Blas {
 public:
-    explicit Blas(cudaStream_t stream);
+    // fp32_emulation_workspace > 0 (float32 models): float32 products may run as nine bfloat16
+    // tensor-core products of operands split three ways (cuBLAS 12.9 "BF16x9", results as accurate as
+    // float32 arithmetic), which needs that much workspace for the split operands. Off with
+    // CUBERT_FP32_EMULATION=0 or an older cuBLAS. CUBERT_BLAS_WORKSPACE_MB overrides the size.
+    explicit Blas(cudaStream_t stream, size_t fp32_emulation_workspace = 0);
+    bool fp32_emulation() const { return fp32_emulation_; }
     ~Blas();
     Blas(const Blas &) = delete;
     Blas &operator=(const Blas &) = delete;
@@ -53,6 +60,7 @@ private:
     cublasHandle_t handle_ = nullptr;
     cublasLtHandle_t lt_ = nullptr;
     DeviceBuffer workspace_;
+    bool fp32_emulation_ = false;
     std::map<LtKey, LtPlan> plans_;
 };
 

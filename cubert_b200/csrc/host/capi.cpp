@@ -247,6 +247,7 @@ int cubert_b200_model_info(void *model, int compute_type, cubert_b200_info *info
             info->num_hidden_layers = (int32_t) b->num_hidden_layers;
             info->num_attention_heads = (int32_t) b->num_attention_heads;
             info->has_pooler_dense = b->has_pooler_dense() ? 1 : 0;
+            info->fp32_gemm_emulation = b->fp32_gemm_emulation() ? 1 : 0;
         });
     });
 }

@@ -32,8 +32,11 @@ struct OccupancyCache {
     size_t smem[kMaxDevices];
 };
 
+// With `opt_in`, the kernel is first allowed all the dynamic shared memory the device offers a
+// block (needed above 48 KB); the limit is the same for every caller, so racing setters agree.
 template <typename Kernel>
-inline int resident_blocks(Kernel kernel, int block_threads, size_t dynamic_smem, OccupancyCache *cache) {
+inline int resident_blocks(Kernel kernel, int block_threads, size_t dynamic_smem, OccupancyCache *cache,
+                           bool opt_in = false) {
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
         (void) cudaGetLastError();
@@ -41,6 +44,17 @@ inline int resident_blocks(Kernel kernel, int block_threads, size_t dynamic_smem
     }
     if (cache->blocks[device] > 0 && cache->smem[device] == dynamic_smem) {
         return cache->blocks[device];
+    }
+    if (opt_in) {
+        int limit = 0;
+        cudaFuncAttributes attr;
+        if (cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess ||
+            cudaFuncGetAttributes(&attr, kernel) != cudaSuccess ||
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 limit - (int) attr.sharedSizeBytes) != cudaSuccess) {
+            (void) cudaGetLastError();
+            return 0;  // the launch would be refused: callers fall back
+        }
     }
     int sms = 0, per_sm = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
@@ -224,6 +238,65 @@ __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// ---------------------------------------------------------------- bulk asynchronous copies (global -> shared)
+// The copy engine moves a contiguous run of bytes into shared memory and signals an mbarrier with
+// the byte count; no register is held while the data is in flight. Source, destination and size
+// must be multiples of 16 bytes. Plain (non-multicast) form only.
+__device__ __forceinline__ uint32_t smem_addr(const void *p) {
+    return (uint32_t) __cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
+}
+
+// Makes freshly initialised mbarriers visible to the copy engine.
+__device__ __forceinline__ void mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// One arrival that also announces `bytes` of copy traffic still to land on the barrier.
+__device__ __forceinline__ void mbar_arrive_expect(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *global_src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_addr(smem_dst)),
+                 "l"(__cvta_generic_to_global(global_src)), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Waits for the phase with the given parity to complete, giving up after kMaxBarrierPolls polls
+// (each poll may itself block for a hardware-defined short time). Returns false on give-up.
+constexpr uint32_t kMaxBarrierPolls = 1u << 22;
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kMaxBarrierPolls; ++i) {
+        if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
+    }
+    return false;
+}
+
+__device__ __forceinline__ uint4 ld_shared_vec(const void *p) {
+    return *reinterpret_cast<const uint4 *>(p);
 }
 
 // ---------------------------------------------------------------- reductions

@@ -13,11 +13,16 @@
 //
 // HBM traffic per row: K2 reads x and residual and writes out (3 * C * e bytes);
 // K1 reads one gathered word row and writes out (2 * H * e bytes) plus 5 index bytes.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace cubk {
 
 constexpr float kLayerNormEps = 1e-12f;  // src/cuBERT/op/LayerNorm.cpp:35, op/LayerNorm.cu:70
+
+// Warps that gave up waiting for a shared-memory copy since the library was loaded (per device).
+__device__ unsigned int g_copy_timeouts = 0;
 
 template <int TPR, int BLOCK>
 __device__ __forceinline__ float row_sum(float v, float *red) {
@@ -77,11 +82,17 @@ struct Param {
     }
 };
 
-// Normalise the register-resident row `v` and store it.
-template <typename T, int TPR, int VPT, int BLOCK, bool IN_SMEM>
+struct NoHook {
+    __device__ __forceinline__ void operator()() const {}
+};
+
+// Normalise the register-resident row `v` and store it. `after_mean` runs once the first
+// reduction has consumed every thread's inputs (the place to recycle the buffer they came from).
+template <typename T, int TPR, int VPT, int BLOCK, bool IN_SMEM, typename Hook = NoHook>
 __device__ __forceinline__ void normalise_store(float2 (&v)[VPT][Vec2<T>::PAIRS], int lane, int nvec, int channels,
                                                 bool active, const Param<T, IN_SMEM> &p_gamma,
-                                                const Param<T, IN_SMEM> &p_beta, T *out_row, float *red) {
+                                                const Param<T, IN_SMEM> &p_beta, T *out_row, float *red,
+                                                Hook after_mean = Hook()) {
     constexpr int EPV = Vec<T>::EPV;
     constexpr int PAIRS = Vec2<T>::PAIRS;
     float2 s2 = make_float2(0.f, 0.f);
@@ -96,6 +107,7 @@ __device__ __forceinline__ void normalise_store(float2 (&v)[VPT][Vec2<T>::PAIRS]
     }
     const float mean = row_sum<TPR, BLOCK>(s2.x + s2.y, red) / (float) channels;
     const float2 neg_mean = splat2(-mean);
+    after_mean();
 
     float2 q2 = make_float2(0.f, 0.f);
 #pragma unroll
@@ -330,6 +342,165 @@ embed_ln_kernel(const int32_t *ids, const int8_t *segment_ids, const T *word, co
     }
 }
 
+// K1 for rows that fit one warp, with the gathered word rows staged through shared memory by the
+// copy engine. Every warp owns a ring of DEPTH row slots, each with its own mbarrier; lane d (d <
+// DEPTH) owns slot d: it issues one bulk copy of the whole word row per step into its slot and reads
+// the token indices of the step after that, so DEPTH rows per warp are in flight while no register
+// holds them. A slot is refilled after the mean reduction of the row it held, i.e. once every lane's
+// shared-memory reads of it have been consumed. Tokens are walked position-major as above.
+// A barrier wait that runs out of polls sets CUBK_STATUS_COPY_TIMEOUT and counts in g_copy_timeouts,
+// drains (bounded) the copies the warp still has in flight and ends the warp's work.
+constexpr int kBulkBlock = 256;
+
+template <typename T, int VPT, int DEPTH>
+__global__ void __launch_bounds__(kBulkBlock, (VPT * Vec<T>::EPV <= 24 ? 3 : (VPT * Vec<T>::EPV <= 32 ? 2 : 1)))
+embed_ln_bulk_kernel(const int32_t *ids, const int8_t *segment_ids, const T *word, const T *pos, const T *type,
+                     const T *gamma, const T *beta, T *out, uint32_t tokens, FastDiv batch_div, int seq,
+                     int hidden, int nvec, int vocab, int type_vocab, uint32_t *status) {
+    constexpr int EPV = Vec<T>::EPV;
+    constexpr int PAIRS = Vec2<T>::PAIRS;
+    constexpr int TPR = 32;
+    constexpr int GROUPS = kBulkBlock / TPR;
+    static_assert((DEPTH & (DEPTH - 1)) == 0 && DEPTH <= 32, "DEPTH is a power of two");
+    extern __shared__ float4 s_dyn[];
+    const uint32_t row_bytes = (uint32_t) hidden * (uint32_t) sizeof(T);
+    unsigned char *ring_all = reinterpret_cast<unsigned char *>(s_dyn);
+    float4 *s_params = reinterpret_cast<float4 *>(ring_all + (size_t) GROUPS * DEPTH * row_bytes);
+    uint64_t *bars_all = reinterpret_cast<uint64_t *>(s_params + 2 * (EPV / 4) * nvec);
+    Param<T, true> p_gamma{s_params, gamma};
+    Param<T, true> p_beta{s_params + (EPV / 4) * nvec, beta};
+
+    const int lane = threadIdx.x % TPR;
+    const int group = threadIdx.x / TPR;
+    unsigned char *ring = ring_all + (size_t) group * DEPTH * row_bytes;
+    uint64_t *bars = bars_all + group * DEPTH;
+
+    const uint32_t total_groups = gridDim.x * GROUPS;
+    const uint32_t g = blockIdx.x * GROUPS + group;
+    const uint32_t share = tokens / total_groups;
+    const uint32_t extra = tokens - share * total_groups;
+    const uint32_t j_begin = g * share + min(g, extra);
+    const uint32_t j_count = share + (g < extra ? 1u : 0u);
+
+    auto token_of = [&](uint32_t j, uint32_t &s) {
+        s = fast_div(j, batch_div);
+        return (j - s * batch_div.div) * (uint32_t) seq + s;
+    };
+
+    if (lane < DEPTH) {
+        mbar_init(&bars[lane], 1);
+        mbar_init_fence();
+    }
+    __syncwarp();
+
+    // slot owners: indices of the row in the slot (seg_cur) and of the row that follows it there
+    int id_next = 0, seg_next = 0, seg_cur = 0;
+    auto fetch_next = [&](uint32_t step) {
+        if (step < j_count) {
+            uint32_t s;
+            const uint32_t token = token_of(j_begin + step, s);
+            id_next = ids[token];
+            seg_next = segment_ids[token];
+        }
+    };
+    auto issue = [&](int slot) {  // copy of word[id_next] into `slot`; its segment id becomes current
+        int wid = id_next;
+        if (wid < 0 || wid >= vocab) {
+            if (status != nullptr) {
+                atomicOr(status, CUBK_STATUS_BAD_TOKEN_ID);
+            }
+            wid = min(max(wid, 0), vocab - 1);
+        }
+        mbar_arrive_expect(&bars[slot], row_bytes);
+        bulk_load(ring + (size_t) slot * row_bytes, word + (size_t) wid * hidden, row_bytes, &bars[slot]);
+        seg_cur = seg_next;
+    };
+    if (lane < DEPTH) {
+        fetch_next(lane);
+        if ((uint32_t) lane < j_count) {
+            issue(lane);
+        }
+        fetch_next(lane + DEPTH);
+    }
+
+    stage_param<T>(gamma, s_params, nvec, threadIdx.x, kBulkBlock);
+    stage_param<T>(beta, s_params + (EPV / 4) * nvec, nvec, threadIdx.x, kBulkBlock);
+    __syncthreads();
+
+    float2 pos_row[VPT][PAIRS];
+    uint32_t cur_s = 0xffffffffu;
+
+    for (uint32_t step = 0; step < j_count; ++step) {
+        const int slot = (int) (step % DEPTH);
+        const uint32_t parity = (step / DEPTH) & 1u;
+        uint32_t s = 0;
+        const uint32_t token = token_of(j_begin + step, s);
+        int tid = __shfl_sync(0xffffffffu, seg_cur, slot);
+        if (tid < 0 || tid >= type_vocab) {
+            if (status != nullptr && lane == 0) {
+                atomicOr(status, CUBK_STATUS_BAD_SEGMENT_ID);
+            }
+            tid = min(max(tid, 0), type_vocab - 1);
+        }
+        const T *trow = type + (size_t) tid * hidden;
+        uint4 rt[VPT];
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int idx = lane + k * TPR;
+            rt[k] = idx < nvec ? ld_param(trow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
+        }
+        if (s != cur_s) {  // uniform within the warp
+            cur_s = s;
+            const T *prow = pos + (size_t) s * hidden;
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                const int idx = lane + k * TPR;
+                const uint4 raw = idx < nvec ? ld_param(prow + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
+                Vec2<T>::unpack(raw, pos_row[k]);
+            }
+        }
+
+        if (!mbar_wait_bounded(&bars[slot], parity)) {
+            if (lane == 0) {
+                atomicAdd(&g_copy_timeouts, 1u);
+                if (status != nullptr) {
+                    atomicOr(status, CUBK_STATUS_COPY_TIMEOUT);
+                }
+            }
+            // drain what is still in flight (this row and the up to DEPTH - 1 after it), then give up
+            for (uint32_t u = step; u < j_count && u < step + DEPTH; ++u) {
+                (void) mbar_wait_bounded(&bars[u % DEPTH], (u / DEPTH) & 1u);
+            }
+            break;
+        }
+        const unsigned char *srow = ring + (size_t) slot * row_bytes;
+        float2 v[VPT][PAIRS];
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int idx = lane + k * TPR;
+            const uint4 rw = idx < nvec ? ld_shared_vec(srow + (size_t) idx * 16) : make_uint4(0, 0, 0, 0);
+            float2 t[PAIRS];
+            Vec2<T>::unpack(rw, v[k]);
+            Vec2<T>::unpack(rt[k], t);
+#pragma unroll
+            for (int e = 0; e < PAIRS; ++e) {
+                v[k][e] = add2(add2(v[k][e], pos_row[k][e]), t[e]);  // (word + pos) + type, the reference's order
+            }
+        }
+
+        auto refill = [&]() {
+            if (lane == slot) {
+                if (step + DEPTH < j_count) {
+                    issue(slot);
+                }
+                fetch_next(step + 2 * DEPTH);
+            }
+        };
+        normalise_store<T, TPR, VPT, kBulkBlock, true>(v, lane, nvec, hidden, true, p_gamma, p_beta,
+                                                       out + (size_t) token * hidden, nullptr, refill);
+    }
+}
+
 // ------------------------------------------------------------------ generic rows (any width, any alignment)
 // One block per row, three scalar passes over the row (sum, centred squares, write).
 template <typename T>
@@ -421,6 +592,19 @@ generic_ln_kernel(Loader load, const T *gamma, const T *beta, T *out, int channe
 constexpr int kMaxRowVectors = 1024;
 constexpr size_t kMaxParamSmem = 47 * 1024;  // dynamic + static stay below the 48 KB that needs no opt-in
 
+// Whether K1 stages its word rows through shared memory. Measured on B200 (hidden 768): with float32
+// rows (3 KB) and 32768 tokens the staged kernel takes 30 us against 33 us, with 4096 tokens 8.4 us
+// against 7.6 us, and with binary16 rows (1.5 KB) 25 us against 22 us, where the per-row instruction
+// cost rather than the bytes in flight sets the pace. So: rows of 2 KB or more and at least 16384 tokens.
+// CUBK_BULK_COPY=0 / =1 in the environment forces the choice (read on every call).
+static bool use_bulk_rows(size_t row_bytes, int64_t tokens) {
+    const char *v = getenv("CUBK_BULK_COPY");
+    if (v != nullptr && (v[0] == '0' || v[0] == '1')) {
+        return v[0] == '1';
+    }
+    return row_bytes >= 2048 && tokens >= 16384;
+}
+
 template <typename T>
 int bias_residual_ln(const T *x, const T *bias, const T *residual, const T *gamma, const T *beta,
                      int64_t rows, int channels, T *out, cudaStream_t stream) {
@@ -461,6 +645,44 @@ int bias_residual_ln(const T *x, const T *bias, const T *residual, const T *gamm
     return check_launch();
 }
 
+// Launches the shared-memory-staged K1 when its ring fits; false = not launched (caller falls back).
+template <typename T, int VPT, int DEPTH>
+bool launch_embed_bulk(const int32_t *ids, const int8_t *segment_ids, const T *word, const T *pos, const T *type,
+                       const T *gamma, const T *beta, T *out, int64_t tokens, int batch, int seq, int hidden,
+                       int nvec, int vocab, int type_vocab, uint32_t *status, cudaStream_t stream) {
+    static OccupancyCache cache;
+    constexpr int GROUPS = kBulkBlock / 32;
+    auto kernel = embed_ln_bulk_kernel<T, VPT, DEPTH>;
+    const size_t smem = (size_t) GROUPS * DEPTH * hidden * sizeof(T) + sizeof(float) * 2 * (size_t) hidden +
+                        sizeof(uint64_t) * GROUPS * DEPTH;
+    const int resident = resident_blocks(kernel, kBulkBlock, smem, &cache, true);
+    if (resident <= 0) {
+        return false;
+    }
+    int64_t grid = (tokens + GROUPS - 1) / GROUPS;
+    if (grid > resident) {
+        grid = resident;
+    }
+    kernel<<<(unsigned) grid, kBulkBlock, smem, stream>>>(ids, segment_ids, word, pos, type, gamma, beta, out,
+                                                          (uint32_t) tokens, make_fastdiv((uint32_t) batch), seq,
+                                                          hidden, nvec, vocab, type_vocab, status);
+    return true;
+}
+
+template <typename T, int VPT>
+bool launch_embed_bulk_depth(const int32_t *ids, const int8_t *segment_ids, const T *word, const T *pos,
+                             const T *type, const T *gamma, const T *beta, T *out, int64_t tokens, int batch,
+                             int seq, int hidden, int nvec, int vocab, int type_vocab, uint32_t *status,
+                             cudaStream_t stream) {
+    // four rows in flight per warp while eight such rings stay within 64 KB, else two
+    if ((size_t) (kBulkBlock / 32) * 4 * hidden * sizeof(T) <= 64 * 1024) {
+        return launch_embed_bulk<T, VPT, 4>(ids, segment_ids, word, pos, type, gamma, beta, out, tokens, batch, seq,
+                                            hidden, nvec, vocab, type_vocab, status, stream);
+    }
+    return launch_embed_bulk<T, VPT, 2>(ids, segment_ids, word, pos, type, gamma, beta, out, tokens, batch, seq,
+                                        hidden, nvec, vocab, type_vocab, status, stream);
+}
+
 template <typename T>
 int embed_ln(const int32_t *ids, const int8_t *segment_ids, const T *word, const T *pos, const T *type,
              const T *gamma, const T *beta, int batch, int seq, int hidden, int vocab, int type_vocab,
@@ -485,6 +707,22 @@ int embed_ln(const int32_t *ids, const int8_t *segment_ids, const T *word, const
     if (vec_ok) {
         const int nvec = hidden / EPV;
         const FastDiv batch_div = make_fastdiv((uint32_t) batch);
+        if (nvec <= 256 && use_bulk_rows(sizeof(T) * (size_t) hidden, tokens)) {  // a row fits one warp
+            bool launched = false;
+#define BULK(VPT)                                                                                           \
+    launched = launch_embed_bulk_depth<T, VPT>(ids, segment_ids, word, pos, type, gamma, beta, out, tokens, \
+                                               batch, seq, hidden, nvec, vocab, type_vocab, status, stream)
+            if (nvec <= 32) { BULK(1); }
+            else if (nvec <= 64) { BULK(2); }
+            else if (nvec <= 96) { BULK(3); }
+            else if (nvec <= 128) { BULK(4); }
+            else if (nvec <= 192) { BULK(6); }
+            else { BULK(8); }
+#undef BULK
+            if (launched) {
+                return check_launch();
+            }
+        }
 #define LAUNCH(TPR, VPT, BLOCK, PERSISTENT)                                                           \
     {                                                                                                 \
         static OccupancyCache cache;                                                                  \
@@ -510,6 +748,18 @@ int embed_ln(const int32_t *ids, const int8_t *segment_ids, const T *word, const
 }  // namespace cubk
 
 extern "C" {
+
+int cubk_copy_timeouts(unsigned int *count) {
+    if (count == nullptr) {
+        return CUBK_ERR_INVALID_ARG;
+    }
+    cudaError_t err = cudaMemcpyFromSymbol(count, cubk::g_copy_timeouts, sizeof(unsigned int));
+    if (err != cudaSuccess) {
+        cubk::set_last_error(err);
+        return CUBK_ERR_LAUNCH;
+    }
+    return CUBK_OK;
+}
 
 int cubk_bias_residual_ln_f32(const float *x, const float *bias, const float *residual, const float *gamma,
                               const float *beta, int64_t rows, int channels, float *out, void *stream) {

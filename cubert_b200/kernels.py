@@ -21,6 +21,7 @@ CUBK_ERR_SCRATCH = -4
 STATIC_POOL_SCRATCH_BYTES = 512 * 1024
 STATUS_BAD_TOKEN_ID = 1
 STATUS_BAD_SEGMENT_ID = 2
+STATUS_COPY_TIMEOUT = 4
 
 _P = C.c_void_p
 _I = C.c_int
@@ -32,6 +33,7 @@ _Z = C.c_size_t
 _SIGNATURES = {
     "cubk_version": (_I, []),
     "cubk_last_cuda_error": (C.c_char_p, []),
+    "cubk_copy_timeouts": (_I, [_P]),
     "cubk_embed_ln_{t}": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P]),
     "cubk_embed_gather_i32": (_I, [_P, _L, _P, _I, _I, _I, _P, _P, _P]),
     "cubk_embed_gather_i8": (_I, [_P, _L, _P, _I, _I, _I, _P, _P, _P]),
@@ -89,3 +91,10 @@ def check(rc):
     if rc != CUBK_OK:
         detail = load().cubk_last_cuda_error().decode() if rc == CUBK_ERR_LAUNCH else ""
         raise KernelError("cubk call failed with status %d %s" % (rc, detail))
+
+
+def copy_timeouts():
+    """Warps on the current device that gave up waiting for a shared-memory copy (expected: 0)."""
+    n = C.c_uint(0)
+    check(load().cubk_copy_timeouts(C.byref(n)))
+    return n.value

@@ -51,6 +51,8 @@ struct cubert_b200_info {
     int32_t num_hidden_layers;
     int32_t num_attention_heads;
     int32_t has_pooler_dense; /* 1: first-token dense + tanh pooler, 0: mean pooler */
+    int32_t fp32_gemm_emulation; /* 1: a float32 model whose cuBLAS products run as three-way bfloat16 splits on
+                                    the tensor cores (cuBLAS 12.9 or newer; CUBERT_FP32_EMULATION=0 turns it off) */
 };
 int cubert_b200_model_info(void *model, int compute_type, struct cubert_b200_info *info);
 

@@ -42,10 +42,19 @@ extern "C" {
  * The offending index is clamped into range so that no out-of-bounds read happens. */
 #define CUBK_STATUS_BAD_TOKEN_ID   1u
 #define CUBK_STATUS_BAD_SEGMENT_ID 2u
+/* A wait for an asynchronous shared-memory copy inside cubk_embed_ln_* ran out of polls; the rows of
+ * the affected warp from that point on were not written. Not expected in normal operation. */
+#define CUBK_STATUS_COPY_TIMEOUT   4u
 
 /* Library version and the text of the last CUDA error seen by a failed launch (thread-local). */
 int cubk_version(void);
 const char *cubk_last_cuda_error(void);
+
+/* Warps, on the current device and since the library was loaded, that gave up waiting for one of the
+ * asynchronous global-to-shared copies the row kernels (cubk_embed_ln_*, cubk_bias_residual_ln_*) stage
+ * their inputs with. Every such wait is bounded; a warp that gives up stops writing rows. Expected to
+ * stay 0. Synchronises with the device. No counterpart in the reference. */
+int cubk_copy_timeouts(unsigned int *count);
 
 /* ---- K1: embedding lookup + position/token-type add + LayerNorm --------------------------
  * out[b,s,:] = LayerNorm((word[ids[b,s]] + pos[s]) + type[segment_ids[b,s]]; gamma, beta)

@@ -61,6 +61,20 @@ def build_pywrap():
     return PYWRAP_DIR
 
 
+BENCHMARK_BIN = os.path.join(HERE, "_ref", "benchmark_cu")
+
+
+def build_benchmark():
+    """Compile the reference's own benchmark program (benchmark/benchmark_cu.cpp, unmodified) against our
+    libcuBERT.so. Returns the path of the binary, or None where it cannot be built."""
+    if not os.path.exists(BENCHMARK_BIN):
+        if not os.path.exists(os.path.join(REFERENCE_SRC, "..", "benchmark", "benchmark_cu.cpp")):
+            return None
+        subprocess.run(["make", "-C", HERE, "REF=" + REFERENCE_SRC, "ref_benchmark"], check=True,
+                       stdout=subprocess.DEVNULL)
+    return BENCHMARK_BIN
+
+
 def _f32(a):
     return np.ascontiguousarray(a, dtype=np.float32)
 

@@ -18,6 +18,13 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: test needs a CUDA device")
+    # Bind the CUDA toolkit's cuBLAS (what a C or C++ host of libcuBERT.so gets) before torch loads the
+    # older copy it bundles; harmless when the native libraries are not built yet.
+    try:
+        from cubert_b200 import model
+        model.load()
+    except Exception:
+        pass
 
 
 def _has_gpu():

@@ -279,10 +279,13 @@ def test_masked_softmax(oracle, t, kind, batch, heads, seq):
 
 # ============================================================================ K1 embedding + add + LayerNorm
 
+@pytest.mark.parametrize("staged", ["0", "1"])   # register-resident rows / word rows staged through shared memory
 @pytest.mark.parametrize("t", DTYPES)
 @pytest.mark.parametrize("batch,seq,hidden,vocab", [(2, 4, 3, 5), (3, 7, 10, 11), (4, 32, 768, 2000), (2, 128, 1024, 3000),
-                                                    (1, 16, 200, 50), (2, 5, 4096, 30)])
-def test_embed_ln(oracle, t, batch, seq, hidden, vocab):
+                                                    (1, 16, 200, 50), (2, 5, 4096, 30), (5, 9, 32, 7), (300, 64, 256, 999),
+                                                    (7, 33, 1536, 100)])
+def test_embed_ln(oracle, t, batch, seq, hidden, vocab, staged, monkeypatch):
+    monkeypatch.setenv("CUBK_BULK_COPY", staged)
     rng = np.random.default_rng(hidden + vocab)
     word, wh = _prep(rng.standard_normal((vocab, hidden)) * 0.02, t)
     pos, ph = _prep(rng.standard_normal((seq + 3, hidden)) * 0.02, t)
@@ -296,9 +299,34 @@ def test_embed_ln(oracle, t, batch, seq, hidden, vocab):
     ref = oracle.bert_embeddings(ids, seg, wh, ph[:seq], th, beh, gh)
     _check(got, ref, t, 1.0, "embed_ln")
     assert int(status.item()) == 0
+    assert kernels.copy_timeouts() == 0
 
 
-def test_embed_out_of_range_ids_are_clamped_and_flagged(oracle):
+@pytest.mark.parametrize("t", DTYPES)
+def test_embed_ln_sweep_shape_with_the_default_kernel_choice(oracle, t, monkeypatch):
+    """256 x 128 tokens, hidden 768, vocabulary 21128: float32 takes the staged kernel by default,
+    binary16 the register-resident one; every token of the even split over warps is checked."""
+    monkeypatch.delenv("CUBK_BULK_COPY", raising=False)
+    batch, seq, hidden, vocab = 256, 128, 768, 21128
+    rng = np.random.default_rng(1)
+    word, wh = _prep(rng.standard_normal((vocab, hidden)) * 0.02, t)
+    pos, ph = _prep(rng.standard_normal((512, hidden)) * 0.02, t)
+    typ, th = _prep(rng.standard_normal((2, hidden)) * 0.02, t)
+    g, gh = _prep(1 + 0.1 * rng.standard_normal(hidden), t)
+    be, beh = _prep(0.1 * rng.standard_normal(hidden), t)
+    ids = rng.integers(0, vocab, (batch, seq), dtype=np.int32)
+    seg = rng.integers(0, 2, (batch, seq)).astype(np.int8)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = G.embed_ln(G.dev(ids), G.dev(seg), word, pos, typ, g, be, t, status)
+    ref = oracle.bert_embeddings(ids, seg, wh, ph[:seq], th, beh, gh)
+    _check(got, ref, t, 1.0, "embed_ln 256x128")
+    assert int(status.item()) == 0
+    assert kernels.copy_timeouts() == 0
+
+
+@pytest.mark.parametrize("staged", ["0", "1"])
+def test_embed_out_of_range_ids_are_clamped_and_flagged(oracle, staged, monkeypatch):
+    monkeypatch.setenv("CUBK_BULK_COPY", staged)
     rng = np.random.default_rng(0)
     vocab, hidden, seq = 10, 768, 4
     word = rng.standard_normal((vocab, hidden)).astype(np.float32)

@@ -379,3 +379,57 @@ def test_through_the_references_own_python_wrapper(model_files, reference_python
     assert rel_err(new_output.logits, g["logits"]) < 1e-5
     assert rel_err(new_output.sequence_output, g["sequence_output"]) < 1e-5
     del m
+
+
+@pytest.mark.gpu
+def test_float32_products_on_tensor_cores_keep_float32_accuracy(tmp_path, oracle, monkeypatch):
+    """A float32 model's cuBLAS products run, where cuBLAS offers it, as three-way bfloat16 splits on the
+    tensor cores. Both ways must stay within the float32 bar of the oracle, on BERT-base geometry
+    (sums over 768 and 3072 terms)."""
+    cfg = synthetic.config("base", layers=2)
+    var = synthetic.random_weights(cfg, 5)
+    path = str(tmp_path / "base2.pb")
+    frozen_graph.write_frozen_graph(path, var)
+    B, S = 16, 32
+    ids, mask, seg, _ = synthetic.random_inputs(cfg, B, S, 5, lengths=(5, S), segments="random")
+    ref = oracle.bert_forward(var, synthetic.model_geometry(cfg, S), ids, mask, seg)
+    errs = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("CUBERT_FP32_EMULATION", mode)
+        m = model.Model(path, B, S, cfg["layers"], cfg["heads"], model.ComputeType.FLOAT)
+        if mode == "0":
+            assert m.info["fp32_gemm_emulation"] == 0
+        active = m.info["fp32_gemm_emulation"]
+        for _ in range(3):   # eager, captured, replayed
+            got = _run(m, ids, mask, seg, cfg)
+        errs[mode] = (active, {k: rel_err(got[k], ref[k]) for k in got})
+        m.close()
+        for k, e in errs[mode][1].items():
+            assert e < 1e-5, (mode, k, e)
+    if errs["1"][0] == 0:
+        pytest.skip("this cuBLAS has no float32 emulation; the float32 pipes were checked")
+
+
+@pytest.mark.gpu
+def test_the_references_own_benchmark_program(tmp_path):
+    """benchmark/benchmark_cu.cpp of the reference, compiled unchanged against this library (make -C
+    oracle ref_benchmark): BERT-base float32, batch 128, seq 32, cuBERT_POOLED_OUTPUT, 10 warm-up + 10
+    timed calls with random ids, masks and segments. It must run to the end and write finite tanh values."""
+    import subprocess
+    from cubert_b200 import build as native
+    from oracle import bindings
+    native.build_all(verbose=False)
+    binary = bindings.build_benchmark()
+    if binary is None:
+        pytest.skip("reference benchmark not built (reference tree absent)")
+    cfg = synthetic.config("base")
+    frozen_graph.write_frozen_graph(str(tmp_path / "bert_frozen_seq32.pb"), synthetic.random_weights(cfg, 0))
+    proc = subprocess.run([binary], cwd=str(tmp_path), stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                          timeout=600, universal_newlines=True)
+    assert proc.returncode == 0, proc.stdout[-2000:]
+    times = [int(l.split()[1][:-2]) for l in proc.stdout.splitlines() if l.startswith("cuBERT: ") and l.endswith("ms")]
+    assert len(times) == 20, proc.stdout[-2000:]
+    assert max(times[10:]) < 100          # the reference publishes 184.6 ms per call on a Tesla P4
+    values = np.loadtxt(str(tmp_path / "cuBERT.txt"), dtype=np.float64)
+    assert values.size == 20 * 128 * 768
+    assert np.all(np.isfinite(values)) and np.all(np.abs(values) <= 1.0) and values.std() > 1e-3

@@ -86,6 +86,15 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
         blas_.reset(new Blas(stream_, emulation_ws));
     }
     use_graphs_ = env_int("CUBERT_CUDA_GRAPH", 1) != 0;
+    tail_chunks_ = env_int("CUBERT_TAIL_CHUNKS", 4);
+    tail_chunks_ = tail_chunks_ < 1 ? 1 : (tail_chunks_ > (int) kMaxTailChunks ? (int) kMaxTailChunks : tail_chunks_);
+    tail_layers_ = env_int("CUBERT_TAIL_LAYERS", 2);
+    tail_layers_ = tail_layers_ < 0 ? 0 : tail_layers_;
+    CUDA_CHECK(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
+    CUDA_CHECK(cudaEventCreateWithFlags(&embed_ready_, cudaEventDisableTiming));
+    for (cudaEvent_t &ev : chunk_ready_) {
+        CUDA_CHECK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    }
 
     const bool half = Storage<T>::is_half;
     algo_attention_ = gemm_algo_from_env("GEMM_ALGO_ATTENTION", half);
@@ -248,6 +257,18 @@ Bert<T>::~Bert() {
         cudaEventDestroy(t.stop);
     }
     blas_.reset();
+    if (copy_stream_ != nullptr) {
+        cudaStreamSynchronize(copy_stream_);
+        cudaStreamDestroy(copy_stream_);
+    }
+    if (embed_ready_ != nullptr) {
+        cudaEventDestroy(embed_ready_);
+    }
+    for (cudaEvent_t ev : chunk_ready_) {
+        if (ev != nullptr) {
+            cudaEventDestroy(ev);
+        }
+    }
     if (h_token_index_ != nullptr) {
         cudaFreeHost(h_token_index_);
     }
@@ -407,38 +428,38 @@ constexpr size_t kMaxCachedGraphs = 256;
 template <typename T>
 void Bert<T>::run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments,
                   size_t packed) {
+    const GraphKey key{batch_size, packed, d_ids, d_mask, d_segments, kWholePass, 0, 0};
+    run_graph(key, [&] { forward(batch_size, d_ids, d_mask, d_segments, packed); });
+}
+
+// Runs `body` (a sequence of launches on stream_) eagerly the first time a key is seen (cuBLASLt picks
+// its algorithms, occupancy is queried), captures it into a CUDA graph the second time and replays that
+// graph from then on.
+template <typename T>
+void Bert<T>::run_graph(const GraphKey &key, const std::function<void()> &body) {
     if (!use_graphs_ || profiling_) {
-        forward(batch_size, d_ids, d_mask, d_segments, packed);
+        body();
         return;
     }
-    const GraphKey key{batch_size, packed, d_ids, d_mask, d_segments};
     auto it = graphs_.find(key);
     if (it == graphs_.end()) {
         if (graphs_.size() >= kMaxCachedGraphs) {
-            forward(batch_size, d_ids, d_mask, d_segments, packed);
+            body();
             return;
         }
         it = graphs_.emplace(key, GraphEntry()).first;
     }
     GraphEntry &g = it->second;
     if (g.exec != nullptr) {
-        // the launch counters keep counting what the graph replays
-        launches_[CUBERT_B200_K_EMBED_LN] += 1;
-        launches_[CUBERT_B200_K_BIAS_RESIDUAL_LN] += 2 * (int64_t) num_hidden_layers;
-        launches_[CUBERT_B200_K_BIAS_GELU] += (int64_t) num_hidden_layers;
-        launches_[CUBERT_B200_K_MASKED_SOFTMAX] += (int64_t) num_hidden_layers;
-        launches_[has_pooler_dense_ ? CUBERT_B200_K_BIAS_TANH : CUBERT_B200_K_MEAN_POOL] += 1;
-        if (has_classifier_) {
-            launches_[CUBERT_B200_K_LOGITS_PROBS] += 1;
+        for (int k = 0; k < CUBERT_B200_K_COUNT; ++k) {
+            launches_[k] += g.launches[k];  // the launch counters keep counting what the graph replays
         }
-        launches_[CUBERT_B200_K_GEMM] += 6 * (int64_t) num_hidden_layers + (has_pooler_dense_ ? 1 : 0);
         CUDA_CHECK(cudaGraphLaunch(g.exec, stream_));
         return;
     }
     g.seen += 1;
     if (g.seen == 1) {
-        // first call with this shape: run eagerly (cuBLASLt picks its algorithms, occupancy is queried)
-        forward(batch_size, d_ids, d_mask, d_segments, packed);
+        body();
         return;
     }
     const auto saved_launches = launches_;
@@ -446,7 +467,7 @@ void Bert<T>::run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask,
     cudaGraph_t graph = nullptr;
     CUDA_CHECK(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
     try {
-        forward(batch_size, d_ids, d_mask, d_segments, packed);
+        body();
     } catch (...) {
         cudaStreamEndCapture(stream_, &graph);
         if (graph != nullptr) {
@@ -455,6 +476,9 @@ void Bert<T>::run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask,
         throw;
     }
     CUDA_CHECK(cudaStreamEndCapture(stream_, &graph));
+    for (int k = 0; k < CUBERT_B200_K_COUNT; ++k) {
+        g.launches[k] = launches_[k] - saved_launches[k];
+    }
     launches_ = saved_launches;  // capturing launched nothing
     bytes_ = saved_bytes;
     cudaError_t err = cudaGraphInstantiate(&g.exec, graph, 0);
@@ -463,45 +487,76 @@ void Bert<T>::run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask,
         g.exec = nullptr;
         use_graphs_ = false;  // fall back to plain launches for good
         (void) cudaGetLastError();
-        forward(batch_size, d_ids, d_mask, d_segments, packed);
+        body();
         return;
     }
-    run(batch_size, d_ids, d_mask, d_segments, packed);
+    run_graph(key, body);
 }
 
 template <typename T>
 void Bert<T>::forward(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments,
                       size_t packed) {
-    const int B = (int) batch_size, S = (int) seq_length, H = (int) hidden_size, I = (int) intermediate_size;
-    const int heads = (int) num_attention_heads, d = H / heads;
-    const int64_t R = (int64_t) B * S;      // rows of the [batch, seq] layout
-    const int64_t N = packed > 0 ? (int64_t) packed : R;  // rows the token-wise steps work on
+    forward_embed(batch_size, d_ids, d_segments, packed);
+    forward_layers(0, num_hidden_layers, 0, batch_size, batch_size, d_mask, packed);
+    forward_heads(batch_size, d_mask, packed);
+}
+
+// K1: embeddings (src/cuBERT/op_bert/BertEmbeddings.cpp:50-66); with `packed`, also the gather of the
+// kept tokens' rows into the first layer's input.
+template <typename T>
+void Bert<T>::forward_embed(size_t batch_size, const int32_t *d_ids, const int8_t *d_segments, size_t packed) {
+    const int B = (int) batch_size, S = (int) seq_length, H = (int) hidden_size;
+    const int64_t R = (int64_t) B * S;
     const int64_t e = sizeof(T);
     void *st = stream_;
-    const int32_t *tok = token_index_.template as<int32_t>();
-
-    // K1: embeddings (src/cuBERT/op_bert/BertEmbeddings.cpp:50-66)
     begin(CUBERT_B200_K_EMBED_LN);
     KERNEL_CHECK(K<T>::embed_ln(d_ids, d_segments, word_emb_.template as<T>(), pos_emb_.template as<T>(), type_emb_.template as<T>(),
                                 emb_ln_gamma_.template as<T>(), emb_ln_beta_.template as<T>(), B, S, H, (int) vocab_size,
                                 (int) type_vocab_size, embedding_.template as<T>(), status_.template as<uint32_t>(), st));
     end(CUBERT_B200_K_EMBED_LN, 2 * R * H * e + 5 * R + (int64_t) S * H * e + (int64_t) type_vocab_size * H * e +
                                     2 * H * e);
-
-    // encoder (src/cuBERT/op_att/Transformer.cpp:145-175, op_att/AttentionSelf.cpp:96-111)
-    const float att_scale = (float) (1.0 / std::sqrt((double) d));  // op_att/AttentionSelf.cpp:58-60
-    const T *x = embedding_.template as<T>();
     if (packed > 0) {
-        // gather the kept tokens' embedding rows; layer 0 writes hidden_[0], so they go to hidden_[1]
-        KERNEL_CHECK(cubk_embed_gather_i32(tok, N, embedding_.get(), (int) R, H, (int) e, hidden_[1].get(), nullptr, st));
-        x = hidden_[1].template as<T>();
+        // layer 0 writes hidden_[0], so the gathered rows go to hidden_[1]
+        KERNEL_CHECK(cubk_embed_gather_i32(token_index_.template as<int32_t>(), (int64_t) packed, embedding_.get(), (int) R, H,
+                                           (int) e, hidden_[1].get(), nullptr, st));
     }
-    for (size_t l = 0; l < num_hidden_layers; ++l) {
+}
+
+// Encoder layers [l_begin, l_end) on the sequences [b0, b0 + nb) of a batch of `batch_size`
+// (src/cuBERT/op_att/Transformer.cpp:145-175, op_att/AttentionSelf.cpp:96-111). Sequences are
+// independent of one another, so a sub-range of them runs on the same rows of every buffer that the
+// whole batch would use. `packed` > 0 (whole batch only): see the class comment.
+template <typename T>
+void Bert<T>::forward_layers(size_t l_begin, size_t l_end, size_t b0, size_t nb, size_t batch_size,
+                             const int8_t *d_mask, size_t packed) {
+    (void) batch_size;
+    const int B = (int) nb, S = (int) seq_length, H = (int) hidden_size, I = (int) intermediate_size;
+    const int heads = (int) num_attention_heads, d = H / heads;
+    const int64_t R = (int64_t) B * S;      // rows of the [batch, seq] layout in this range
+    const int64_t N = packed > 0 ? (int64_t) packed : R;  // rows the token-wise steps work on
+    const int64_t e = sizeof(T);
+    const int64_t row0 = (int64_t) b0 * S;  // first row of the range (0 when packed)
+    void *st = stream_;
+    const int32_t *tok = token_index_.template as<int32_t>();
+    const int8_t *mask = d_mask + row0;
+
+    const float att_scale = (float) (1.0 / std::sqrt((double) d));  // op_att/AttentionSelf.cpp:58-60
+    T *qkv = qkv_.template as<T>() + row0 * 3 * H;
+    T *scores = scores_.template as<T>() + (int64_t) b0 * heads * S * S;
+    T *context = context_.template as<T>() + row0 * H;
+    T *dense_out = dense_out_.template as<T>() + row0 * H;
+    T *att_out = att_out_.template as<T>() + row0 * H;
+    T *inter = inter_.template as<T>() + row0 * I;
+    const size_t p0 = b0 * (size_t) heads;  // first entry of the range in the pointer arrays
+
+    for (size_t l = l_begin; l < l_end; ++l) {
         Layer &L = layers_[l];
-        T *y = hidden_[l % 2].template as<T>();
+        const T *x = l == 0 ? (packed > 0 ? hidden_[1].template as<T>() : embedding_.template as<T>() + row0 * H)
+                            : hidden_[(l - 1) % 2].template as<T>() + row0 * H;
+        T *y = hidden_[l % 2].template as<T>() + row0 * H;
 
         // Q, K, V in one projection with the bias in the GEMM epilogue
-        T *qkv_out = packed > 0 ? qkv_packed_.template as<T>() : qkv_.template as<T>();
+        T *qkv_out = packed > 0 ? qkv_packed_.template as<T>() : qkv;
         begin(CUBERT_B200_K_GEMM);
         blas_->gemm_bias<T>(3 * H, (int) N, H, L.qkv_kernel.template as<T>(), 3 * H, x, H, L.qkv_bias.template as<T>(), qkv_out,
                             3 * H);
@@ -513,62 +568,72 @@ void Bert<T>::forward(size_t batch_size, const int32_t *d_ids, const int8_t *d_m
 
         // scores[b, i, h, j] = (1/sqrt(d)) * sum_c K[b,j,h,c] * Q[b,i,h,c]   (op_att/BatchMatMul.cpp:57-68)
         begin(CUBERT_B200_K_GEMM);
-        blas_->gemm_batched<T>(true, false, S, S, d, att_scale, k_ptrs_.template as<const T *>(), 3 * H,
-                               q_ptrs_.template as<const T *>(), 3 * H, 0.f, score_ptrs_.template as<T *>(), S * heads, B * heads,
-                               algo_qk_);
+        blas_->gemm_batched<T>(true, false, S, S, d, att_scale, k_ptrs_.template as<const T *>() + p0, 3 * H,
+                               q_ptrs_.template as<const T *>() + p0, 3 * H, 0.f, score_ptrs_.template as<T *>() + p0, S * heads,
+                               B * heads, algo_qk_);
         end(CUBERT_B200_K_GEMM, 0);
 
         // K4: mask + softmax in place over rows [B*S*heads, S]
         begin(CUBERT_B200_K_MASKED_SOFTMAX);
-        KERNEL_CHECK(K<T>::masked_softmax(scores_.template as<T>(), d_mask, R * heads, (int64_t) S * heads, S, 1.0f,
-                                          scores_.template as<T>(), st));
+        KERNEL_CHECK(K<T>::masked_softmax(scores, mask, R * heads, (int64_t) S * heads, S, 1.0f, scores, st));
         end(CUBERT_B200_K_MASKED_SOFTMAX, 2 * R * heads * S * e + R);
 
         // context[b, i, h, c] = sum_j V[b,j,h,c] * P[b,i,h,j]   (op_att/BatchMatMul.cpp:124-135)
         begin(CUBERT_B200_K_GEMM);
-        blas_->gemm_batched<T>(false, false, d, S, S, 1.f, v_ptrs_.template as<const T *>(), 3 * H,
-                               score_ptrs_.template as<const T *>(), S * heads, 0.f, ctx_ptrs_.template as<T *>(), H, B * heads,
-                               algo_qkv_);
+        blas_->gemm_batched<T>(false, false, d, S, S, 1.f, v_ptrs_.template as<const T *>() + p0, 3 * H,
+                               score_ptrs_.template as<const T *>() + p0, S * heads, 0.f, ctx_ptrs_.template as<T *>() + p0, H,
+                               B * heads, algo_qkv_);
         end(CUBERT_B200_K_GEMM, 0);
 
         // attention output projection, then K2: LayerNorm(dense + bias + layer input)
-        const T *ctx = context_.template as<T>();
+        const T *ctx = context;
         if (packed > 0) {
             KERNEL_CHECK(cubk_embed_gather_i32(tok, N, context_.get(), (int) R, H, (int) e, ctx_packed_.get(), nullptr, st));
             ctx = ctx_packed_.template as<T>();
         }
         begin(CUBERT_B200_K_GEMM);
-        blas_->gemm<T>(false, false, H, (int) N, H, 1.f, L.att_out_kernel.template as<T>(), H, ctx, H, 0.f,
-                       dense_out_.template as<T>(), H, algo_attention_);
+        blas_->gemm<T>(false, false, H, (int) N, H, 1.f, L.att_out_kernel.template as<T>(), H, ctx, H, 0.f, dense_out, H,
+                       algo_attention_);
         end(CUBERT_B200_K_GEMM, 0);
         begin(CUBERT_B200_K_BIAS_RESIDUAL_LN);
-        KERNEL_CHECK(K<T>::bias_residual_ln(dense_out_.template as<T>(), L.att_out_bias.template as<T>(), x, L.att_ln_gamma.template as<T>(),
-                                            L.att_ln_beta.template as<T>(), N, H, att_out_.template as<T>(), st));
+        KERNEL_CHECK(K<T>::bias_residual_ln(dense_out, L.att_out_bias.template as<T>(), x, L.att_ln_gamma.template as<T>(),
+                                            L.att_ln_beta.template as<T>(), N, H, att_out, st));
         end(CUBERT_B200_K_BIAS_RESIDUAL_LN, 3 * N * H * e + 3 * H * e);
 
         // intermediate projection, then K3: bias + GELU in place
         begin(CUBERT_B200_K_GEMM);
-        blas_->gemm<T>(false, false, I, (int) N, H, 1.f, L.inter_kernel.template as<T>(), I, att_out_.template as<T>(), H, 0.f,
-                       inter_.template as<T>(), I, algo_intermediate_);
+        blas_->gemm<T>(false, false, I, (int) N, H, 1.f, L.inter_kernel.template as<T>(), I, att_out, H, 0.f, inter, I,
+                       algo_intermediate_);
         end(CUBERT_B200_K_GEMM, 0);
         begin(CUBERT_B200_K_BIAS_GELU);
-        KERNEL_CHECK(K<T>::bias_gelu(inter_.template as<T>(), L.inter_bias.template as<T>(), N, I, inter_.template as<T>(), st));
+        KERNEL_CHECK(K<T>::bias_gelu(inter, L.inter_bias.template as<T>(), N, I, inter, st));
         end(CUBERT_B200_K_BIAS_GELU, 2 * N * I * e + I * e);
 
         // output projection, then K2: LayerNorm(dense + bias + attention output)
         begin(CUBERT_B200_K_GEMM);
-        blas_->gemm<T>(false, false, H, (int) N, I, 1.f, L.out_kernel.template as<T>(), H, inter_.template as<T>(), I, 0.f,
-                       dense_out_.template as<T>(), H, algo_output_);
+        blas_->gemm<T>(false, false, H, (int) N, I, 1.f, L.out_kernel.template as<T>(), H, inter, I, 0.f, dense_out, H,
+                       algo_output_);
         end(CUBERT_B200_K_GEMM, 0);
         begin(CUBERT_B200_K_BIAS_RESIDUAL_LN);
-        KERNEL_CHECK(K<T>::bias_residual_ln(dense_out_.template as<T>(), L.out_bias.template as<T>(), att_out_.template as<T>(),
-                                            L.out_ln_gamma.template as<T>(), L.out_ln_beta.template as<T>(), N, H, y, st));
+        KERNEL_CHECK(K<T>::bias_residual_ln(dense_out, L.out_bias.template as<T>(), att_out, L.out_ln_gamma.template as<T>(),
+                                            L.out_ln_beta.template as<T>(), N, H, y, st));
         end(CUBERT_B200_K_BIAS_RESIDUAL_LN, 3 * N * H * e + 3 * H * e);
-
-        x = y;
     }
+}
 
-    // pooler (src/cuBERT/op_bert/BertPooler.cpp:62-77,93-96)
+// Pooler and classifier over the whole batch (src/cuBERT/op_bert/BertPooler.cpp:62-77,93-96;
+// src/cuBERT/op_out/AdditionalOutputLayer.cpp:44-66).
+template <typename T>
+void Bert<T>::forward_heads(size_t batch_size, const int8_t *d_mask, size_t packed) {
+    const int B = (int) batch_size, S = (int) seq_length, H = (int) hidden_size;
+    const int64_t R = (int64_t) B * S;
+    const int64_t N = packed > 0 ? (int64_t) packed : R;
+    const int64_t e = sizeof(T);
+    void *st = stream_;
+    // what the last layer wrote; with no layers, the embeddings (gathered into hidden_[1] when packed)
+    const T *x = num_hidden_layers == 0 ? (packed > 0 ? hidden_[1].template as<T>() : embedding_.template as<T>())
+                                        : hidden_[(num_hidden_layers - 1) % 2].template as<T>();
+
     if (has_pooler_dense_) {
         const T *first = x;       // first token of every sequence: rows S apart, or gathered when packed
         int first_ld = H * S;
@@ -598,7 +663,6 @@ void Bert<T>::forward(size_t batch_size, const int32_t *d_ids, const int8_t *d_m
         end(CUBERT_B200_K_EVENT_OVERHEAD, 0);
     }
 
-    // classifier head (src/cuBERT/op_out/AdditionalOutputLayer.cpp:44-66)
     if (has_classifier_) {
         begin(CUBERT_B200_K_LOGITS_PROBS);
         KERNEL_CHECK(K<T>::logits_probs(pooled_.template as<T>(), output_weights_.template as<T>(),
@@ -641,6 +705,129 @@ void Bert<T>::output(size_t batch_size, cuBERT_Output *out, bool to_float) {
     copy(out->sequence_output, sequence_output_, B * S * H);
     copy(out->embedding_output, embedding_.template as<T>(), B * S * H);
     CUDA_CHECK(cudaStreamSynchronize(stream_));
+}
+
+// ------------------------------------------------------------------ compute + output with overlapped copies
+constexpr size_t kMinOverlapBytes = 8u << 20;   // per-position output below this: the plain path
+constexpr size_t kMinChunkedTokens = 16384;      // the tail is split only when every sub-batch stays large
+
+template <typename T>
+void Bert<T>::compute_output(size_t batch_size, const int *input_ids, const int8_t *input_mask,
+                             const int8_t *segment_ids, cuBERT_Output *out, bool to_float) {
+    const bool per_position = out->sequence_output != nullptr || out->embedding_output != nullptr;
+    const size_t S = seq_length, H = hidden_size, L = num_hidden_layers;
+    const size_t tokens = batch_size * S;
+    if (!per_position || profiling_ || batch_size == 0 || batch_size > max_batch_size ||
+        tokens * H * sizeof(T) < kMinOverlapBytes || (tail_chunks_ <= 1 && out->embedding_output == nullptr)) {
+        compute(batch_size, input_ids, input_mask, segment_ids, per_position);
+        output(batch_size, out, to_float);
+        return;
+    }
+    if (input_ids == nullptr || input_mask == nullptr || segment_ids == nullptr) {
+        throw std::invalid_argument("null input");
+    }
+    CUDA_CHECK(cudaSetDevice(device_));
+    if ((out->logits != nullptr || out->probs != nullptr) && !has_classifier_) {
+        std::cerr << "model does not have additional_output_layer, the output logits is wrong." << std::endl;
+    }
+    const bool convert = to_float && Storage<T>::is_half;
+    const size_t out_elem = convert ? sizeof(float) : sizeof(T);
+    if (convert && out->embedding_output != nullptr && float_staging_embedding_.get() == nullptr) {
+        float_staging_embedding_.allocate(sizeof(float) * max_batch_size * S * H);
+    }
+    if (convert && float_staging_small_.get() == nullptr) {
+        float_staging_small_.allocate(sizeof(float) * max_batch_size * (H > num_labels ? H : num_labels));
+    }
+
+    CUDA_CHECK(cudaMemcpyAsync(ids_.get(), input_ids, sizeof(int32_t) * tokens, cudaMemcpyHostToDevice, stream_));
+    CUDA_CHECK(cudaMemcpyAsync(mask_.get(), input_mask, sizeof(int8_t) * tokens, cudaMemcpyHostToDevice, stream_));
+    CUDA_CHECK(cudaMemcpyAsync(segments_.get(), segment_ids, sizeof(int8_t) * tokens, cudaMemcpyHostToDevice, stream_));
+    const int32_t *d_ids = ids_.template as<int32_t>();
+    const int8_t *d_mask = mask_.template as<int8_t>();
+    const int8_t *d_seg = segments_.template as<int8_t>();
+
+    // ---- everything that computes goes to the compute stream first ...
+    forward_embed(batch_size, d_ids, d_seg, 0);
+    const void *embedding_src = embedding_.get();
+    if (out->embedding_output != nullptr) {
+        if (convert) {
+            KERNEL_CHECK(cubk_half_to_float(embedding_.get(), float_staging_embedding_.template as<float>(),
+                                            (int64_t) (tokens * H), stream_));
+            embedding_src = float_staging_embedding_.get();
+        }
+        CUDA_CHECK(cudaEventRecord(embed_ready_, stream_));
+    }
+    size_t chunks = 1;
+    if (out->sequence_output != nullptr && tokens >= kMinChunkedTokens && L > 0) {
+        chunks = (size_t) tail_chunks_ < batch_size ? (size_t) tail_chunks_ : batch_size;
+    }
+    const size_t tail = chunks > 1 ? ((size_t) tail_layers_ < L ? (size_t) tail_layers_ : L) : 0;
+    const size_t per_chunk = (batch_size + chunks - 1) / chunks;
+    if (L - tail > 0) {
+        const GraphKey key{batch_size, 0, d_ids, d_mask, d_seg, kHeadLayers, 0, L - tail};
+        run_graph(key, [&] { forward_layers(0, L - tail, 0, batch_size, batch_size, d_mask, 0); });
+    }
+    size_t used = 0;
+    for (size_t c = 0; c < chunks; ++c) {
+        const size_t b0 = c * per_chunk;
+        if (b0 >= batch_size) {
+            break;
+        }
+        const size_t nb = batch_size - b0 < per_chunk ? batch_size - b0 : per_chunk;
+        if (tail > 0) {
+            const GraphKey key{batch_size, 0, d_ids, d_mask, d_seg, kTailLayers, b0, nb};
+            run_graph(key, [&] { forward_layers(L - tail, L, b0, nb, batch_size, d_mask, 0); });
+        }
+        if (out->sequence_output != nullptr) {
+            if (convert) {
+                KERNEL_CHECK(cubk_half_to_float(sequence_output_ + b0 * S * H,
+                                                float_staging_.template as<float>() + b0 * S * H,
+                                                (int64_t) (nb * S * H), stream_));
+            }
+            CUDA_CHECK(cudaEventRecord(chunk_ready_[c], stream_));
+        }
+        used = c + 1;
+    }
+    {
+        const GraphKey key{batch_size, 0, d_ids, d_mask, d_seg, kHeads, 0, 0};
+        run_graph(key, [&] { forward_heads(batch_size, d_mask, 0); });
+    }
+    auto small = [&](void *dst, const T *src, size_t count) {
+        if (dst == nullptr || src == nullptr) {
+            return;
+        }
+        if (convert) {
+            KERNEL_CHECK(cubk_half_to_float(src, float_staging_small_.template as<float>(), (int64_t) count, stream_));
+            CUDA_CHECK(cudaMemcpyAsync(dst, float_staging_small_.get(), sizeof(float) * count, cudaMemcpyDeviceToHost,
+                                       stream_));
+        } else {
+            CUDA_CHECK(cudaMemcpyAsync(dst, src, sizeof(T) * count, cudaMemcpyDeviceToHost, stream_));
+        }
+    };
+
+    // ---- ... then the large copies on the copy stream, each behind the event that makes its rows final
+    // (a copy into pageable memory blocks the calling thread; by now the GPU has all its work)
+    if (out->embedding_output != nullptr) {
+        CUDA_CHECK(cudaStreamWaitEvent(copy_stream_, embed_ready_, 0));
+        CUDA_CHECK(cudaMemcpyAsync(out->embedding_output, embedding_src, tokens * H * out_elem, cudaMemcpyDeviceToHost,
+                                   copy_stream_));
+    }
+    if (out->sequence_output != nullptr) {
+        const char *src = convert ? float_staging_.template as<char>() : reinterpret_cast<const char *>(sequence_output_);
+        for (size_t c = 0; c < used; ++c) {
+            const size_t b0 = c * per_chunk;
+            const size_t nb = batch_size - b0 < per_chunk ? batch_size - b0 : per_chunk;
+            const size_t off = b0 * S * H * out_elem;
+            CUDA_CHECK(cudaStreamWaitEvent(copy_stream_, chunk_ready_[c], 0));
+            CUDA_CHECK(cudaMemcpyAsync(static_cast<char *>(out->sequence_output) + off, src + off, nb * S * H * out_elem,
+                                       cudaMemcpyDeviceToHost, copy_stream_));
+        }
+    }
+    small(out->logits, has_classifier_ ? logits_.template as<T>() : nullptr, batch_size * num_labels);
+    small(out->probs, has_classifier_ ? probs_.template as<T>() : nullptr, batch_size * num_labels);
+    small(out->pooled_output, pooled_.template as<T>(), batch_size * H);
+    CUDA_CHECK(cudaStreamSynchronize(stream_));
+    CUDA_CHECK(cudaStreamSynchronize(copy_stream_));
 }
 
 template <typename T>

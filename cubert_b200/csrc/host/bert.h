@@ -13,6 +13,7 @@
 #pragma once
 
 #include <array>
+#include <functional>
 #include <map>
 #include <tuple>
 #include <memory>
@@ -54,6 +55,14 @@ public:
     // With to_float, a binary16 model converts on the device first (Bert.cpp:218-259 does it on the host).
     void output(size_t batch_size, cuBERT_Output *out, bool to_float);
 
+    // compute() followed by output(), as one call. For a large request that wants sequence_output, the
+    // last encoder layers run sub-batch by sub-batch and each sub-batch's rows start their device-to-host
+    // copy on a second stream as soon as they are final, while the next sub-batch is computed;
+    // embedding_output leaves right after the embedding kernel. Results are those of the plain pass.
+    // CUBERT_TAIL_CHUNKS (sub-batches, default 4, 1 = off) and CUBERT_TAIL_LAYERS (default 2) tune it.
+    void compute_output(size_t batch_size, const int *input_ids, const int8_t *input_mask,
+                        const int8_t *segment_ids, cuBERT_Output *out, bool to_float);
+
     void synchronize();
     cuBERT_Output device_outputs() const;
     cudaStream_t stream() const { return stream_; }
@@ -86,6 +95,11 @@ private:
     // pooled_output, logits and probs are the same as in the full computation.
     void forward(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments,
                  size_t packed);
+    // its three parts: embeddings, a range of encoder layers on a range of sequences, pooler + classifier
+    void forward_embed(size_t batch_size, const int32_t *d_ids, const int8_t *d_segments, size_t packed);
+    void forward_layers(size_t l_begin, size_t l_end, size_t b0, size_t nb, size_t batch_size, const int8_t *d_mask,
+                        size_t packed);
+    void forward_heads(size_t batch_size, const int8_t *d_mask, size_t packed);
 
     // The forward pass as a CUDA graph, captured on first use per (batch size, input addresses) and
     // replayed afterwards: about 125 kernel launches collapse into one graph launch, which removes
@@ -93,18 +107,23 @@ private:
     // the environment variable CUBERT_CUDA_GRAPH=0.
     void run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments,
              size_t packed);
+    enum Phase { kWholePass = 0, kHeadLayers, kTailLayers, kHeads };
     struct GraphKey {
         size_t batch, packed;
         const void *ids, *mask, *segments;
+        int phase;        // which part of the pass the graph holds
+        size_t b0, nb;    // kTailLayers: the sequences it covers
         bool operator<(const GraphKey &o) const {
-            return std::tie(batch, packed, ids, mask, segments) <
-                   std::tie(o.batch, o.packed, o.ids, o.mask, o.segments);
+            return std::tie(batch, packed, ids, mask, segments, phase, b0, nb) <
+                   std::tie(o.batch, o.packed, o.ids, o.mask, o.segments, o.phase, o.b0, o.nb);
         }
     };
     struct GraphEntry {
         cudaGraphExec_t exec = nullptr;
         int seen = 0;  // calls with this key so far; the first runs eagerly, the second captures
+        std::array<int64_t, CUBERT_B200_K_COUNT> launches{};  // launches per family inside the graph
     };
+    void run_graph(const GraphKey &key, const std::function<void()> &body);
     std::map<GraphKey, GraphEntry> graphs_;
     bool use_graphs_ = true;
 
@@ -137,6 +156,14 @@ private:
     DeviceBuffer token_index_, first_index_, qkv_packed_, ctx_packed_, first_rows_;
     size_t build_token_index(size_t batch_size, const int8_t *input_mask);
     T *sequence_output_ = nullptr;
+
+    // overlapped output copies
+    static constexpr size_t kMaxTailChunks = 8;
+    int tail_chunks_ = 4, tail_layers_ = 2;
+    cudaStream_t copy_stream_ = nullptr;
+    cudaEvent_t embed_ready_ = nullptr;
+    cudaEvent_t chunk_ready_[kMaxTailChunks] = {};
+    DeviceBuffer float_staging_embedding_, float_staging_small_;  // float32 conversions of the overlapped path
 
     int algo_attention_, algo_intermediate_, algo_output_, algo_pooler_, algo_qk_, algo_qkv_;
 

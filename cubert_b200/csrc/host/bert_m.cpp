@@ -83,10 +83,9 @@ unsigned int BertM<T>::compute(size_t batch_size, int *input_ids, int8_t *input_
     const unsigned int choice = (unsigned int) (rr.fetch_add(1) % bert_instances.size());
     Bert<T> *bert = bert_instances[choice].get();
     std::lock_guard<std::mutex> lg(*mutex_instances[choice]);
-    // Only when no per-position output is wanted may the replica skip padding tokens.
-    const bool all_positions = output->sequence_output != nullptr || output->embedding_output != nullptr;
-    bert->compute(batch_size, input_ids, input_mask, segment_ids, all_positions);
-    bert->output(batch_size, output, output_to_float);
+    // Only when no per-position output is wanted may the replica skip padding tokens; when one is
+    // wanted, its device-to-host copy overlaps the computation (Bert::compute_output).
+    bert->compute_output(batch_size, input_ids, input_mask, segment_ids, output, output_to_float);
     return choice;
 }
 

@@ -382,6 +382,60 @@ def test_through_the_references_own_python_wrapper(model_files, reference_python
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("ct", [model.ComputeType.FLOAT, model.ComputeType.HALF])
+@pytest.mark.parametrize("chunks,layers,batch", [("4", "2", 601), ("3", "1", 600), ("8", "5", 515), ("1", "2", 600),
+                                                  ("4", "0", 520)])
+def test_output_copies_overlap_the_computation(model_files, oracle, ct, chunks, layers, batch, monkeypatch):
+    """A large request that wants per-position outputs runs its last encoder layers sub-batch by sub-batch
+    and copies each sub-batch's rows out while the next is computed; embedding_output leaves right after
+    the embedding kernel. Every output of every sequence must be what the plain pass gives: uneven
+    splits, more tail layers than the model has, no tail layers, repeated calls (graphs replayed),
+    float32 conversion, and a smaller request afterwards."""
+    path, cfg, var = model_files["small"]
+    S = 32
+    ids, mask, seg, _ = synthetic.random_inputs(cfg, batch, S, 23, lengths=(3, S), segments="random")
+    dt = np.float32 if ct == model.ComputeType.FLOAT else np.float16
+    tol = 1e-5 if ct == model.ComputeType.FLOAT else 4e-3
+
+    monkeypatch.setenv("CUBERT_TAIL_CHUNKS", "1")
+    plain = model.Model(path, batch, S, cfg["layers"], cfg["heads"], ct)
+    want = {}
+    for name, kind, shape in (("sequence_output", model.OutputType.SEQUENCE_OUTPUT, (batch, S, cfg["hidden"])),
+                              ("pooled_output", model.OutputType.POOLED_OUTPUT, (batch, cfg["hidden"])),
+                              ("logits", model.OutputType.LOGITS, (batch, 2)),
+                              ("probs", model.OutputType.PROBS, (batch, 2))):
+        want[name] = np.zeros(shape, dt)
+        plain.compute(ids, mask, seg, want[name], kind)     # one output at a time: the plain path
+    plain.close()
+
+    monkeypatch.setenv("CUBERT_TAIL_CHUNKS", chunks)
+    monkeypatch.setenv("CUBERT_TAIL_LAYERS", layers)
+    m = model.Model(path, batch, S, cfg["layers"], cfg["heads"], ct)
+    for to_float in (False, True):
+        for _ in range(3):   # eager, captured, replayed
+            got = _run(m, ids, mask, seg, cfg, to_float=to_float)
+            for k, ref in want.items():
+                assert got[k].dtype == (np.float32 if to_float else dt)
+                assert rel_err(got[k], ref) < tol, (k, to_float, rel_err(got[k], ref))
+    if ct == model.ComputeType.FLOAT:
+        truth = oracle.bert_forward(var, synthetic.model_geometry(cfg, S), ids, mask, seg)
+        for k in got:
+            assert rel_err(got[k], truth[k]) < 1e-5, (k, rel_err(got[k], truth[k]))
+    else:
+        r16 = lambda n: var["bert/embeddings/" + n].astype(np.float16).astype(np.float32)  # noqa: E731
+        truth = oracle.bert_embeddings(ids, seg, r16("word_embeddings"), r16("position_embeddings")[:S],
+                                       r16("token_type_embeddings"), r16("LayerNorm/beta"), r16("LayerNorm/gamma"))
+        assert rel_err(got["embedding_output"], truth.reshape(batch, S, -1)) < 2e-3
+    # a smaller request afterwards, sequence_output alone
+    nb = batch // 2 + 1
+    out = model.Output()
+    out.sequence_output = np.zeros((nb, S, cfg["hidden"]), dt)
+    m.compute_m(ids[:nb], mask[:nb], seg[:nb], out)
+    assert rel_err(out.sequence_output, want["sequence_output"][:nb]) < tol
+    m.close()
+
+
+@pytest.mark.gpu
 def test_float32_products_on_tensor_cores_keep_float32_accuracy(tmp_path, oracle, monkeypatch):
     """A float32 model's cuBLAS products run, where cuBLAS offers it, as three-way bfloat16 splits on the
     tensor cores. Both ways must stay within the float32 bar of the oracle, on BERT-base geometry

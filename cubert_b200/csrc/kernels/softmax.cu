@@ -6,10 +6,12 @@
 // 16-byte vectors per lane, and every lane group works on ROWS rows at once so that
 // ROWS * VPT independent 128-bit loads are in flight per thread. Short rows (seq 32 in
 // binary16 is 64 bytes) therefore still produce 512-byte contiguous warp accesses. Blocks
-// are bound to one batch entry: a thread reads its columns of the int8 [batch, seq] mask
-// once, keeps them as additive float terms in registers and reuses them for every row it
-// handles; the reference's score-sized broadcast mask tensor never exists. Arithmetic is
+// are bound to one batch entry: its columns of the int8 [batch, seq] mask are turned into
+// additive float terms once (in registers for short rows, in shared memory for long ones) and
+// reused for every row of that entry; the reference's score-sized broadcast mask tensor never exists. Arithmetic is
 // float32 issued as packed .f32x2. HBM traffic: one read and one write of the score matrix.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace cubk {
@@ -43,12 +45,16 @@ __device__ __forceinline__ void load_mask_add<__half>(const int8_t *mask_row, in
 // rows share one mask row). Every block takes a contiguous range of items, so it changes batch
 // entry rarely; when it does, each thread converts its columns of the mask into additive terms,
 // which then stay in registers for all the rows that follow.
-template <typename T, int LPR, int VPT, int ROWS, int BLOCK>
+// MASK_SMEM: the additive terms live in shared memory (float32, [EPV/4][nvec] so that 128-bit reads
+// are conflict-free) instead of in registers; long rows then need half the registers, and twice as
+// many warps stay resident.
+template <typename T, int LPR, int VPT, int ROWS, int BLOCK, bool MASK_SMEM>
 __global__ void __launch_bounds__(BLOCK)
 masked_softmax_kernel(const T *scores, const int8_t *mask, T *out, uint32_t rows_per_batch, int seq, int nvec,
                       float scale, uint32_t total_items, FastDiv items_per_batch) {
     constexpr int EPV = Vec<T>::EPV;
     constexpr int PAIRS = Vec2<T>::PAIRS;
+    extern __shared__ float4 s_madd[];
     constexpr int GPW = 32 / LPR;                          // row groups per warp
     constexpr int ROWS_PER_BLOCK = (BLOCK / 32) * GPW * ROWS;  // rows of one item
     const int lane = threadIdx.x & 31;
@@ -62,9 +68,9 @@ masked_softmax_kernel(const T *scores, const int8_t *mask, T *out, uint32_t rows
     const uint32_t item_begin = blockIdx.x * share + min(blockIdx.x, extra);
     const uint32_t item_end = item_begin + share + (blockIdx.x < extra ? 1u : 0u);
 
-    float2 madd[VPT][PAIRS];
+    float2 madd[MASK_SMEM ? 1 : VPT][PAIRS];
 #pragma unroll
-    for (int k = 0; k < VPT; ++k) {
+    for (int k = 0; k < (MASK_SMEM ? 1 : VPT); ++k) {
 #pragma unroll
         for (int e = 0; e < PAIRS; ++e) {
             madd[k][e] = make_float2(0.f, 0.f);
@@ -76,11 +82,31 @@ masked_softmax_kernel(const T *scores, const int8_t *mask, T *out, uint32_t rows
 
     for (uint32_t item = item_begin; item < item_end; ++item) {
         const uint32_t b = fast_div(item, items_per_batch);
+        if (b != cur_b && MASK_SMEM) {  // uniform over the block: all its threads walk the same items
+            cur_b = b;
+            __syncthreads();  // the previous entry's terms are no longer read
+            for (int idx = threadIdx.x; idx < nvec; idx += BLOCK) {
+                float add[EPV];
+                if (mask != nullptr) {
+                    load_mask_add<T>(mask + (size_t) b * seq, idx, add);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) {
+                        add[e] = 0.f;
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < EPV / 4; ++q) {
+                    s_madd[q * nvec + idx] = make_float4(add[4 * q], add[4 * q + 1], add[4 * q + 2], add[4 * q + 3]);
+                }
+            }
+            __syncthreads();
+        }
         if (b != cur_b) {
             cur_b = b;
             if (mask != nullptr) {
 #pragma unroll
-                for (int k = 0; k < VPT; ++k) {
+                for (int k = 0; k < (MASK_SMEM ? 0 : VPT); ++k) {
                     const int idx = l + k * LPR;
                     if (idx < nvec) {
                         float add[EPV];
@@ -120,9 +146,18 @@ masked_softmax_kernel(const T *scores, const int8_t *mask, T *out, uint32_t rows
             for (int k = 0; k < VPT; ++k) {
                 Vec2<T>::unpack(raw[r][k], v[k]);
                 if (l + k * LPR < nvec) {
+                    float2 m[PAIRS];
+                    if (MASK_SMEM) {
+#pragma unroll
+                        for (int q = 0; q < EPV / 4; ++q) {
+                            const float4 f = s_madd[q * nvec + l + k * LPR];
+                            m[2 * q] = make_float2(f.x, f.y);
+                            m[2 * q + 1] = make_float2(f.z, f.w);
+                        }
+                    }
 #pragma unroll
                     for (int e = 0; e < PAIRS; ++e) {
-                        v[k][e] = fma2(scale2, v[k][e], madd[k][e]);
+                        v[k][e] = fma2(scale2, v[k][e], MASK_SMEM ? m[e] : madd[MASK_SMEM ? 0 : k][e]);
                         mx = fmaxf(mx, fmaxf(v[k][e].x, v[k][e].y));
                     }
                 }
@@ -197,6 +232,16 @@ masked_softmax_generic_kernel(const T *scores, const int8_t *mask, T *out, int64
     }
 }
 
+// Rows of four or more vectors per lane keep the additive mask terms in shared memory by default.
+// Inside a BERT step, where the GEMMs hold the GPU at its power cap (SM clock 1.3-1.6 GHz), the lower
+// register count wins: BERT-large seq 512 binary16 1621 -> 1496 us per launch, BERT-base seq 128
+// 34.1 -> 32.7 us. Timed alone at 1.9 GHz the register variant is ahead (1353 against 1410 us on the
+// same 8.6 GB). CUBK_SOFTMAX_MASK_SMEM=0 selects the register variant.
+static bool mask_in_smem() {
+    const char *v = getenv("CUBK_SOFTMAX_MASK_SMEM");
+    return v == nullptr || v[0] != '0';
+}
+
 template <typename T>
 int masked_softmax(const T *scores, const int8_t *mask, int64_t rows, int64_t rows_per_batch, int seq,
                    float scale, T *out, cudaStream_t stream) {
@@ -220,19 +265,23 @@ int masked_softmax(const T *scores, const int8_t *mask, int64_t rows, int64_t ro
                         (mask == nullptr || aligned8(mask)) && rows_per_batch <= 0x7fffffffLL &&
                         rows % rows_per_batch == 0;
     if (vec_ok) {
-#define LAUNCH(LPR, VPT, ROWS)                                                                          \
+#define LAUNCH_AS(LPR, VPT, ROWS, MASK_SMEM)                                                            \
     {                                                                                                   \
         static OccupancyCache cache;                                                                    \
-        auto kernel = masked_softmax_kernel<T, LPR, VPT, ROWS, BLOCK>;                                  \
+        auto kernel = masked_softmax_kernel<T, LPR, VPT, ROWS, BLOCK, MASK_SMEM>;                       \
+        const size_t smem = MASK_SMEM ? sizeof(float) * (size_t) seq : 0;                               \
         const int64_t rows_per_block = (int64_t) (BLOCK / 32) * (32 / LPR) * ROWS;                      \
         const int64_t per_batch = (rows_per_batch + rows_per_block - 1) / rows_per_block;               \
         const int64_t items = per_batch * batches;                                                      \
-        int64_t grid = resident_blocks(kernel, BLOCK, 0, &cache);                                       \
+        int64_t grid = resident_blocks(kernel, BLOCK, smem, &cache);                                    \
         if (grid > items) grid = items;                                                                 \
-        kernel<<<(unsigned) grid, BLOCK, 0, stream>>>(scores, mask, out, (uint32_t) rows_per_batch,     \
-                                                      seq, nvec, scale, (uint32_t) items,               \
-                                                      make_fastdiv((uint32_t) per_batch));              \
+        kernel<<<(unsigned) grid, BLOCK, smem, stream>>>(scores, mask, out, (uint32_t) rows_per_batch,  \
+                                                         seq, nvec, scale, (uint32_t) items,            \
+                                                         make_fastdiv((uint32_t) per_batch));           \
     }
+#define LAUNCH(LPR, VPT, ROWS) LAUNCH_AS(LPR, VPT, ROWS, false)
+#define LAUNCH_LONG(LPR, VPT, ROWS)                                  \
+    if (mask_in_smem()) LAUNCH_AS(LPR, VPT, ROWS, true) else LAUNCH_AS(LPR, VPT, ROWS, false)
         if (nvec <= 1) {
             LAUNCH(1, 1, 4);
         } else if (nvec <= 2) {
@@ -242,17 +291,20 @@ int masked_softmax(const T *scores, const int8_t *mask, int64_t rows, int64_t ro
         } else if (nvec <= 8) {
             LAUNCH(8, 1, 4);
         } else if (nvec <= 16) {
-            LAUNCH(4, 4, 1);  // fewer lanes per row: 2 shuffle steps per reduction instead of 4
+            // fewer lanes per row: 2 shuffle steps per reduction instead of 4
+            LAUNCH_LONG(4, 4, 1)
         } else if (nvec <= 32) {
             LAUNCH(32, 1, 4);
         } else if (nvec <= 64) {
-            LAUNCH(16, 4, 1);
+            LAUNCH_LONG(16, 4, 1)
         } else if (nvec <= 128) {
-            LAUNCH(32, 4, 1);
+            LAUNCH_LONG(32, 4, 1)
         } else {
-            LAUNCH(32, 8, 1);
+            LAUNCH_LONG(32, 8, 1)
         }
+#undef LAUNCH_LONG
 #undef LAUNCH
+#undef LAUNCH_AS
     } else {
         const int64_t grid = (rows + 3) / 4;
         masked_softmax_generic_kernel<T><<<(unsigned) grid, 128, 0, stream>>>(scores, mask, out, rows,

@@ -151,7 +151,7 @@ def measured_peak():
 NCU_TRAFFIC_BYTES = {
     "bias_gelu": 347537280,         # 201.4 MB read + 146.2 MB written (rest of the output still in L2)
     "bias_residual_ln": 108957440,  # 100.7 MB read + 8.3 MB written
-    "masked_softmax": 148045312,    # 100.7 MB read + 47.3 MB written
+    "masked_softmax": 147773000,    # 100.7 MB read + 47.1 MB written
     "embed_ln": 29354880,           # 26.0 MB read + 3.3 MB written: word rows are served by L2
 }
 

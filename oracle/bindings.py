@@ -61,6 +61,21 @@ def build_pywrap():
     return PYWRAP_DIR
 
 
+REF_HOST_B200_SO = os.path.join(HERE, "_ref", "libcubert_ref_host_b200.so")
+
+
+def build_host_b200():
+    """Link the reference's own GPU host code (HAVE_CUDA build of Bert, Transformer, Dense, ...) with
+    ref_host_b200_ops.cu, which serves its operator templates from OUR kernel library. Returns the
+    path of the library, or None where it cannot be built (reference tree absent)."""
+    if not os.path.exists(REF_HOST_B200_SO):
+        if not reference_tree_present():
+            return None
+        subprocess.run(["make", "-C", HERE, "REF=" + REFERENCE_SRC, "ref_host_b200"], check=True,
+                       stdout=subprocess.DEVNULL)
+    return REF_HOST_B200_SO
+
+
 BENCHMARK_BIN = os.path.join(HERE, "_ref", "benchmark_cu")
 
 
@@ -461,3 +476,48 @@ class ReferenceGPU:
 
     def fn(self, name, t):
         return getattr(self.lib, "refgpu_%s_%s" % (name, t))
+
+
+class ReferenceHostOnOurKernels:
+    """The reference's own Bert<T> host class (GPU build) running on this repository's kernels
+    (oracle/_ref/libcubert_ref_host_b200.so). Host arrays in, host arrays out; needs a GPU."""
+
+    def __init__(self):
+        if not os.path.exists(REF_HOST_B200_SO):
+            raise FileNotFoundError(REF_HOST_B200_SO)
+        self.lib = C.CDLL(REF_HOST_B200_SO)
+        P, I = C.c_void_p, C.c_int
+        self.lib.refhost_open.restype = P
+        self.lib.refhost_open.argtypes = [I, C.POINTER(C.c_char_p), C.POINTER(P), I, I, I, I, I, I, I, I, I, I]
+        self.lib.refhost_compute.argtypes = [P, I, I, P, P, P]
+        self.lib.refhost_output.argtypes = [P, I, I, P, P, P, P, P]
+        self.lib.refhost_close.argtypes = [P, I]
+
+    def forward(self, var, cfg, ids, mask, seg, half=False):
+        """var: name -> float32 array (rounded to binary16 here when `half`); cfg as model_geometry()."""
+        dt = np.float16 if half else np.float32
+        keep = {k: np.ascontiguousarray(v, dtype=dt) for k, v in var.items()}
+        names = (C.c_char_p * len(keep))(*[k.encode() for k in keep])
+        ptrs = (C.c_void_p * len(keep))(*[v.ctypes.data for v in keep.values()])
+        batch = ids.shape[0]
+        h = self.lib.refhost_open(len(keep), names, ptrs, int(half), batch, cfg["seq"], cfg["vocab"],
+                                  cfg["type_vocab"], cfg["hidden"], cfg["layers"], cfg["heads"],
+                                  cfg["intermediate"], cfg.get("num_labels", 1))
+        ids = np.ascontiguousarray(ids, np.int32).copy()
+        mask = np.ascontiguousarray(mask, np.int8).copy()
+        seg = np.ascontiguousarray(seg, np.int8).copy()
+        s, hid, labels = cfg["seq"], cfg["hidden"], cfg.get("num_labels", 1)
+        out = {"embedding_output": np.empty((batch, s, hid), dt), "sequence_output": np.empty((batch, s, hid), dt),
+               "pooled_output": np.empty((batch, hid), dt)}
+        if "output_weights" in var:
+            out["logits"] = np.empty((batch, labels), dt)
+            out["probs"] = np.empty((batch, labels), dt)
+        addr = lambda a: a.ctypes.data if a is not None else None  # noqa: E731
+        try:
+            self.lib.refhost_compute(h, int(half), batch, ids.ctypes.data, mask.ctypes.data, seg.ctypes.data)
+            self.lib.refhost_output(h, int(half), batch, addr(out.get("logits")), addr(out.get("probs")),
+                                    addr(out["pooled_output"]), addr(out["sequence_output"]),
+                                    addr(out["embedding_output"]))
+        finally:
+            self.lib.refhost_close(h, int(half))
+        return out

@@ -487,3 +487,32 @@ def test_the_references_own_benchmark_program(tmp_path):
     values = np.loadtxt(str(tmp_path / "cuBERT.txt"), dtype=np.float64)
     assert values.size == 20 * 128 * 768
     assert np.all(np.isfinite(values)) and np.all(np.abs(values) <= 1.0) and values.std() > 1e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", list(CASES))
+def test_the_references_own_host_code_on_our_kernels(model_files, oracle, name):
+    """The inner drop-in boundary: the reference's unmodified GPU host code (Bert, Transformer,
+    AttentionSelf, Dense, BatchMatMul, its cuBLAS wrappers) linked with oracle/ref_host_b200_ops.cu, which
+    defines the reference's operator templates (layer_norm_, softmax_, gelu, embedding, _not, tanh_,
+    reduce_mean_1) as calls into this repository's launch layer. float32 must reproduce the reference's
+    CPU results (golden fixtures) to 1e-5; binary16 must stay within the binary16 bars."""
+    from cubert_b200 import build as native
+    from oracle import bindings
+    native.build_all(verbose=False)
+    if bindings.build_host_b200() is None:
+        pytest.skip("reference host library not built (reference tree absent)")
+    host = bindings.ReferenceHostOnOurKernels()
+    path, cfg, var = model_files[name]
+    g = golden(name)
+    ids, mask, seg = g["ids"], g["mask"], g["seg"]
+    geo = synthetic.model_geometry(cfg, ids.shape[1])
+    got = host.forward(var, geo, ids, mask, seg)
+    for k in got:
+        assert rel_err(got[k], g[k]) < 1e-5, (k, rel_err(got[k], g[k]))
+    var16 = {k: v.astype(np.float16).astype(np.float32) for k, v in var.items()}
+    ref16 = oracle.bert_forward(var16, geo, ids, mask, seg)
+    got16 = host.forward(var, geo, ids, mask, seg, half=True)
+    for k in got16:
+        assert got16[k].dtype == np.float16
+        assert np.max(np.abs(got16[k].astype(np.float32) - ref16[k])) < (1e-2 if k in ("probs", "pooled_output") else 6e-2), k

@@ -478,14 +478,29 @@ class ReferenceGPU:
         return getattr(self.lib, "refgpu_%s_%s" % (name, t))
 
 
-class ReferenceHostOnOurKernels:
-    """The reference's own Bert<T> host class (GPU build) running on this repository's kernels
-    (oracle/_ref/libcubert_ref_host_b200.so). Host arrays in, host arrays out; needs a GPU."""
+REF_GPU_FULL_SO = os.path.join(HERE, "_ref", "libcubert_ref_gpu_full.so")
 
-    def __init__(self):
-        if not os.path.exists(REF_HOST_B200_SO):
-            raise FileNotFoundError(REF_HOST_B200_SO)
-        self.lib = C.CDLL(REF_HOST_B200_SO)
+
+def build_gpu_full():
+    """The reference's complete GPU build (its host code and its own .cu files) for sm_100a. Returns the
+    path of the library, or None where it cannot be built (reference tree absent)."""
+    if not os.path.exists(REF_GPU_FULL_SO):
+        if not reference_tree_present():
+            return None
+        subprocess.run(["make", "-C", HERE, "REF=" + REFERENCE_SRC, "ref_gpu_full"], check=True,
+                       stdout=subprocess.DEVNULL)
+    return REF_GPU_FULL_SO
+
+
+class ReferenceHost:
+    """The reference's own Bert<T> host class in its GPU build, behind ref_host_b200_driver.cpp: either on
+    this repository's kernels (REF_HOST_B200_SO) or on the reference's own (REF_GPU_FULL_SO).
+    Host arrays in, host arrays out; needs a GPU."""
+
+    def __init__(self, library):
+        if not os.path.exists(library):
+            raise FileNotFoundError(library)
+        self.lib = C.CDLL(library)
         P, I = C.c_void_p, C.c_int
         self.lib.refhost_open.restype = P
         self.lib.refhost_open.argtypes = [I, C.POINTER(C.c_char_p), C.POINTER(P), I, I, I, I, I, I, I, I, I, I]
@@ -493,31 +508,42 @@ class ReferenceHostOnOurKernels:
         self.lib.refhost_output.argtypes = [P, I, I, P, P, P, P, P]
         self.lib.refhost_close.argtypes = [P, I]
 
-    def forward(self, var, cfg, ids, mask, seg, half=False):
+    def open(self, var, cfg, max_batch, half=False):
         """var: name -> float32 array (rounded to binary16 here when `half`); cfg as model_geometry()."""
         dt = np.float16 if half else np.float32
         keep = {k: np.ascontiguousarray(v, dtype=dt) for k, v in var.items()}
         names = (C.c_char_p * len(keep))(*[k.encode() for k in keep])
         ptrs = (C.c_void_p * len(keep))(*[v.ctypes.data for v in keep.values()])
-        batch = ids.shape[0]
-        h = self.lib.refhost_open(len(keep), names, ptrs, int(half), batch, cfg["seq"], cfg["vocab"],
+        h = self.lib.refhost_open(len(keep), names, ptrs, int(half), max_batch, cfg["seq"], cfg["vocab"],
                                   cfg["type_vocab"], cfg["hidden"], cfg["layers"], cfg["heads"],
                                   cfg["intermediate"], cfg.get("num_labels", 1))
+        return dict(handle=h, half=int(half), dtype=dt, cfg=cfg, classifier="output_weights" in var, keep=keep)
+
+    def compute(self, m, ids, mask, seg):
+        """ids int32, mask int8, seg int8, C-contiguous [batch, seq]."""
+        self.lib.refhost_compute(m["handle"], m["half"], ids.shape[0], ids.ctypes.data, mask.ctypes.data, seg.ctypes.data)
+
+    def output(self, m, batch, names=("embedding_output", "sequence_output", "pooled_output", "logits", "probs")):
+        cfg, dt = m["cfg"], m["dtype"]
+        s, hid, labels = cfg["seq"], cfg["hidden"], cfg.get("num_labels", 1)
+        shapes = {"embedding_output": (batch, s, hid), "sequence_output": (batch, s, hid), "pooled_output": (batch, hid),
+                  "logits": (batch, labels), "probs": (batch, labels)}
+        out = {n: np.empty(shapes[n], dt) for n in names if m["classifier"] or n not in ("logits", "probs")}
+        addr = lambda n: out[n].ctypes.data if n in out else None  # noqa: E731
+        self.lib.refhost_output(m["handle"], m["half"], batch, addr("logits"), addr("probs"), addr("pooled_output"),
+                                addr("sequence_output"), addr("embedding_output"))
+        return out
+
+    def close(self, m):
+        self.lib.refhost_close(m["handle"], m["half"])
+
+    def forward(self, var, cfg, ids, mask, seg, half=False):
         ids = np.ascontiguousarray(ids, np.int32).copy()
         mask = np.ascontiguousarray(mask, np.int8).copy()
         seg = np.ascontiguousarray(seg, np.int8).copy()
-        s, hid, labels = cfg["seq"], cfg["hidden"], cfg.get("num_labels", 1)
-        out = {"embedding_output": np.empty((batch, s, hid), dt), "sequence_output": np.empty((batch, s, hid), dt),
-               "pooled_output": np.empty((batch, hid), dt)}
-        if "output_weights" in var:
-            out["logits"] = np.empty((batch, labels), dt)
-            out["probs"] = np.empty((batch, labels), dt)
-        addr = lambda a: a.ctypes.data if a is not None else None  # noqa: E731
+        m = self.open(var, cfg, ids.shape[0], half)
         try:
-            self.lib.refhost_compute(h, int(half), batch, ids.ctypes.data, mask.ctypes.data, seg.ctypes.data)
-            self.lib.refhost_output(h, int(half), batch, addr(out.get("logits")), addr(out.get("probs")),
-                                    addr(out["pooled_output"]), addr(out["sequence_output"]),
-                                    addr(out["embedding_output"]))
+            self.compute(m, ids, mask, seg)
+            return self.output(m, ids.shape[0])
         finally:
-            self.lib.refhost_close(h, int(half))
-        return out
+            self.close(m)

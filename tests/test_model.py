@@ -502,7 +502,7 @@ def test_the_references_own_host_code_on_our_kernels(model_files, oracle, name):
     native.build_all(verbose=False)
     if bindings.build_host_b200() is None:
         pytest.skip("reference host library not built (reference tree absent)")
-    host = bindings.ReferenceHostOnOurKernels()
+    host = bindings.ReferenceHost(bindings.REF_HOST_B200_SO)
     path, cfg, var = model_files[name]
     g = golden(name)
     ids, mask, seg = g["ids"], g["mask"], g["seg"]

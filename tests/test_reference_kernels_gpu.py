@@ -154,3 +154,80 @@ def test_one_layer_of_non_gemm_work_against_the_reference_kernels(refgpu, t):
         with open(os.path.join(out_dir, "vs_reference_kernels_%s.json" % t), "w") as f:
             json.dump(line, f)
     assert lib is not None and our_us < ref_us, line
+
+
+# ============================================================================ whole model: the reference's GPU build
+
+@pytest.mark.parametrize("name,half", [("base_seq32", False), ("base_seq128", True)])
+def test_whole_model_against_the_references_gpu_build(name, half, tmp_path):
+    """The reference's complete GPU build (its host code and its own kernels, compiled for sm_100a by
+    `make -C oracle ref_gpu_full`) and this library on the same B200, same weights, same inputs, both
+    through their host-buffer API: parity of every output, and the time per call side by side, once
+    with pooled_output alone copied back (where this library skips padding) and once with sequence_output too. base_seq32: BERT-base float32, batch 128, seq 32 (the reference's
+    published case); base_seq128: binary16 storage, batch 256, seq 128, valid length U[8,128]."""
+    import time
+    from cubert_b200 import frozen_graph, model, synthetic
+    from oracle import bindings
+    if bindings.build_gpu_full() is None:
+        pytest.skip("reference GPU build not available (reference tree absent at build time)")
+    cfg = synthetic.config("base")
+    if half:
+        B, Sq, seed, lengths = 256, 128, 2, (8, 128)
+    else:
+        B, Sq, seed, lengths = 128, 32, 0, "full"
+    var = synthetic.random_weights(cfg, seed)
+    ids, mask, seg, _ = synthetic.random_inputs(cfg, B, Sq, seed, lengths=lengths)
+    geo = synthetic.model_geometry(cfg, Sq)
+
+    ref = bindings.ReferenceHost(bindings.REF_GPU_FULL_SO)
+    rm = ref.open(var, geo, B, half)
+    ref.compute(rm, ids, mask, seg)
+    want = ref.output(rm, B)
+
+    path = str(tmp_path / "m.pb")
+    frozen_graph.write_frozen_graph(path, {k: v.astype(np.float16) for k, v in var.items()} if half else var)
+    m = model.Model(path, B, Sq, cfg["layers"], cfg["heads"], model.ComputeType.HALF if half else model.ComputeType.FLOAT)
+    dt = np.float16 if half else np.float32
+    out = model.Output()
+    for k, v in want.items():
+        setattr(out, k, np.zeros(v.shape, dt))
+    m.compute_m(ids, mask, seg, out)
+    for k, v in want.items():
+        got = getattr(out, k).astype(np.float64)
+        err = float(np.max(np.abs(got - v.astype(np.float64))))
+        scale = float(np.sqrt(np.mean(v.astype(np.float64) ** 2))) + 1e-30
+        if half:
+            # both sides round to binary16 at different places (the reference after every operator)
+            assert err < (2e-2 if k in ("probs", "pooled_output", "logits") else 1e-1), (k, err)
+        else:
+            # the reference's GPU kernels use fast-math intrinsics (__expf, erff approximations)
+            assert err / scale < 2e-4, (k, err / scale)
+
+    def per_call(fn, n=10):
+        for _ in range(3):
+            fn()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            fn()
+        return (time.perf_counter() - t0) / n * 1e3
+
+    timings = {}
+    for label, names in (("pooled_output", ("pooled_output",)), ("sequence_output + pooled_output",
+                                                                  ("sequence_output", "pooled_output"))):
+        req = model.Output()
+        for k in names:
+            setattr(req, k, np.zeros(want[k].shape, dt))
+        ref_ms = per_call(lambda: (ref.compute(rm, ids, mask, seg), ref.output(rm, B, names=names)))
+        our_ms = per_call(lambda: m.compute_m(ids, mask, seg, req))
+        timings[label] = dict(reference_gpu_ms_per_call=ref_ms, ours_ms_per_call=our_ms, speedup=ref_ms / our_ms)
+    ref.close(rm)
+    m.close()
+    line = dict(workload=name, dtype="f16" if half else "f32", batch=B, seq=Sq, api="host buffers in and out",
+                outputs=timings)
+    print("\nwhole model against the reference's GPU build:", json.dumps(line))
+    out_dir = os.environ.get("CUBERT_TEST_ARTIFACTS", "")
+    if out_dir and os.path.isdir(out_dir):
+        with open(os.path.join(out_dir, "vs_reference_gpu_build_%s.json" % name), "w") as f:
+            json.dump(line, f)
+    for t in timings.values():
+        assert t["ours_ms_per_call"] < t["reference_gpu_ms_per_call"], line

@@ -286,8 +286,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // (each poll may itself block for a hardware-defined short time). Returns false on give-up.
 constexpr uint32_t kMaxBarrierPolls = 1u << 22;
 
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kMaxBarrierPolls; ++i) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, uint32_t polls = kMaxBarrierPolls) {
+    for (uint32_t i = 0; i < polls; ++i) {
         if (mbar_try_wait(bar, parity)) {
             return true;
         }

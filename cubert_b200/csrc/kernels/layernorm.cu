@@ -501,6 +501,26 @@ embed_ln_bulk_kernel(const int32_t *ids, const int8_t *segment_ids, const T *wor
     }
 }
 
+// The give-up path of the bounded barrier wait, on its own: one warp waits for a phase that nothing
+// will ever complete (no copy is issued, no thread arrives), runs out of its `polls` and reports it
+// the way the staged kernels do. Nothing is in flight, so there is nothing to drain.
+__global__ void __launch_bounds__(32) copy_wait_timeout_selftest_kernel(uint32_t polls, uint32_t *status) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_init_fence();
+    }
+    __syncwarp();
+    if (!mbar_wait_bounded(&bar, 0, polls)) {
+        if (threadIdx.x == 0) {
+            atomicAdd(&g_copy_timeouts, 1u);
+            if (status != nullptr) {
+                atomicOr(status, CUBK_STATUS_COPY_TIMEOUT);
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------ generic rows (any width, any alignment)
 // One block per row, three scalar passes over the row (sum, centred squares, write).
 template <typename T>
@@ -759,6 +779,14 @@ int cubk_copy_timeouts(unsigned int *count) {
         return CUBK_ERR_LAUNCH;
     }
     return CUBK_OK;
+}
+
+int cubk_selftest_copy_wait_timeout(unsigned int polls, uint32_t *status, void *stream) {
+    if (polls == 0 || polls > 100000u) {
+        return CUBK_ERR_INVALID_ARG;
+    }
+    cubk::copy_wait_timeout_selftest_kernel<<<1, 32, 0, (cudaStream_t) stream>>>(polls, status);
+    return cubk::check_launch();
 }
 
 int cubk_bias_residual_ln_f32(const float *x, const float *bias, const float *residual, const float *gamma,

@@ -34,6 +34,7 @@ _SIGNATURES = {
     "cubk_version": (_I, []),
     "cubk_last_cuda_error": (C.c_char_p, []),
     "cubk_copy_timeouts": (_I, [_P]),
+    "cubk_selftest_copy_wait_timeout": (_I, [C.c_uint, _P, _P]),
     "cubk_embed_ln_{t}": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P]),
     "cubk_embed_gather_i32": (_I, [_P, _L, _P, _I, _I, _I, _P, _P, _P]),
     "cubk_embed_gather_i8": (_I, [_P, _L, _P, _I, _I, _I, _P, _P, _P]),

@@ -56,6 +56,12 @@ const char *cubk_last_cuda_error(void);
  * stay 0. Synchronises with the device. No counterpart in the reference. */
 int cubk_copy_timeouts(unsigned int *count);
 
+/* Exercises the give-up path of those bounded waits without any copy: one warp polls, at most `polls` times
+ * (1..100000), a barrier that nothing completes, then ORs CUBK_STATUS_COPY_TIMEOUT into *status (device word,
+ * may be NULL) and counts in cubk_copy_timeouts. The kernel always returns; the context stays usable.
+ * For tests. No counterpart in the reference. */
+int cubk_selftest_copy_wait_timeout(unsigned int polls, uint32_t *status, void *stream);
+
 /* ---- K1: embedding lookup + position/token-type add + LayerNorm --------------------------
  * out[b,s,:] = LayerNorm((word[ids[b,s]] + pos[s]) + type[segment_ids[b,s]]; gamma, beta)
  * Replaces BertEmbeddings<T>::compute (src/cuBERT/op_bert/BertEmbeddings.cpp:50-66), i.e.

@@ -293,6 +293,7 @@ def test_masked_softmax(oracle, t, kind, batch, heads, seq, mask_terms, monkeypa
                                                     (7, 33, 1536, 100)])
 def test_embed_ln(oracle, t, batch, seq, hidden, vocab, staged, monkeypatch):
     monkeypatch.setenv("CUBK_BULK_COPY", staged)
+    gave_up_before = kernels.copy_timeouts()
     rng = np.random.default_rng(hidden + vocab)
     word, wh = _prep(rng.standard_normal((vocab, hidden)) * 0.02, t)
     pos, ph = _prep(rng.standard_normal((seq + 3, hidden)) * 0.02, t)
@@ -306,7 +307,7 @@ def test_embed_ln(oracle, t, batch, seq, hidden, vocab, staged, monkeypatch):
     ref = oracle.bert_embeddings(ids, seg, wh, ph[:seq], th, beh, gh)
     _check(got, ref, t, 1.0, "embed_ln")
     assert int(status.item()) == 0
-    assert kernels.copy_timeouts() == 0
+    assert kernels.copy_timeouts() == gave_up_before
 
 
 @pytest.mark.parametrize("t", DTYPES)
@@ -314,6 +315,7 @@ def test_embed_ln_sweep_shape_with_the_default_kernel_choice(oracle, t, monkeypa
     """256 x 128 tokens, hidden 768, vocabulary 21128: float32 takes the staged kernel by default,
     binary16 the register-resident one; every token of the even split over warps is checked."""
     monkeypatch.delenv("CUBK_BULK_COPY", raising=False)
+    gave_up_before = kernels.copy_timeouts()
     batch, seq, hidden, vocab = 256, 128, 768, 21128
     rng = np.random.default_rng(1)
     word, wh = _prep(rng.standard_normal((vocab, hidden)) * 0.02, t)
@@ -328,7 +330,23 @@ def test_embed_ln_sweep_shape_with_the_default_kernel_choice(oracle, t, monkeypa
     ref = oracle.bert_embeddings(ids, seg, wh, ph[:seq], th, beh, gh)
     _check(got, ref, t, 1.0, "embed_ln 256x128")
     assert int(status.item()) == 0
-    assert kernels.copy_timeouts() == 0
+    assert kernels.copy_timeouts() == gave_up_before
+
+
+def test_a_copy_wait_that_runs_out_is_reported_and_leaves_the_context_usable():
+    """The staged kernels bound every wait for an asynchronous copy. Here a warp waits (200 polls) for a
+    barrier that nothing completes: the kernel must return, set CUBK_STATUS_COPY_TIMEOUT, count the
+    give-up, and the next launches on the same context must work."""
+    before = kernels.copy_timeouts()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kernels.check(kernels.load().cubk_selftest_copy_wait_timeout(200, G.ptr(status), G.stream()))
+    torch.cuda.synchronize()
+    assert int(status.item()) == kernels.STATUS_COPY_TIMEOUT
+    assert kernels.copy_timeouts() == before + 1
+    assert kernels.load().cubk_selftest_copy_wait_timeout(0, None, G.stream()) == kernels.CUBK_ERR_INVALID_ARG
+    x = torch.randn(64, 768, device="cuda")
+    y = G.bias_gelu(x, None, "f32")
+    assert torch.isfinite(y).all() and torch.cuda.current_stream().query() is not None
 
 
 @pytest.mark.parametrize("staged", ["0", "1"])

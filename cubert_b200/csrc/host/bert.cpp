@@ -203,6 +203,10 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
     // finite numbers (the attention products multiply them by an exact 0).
     CUDA_CHECK(cudaMemset(qkv_.get(), 0, qkv_.bytes()));
     CUDA_CHECK(cudaMemset(context_.get(), 0, context_.bytes()));
+    prune_last_layer_ = has_pooler_dense_ && num_hidden_layers > 0 && env_int("CUBERT_PRUNE_LAST_LAYER", 1) != 0;
+    if (has_pooler_dense_) {
+        first_rows_.allocate(sizeof(T) * B * H);
+    }
     skip_padding_ = has_pooler_dense_ && env_int("CUBERT_SKIP_PADDING", 1) != 0;
     if (skip_padding_) {
         CUDA_CHECK(cudaMallocHost(reinterpret_cast<void **>(&h_token_index_), sizeof(int32_t) * (R + B)));
@@ -210,7 +214,6 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
         first_index_.allocate(sizeof(int32_t) * B);
         qkv_packed_.allocate(sizeof(T) * R * 3 * H);
         ctx_packed_.allocate(sizeof(T) * R * H);
-        first_rows_.allocate(sizeof(T) * B * H);
     }
 
     // ---- pointer arrays of the batched attention products, one entry per (sequence, head).
@@ -233,6 +236,22 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
     upload(v_ptrs_, vp.data(), vp.size());
     upload(score_ptrs_, sp.data(), sp.size());
     upload(ctx_ptrs_, cp.data(), cp.size());
+    if (prune_last_layer_) {
+        // one query per sequence: compact scores [B, heads, S] at the start of scores_, context [B, hidden]
+        // at the start of context_
+        std::vector<T *> s1(B * heads), c1(B * heads);
+        std::vector<int32_t> first(B);
+        for (size_t b = 0; b < B; ++b) {
+            first[b] = (int32_t) (b * S);
+            for (size_t h = 0; h < heads; ++h) {
+                s1[b * heads + h] = scores_.template as<T>() + (b * heads + h) * S;
+                c1[b * heads + h] = context_.template as<T>() + b * H + h * d;
+            }
+        }
+        upload(score1_ptrs_, s1.data(), s1.size());
+        upload(ctx1_ptrs_, c1.data(), c1.size());
+        upload(first_index_full_, first.data(), first.size());
+    }
 
     sequence_output_ = num_hidden_layers == 0 ? embedding_.template as<T>() : hidden_[(num_hidden_layers - 1) % 2].template as<T>();
     CUDA_CHECK(cudaDeviceSynchronize());
@@ -405,7 +424,11 @@ void Bert<T>::compute(size_t batch_size, const int *input_ids, const int8_t *inp
                                        sizeof(int32_t) * batch_size, cudaMemcpyHostToDevice, stream_));
         }
     }
-    run(batch_size, ids_.template as<int32_t>(), mask_.template as<int8_t>(), segments_.template as<int8_t>(), packed);
+    // the last layer for first tokens only: when nothing per-position is wanted and the request is large
+    // enough for the saved rows to outweigh one extra gather launch
+    const bool heads_only = !all_positions && prune_last_layer_ && (packed > 0 || n >= kMinPositionsForPacking);
+    run(batch_size, ids_.template as<int32_t>(), mask_.template as<int8_t>(), segments_.template as<int8_t>(), packed,
+        heads_only);
 }
 
 template <typename T>
@@ -427,9 +450,9 @@ constexpr size_t kMaxCachedGraphs = 256;
 
 template <typename T>
 void Bert<T>::run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments,
-                  size_t packed) {
-    const GraphKey key{batch_size, packed, d_ids, d_mask, d_segments, kWholePass, 0, 0};
-    run_graph(key, [&] { forward(batch_size, d_ids, d_mask, d_segments, packed); });
+                  size_t packed, bool heads_only) {
+    const GraphKey key{batch_size, packed, d_ids, d_mask, d_segments, heads_only ? kWholePassHeadsOnly : kWholePass, 0, 0};
+    run_graph(key, [&] { forward(batch_size, d_ids, d_mask, d_segments, packed, heads_only); });
 }
 
 // Runs `body` (a sequence of launches on stream_) eagerly the first time a key is seen (cuBLASLt picks
@@ -495,10 +518,16 @@ void Bert<T>::run_graph(const GraphKey &key, const std::function<void()> &body) 
 
 template <typename T>
 void Bert<T>::forward(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments,
-                      size_t packed) {
+                      size_t packed, bool heads_only) {
     forward_embed(batch_size, d_ids, d_segments, packed);
-    forward_layers(0, num_hidden_layers, 0, batch_size, batch_size, d_mask, packed);
-    forward_heads(batch_size, d_mask, packed);
+    if (heads_only && prune_last_layer_) {
+        forward_layers(0, num_hidden_layers - 1, 0, batch_size, batch_size, d_mask, packed);
+        forward_last_layer_first_tokens(batch_size, d_mask, packed);
+        forward_heads(batch_size, d_mask, packed, true);
+    } else {
+        forward_layers(0, num_hidden_layers, 0, batch_size, batch_size, d_mask, packed);
+        forward_heads(batch_size, d_mask, packed);
+    }
 }
 
 // K1: embeddings (src/cuBERT/op_bert/BertEmbeddings.cpp:50-66); with `packed`, also the gather of the
@@ -621,10 +650,87 @@ void Bert<T>::forward_layers(size_t l_begin, size_t l_end, size_t b0, size_t nb,
     }
 }
 
+// The last encoder layer when only the first token of every sequence is read afterwards (the
+// first-token pooler): Q, K and V are still projected for every position, since every key and value
+// feeds the first token's attention, but there is ONE query per sequence, and everything after the
+// attention runs on `batch` rows. Scores [batch, heads, seq] sit at the start of scores_, the context
+// and later activations at the start of their buffers, the layer's output at the start of the
+// hidden buffer the full layer would have written. Same operations on a subset of the rows, so the
+// pooled output is the one the full layer gives.
+template <typename T>
+void Bert<T>::forward_last_layer_first_tokens(size_t batch_size, const int8_t *d_mask, size_t packed) {
+    const int B = (int) batch_size, S = (int) seq_length, H = (int) hidden_size, I = (int) intermediate_size;
+    const int heads = (int) num_attention_heads, d = H / heads;
+    const int64_t R = (int64_t) B * S;
+    const int64_t N = packed > 0 ? (int64_t) packed : R;
+    const int64_t e = sizeof(T);
+    void *st = stream_;
+    const size_t l = num_hidden_layers - 1;
+    Layer &L = layers_[l];
+    const float att_scale = (float) (1.0 / std::sqrt((double) d));
+    const T *x = l == 0 ? (packed > 0 ? hidden_[1].template as<T>() : embedding_.template as<T>())
+                        : hidden_[(l - 1) % 2].template as<T>();
+    T *y = hidden_[l % 2].template as<T>();  // [batch, hidden] here
+
+    T *qkv_out = packed > 0 ? qkv_packed_.template as<T>() : qkv_.template as<T>();
+    begin(CUBERT_B200_K_GEMM);
+    blas_->gemm_bias<T>(3 * H, (int) N, H, L.qkv_kernel.template as<T>(), 3 * H, x, H, L.qkv_bias.template as<T>(), qkv_out,
+                        3 * H);
+    end(CUBERT_B200_K_GEMM, 0);
+    if (packed > 0) {
+        KERNEL_CHECK(cubk_scatter_rows(token_index_.template as<int32_t>(), N, qkv_out, 3 * H, (int) e, qkv_.get(), (int) R, st));
+    }
+
+    // scores[b, h, j] = (1/sqrt(d)) * sum_c K[b,j,h,c] * Q[b,0,h,c]: the batched product with one column
+    begin(CUBERT_B200_K_GEMM);
+    blas_->gemm_batched<T>(true, false, S, 1, d, att_scale, k_ptrs_.template as<const T *>(), 3 * H,
+                           q_ptrs_.template as<const T *>(), 3 * H, 0.f, score1_ptrs_.template as<T *>(), S, B * heads, algo_qk_);
+    end(CUBERT_B200_K_GEMM, 0);
+    begin(CUBERT_B200_K_MASKED_SOFTMAX);
+    KERNEL_CHECK(K<T>::masked_softmax(scores_.template as<T>(), d_mask, (int64_t) B * heads, heads, S, 1.0f,
+                                      scores_.template as<T>(), st));
+    end(CUBERT_B200_K_MASKED_SOFTMAX, 2 * (int64_t) B * heads * S * e + R);
+    begin(CUBERT_B200_K_GEMM);
+    blas_->gemm_batched<T>(false, false, d, 1, S, 1.f, v_ptrs_.template as<const T *>(), 3 * H,
+                           score1_ptrs_.template as<const T *>(), S, 0.f, ctx1_ptrs_.template as<T *>(), H, B * heads, algo_qkv_);
+    end(CUBERT_B200_K_GEMM, 0);
+
+    // the layer input of the first tokens (the residual of the first LayerNorm)
+    const int32_t *first = packed > 0 ? first_index_.template as<int32_t>() : first_index_full_.template as<int32_t>();
+    KERNEL_CHECK(cubk_embed_gather_i32(first, B, x, (int) N, H, (int) e, first_rows_.get(), nullptr, st));
+
+    begin(CUBERT_B200_K_GEMM);
+    blas_->gemm<T>(false, false, H, B, H, 1.f, L.att_out_kernel.template as<T>(), H, context_.template as<T>(), H, 0.f,
+                   dense_out_.template as<T>(), H, algo_attention_);
+    end(CUBERT_B200_K_GEMM, 0);
+    begin(CUBERT_B200_K_BIAS_RESIDUAL_LN);
+    KERNEL_CHECK(K<T>::bias_residual_ln(dense_out_.template as<T>(), L.att_out_bias.template as<T>(), first_rows_.template as<T>(),
+                                        L.att_ln_gamma.template as<T>(), L.att_ln_beta.template as<T>(), B, H,
+                                        att_out_.template as<T>(), st));
+    end(CUBERT_B200_K_BIAS_RESIDUAL_LN, 3 * (int64_t) B * H * e + 3 * H * e);
+
+    begin(CUBERT_B200_K_GEMM);
+    blas_->gemm<T>(false, false, I, B, H, 1.f, L.inter_kernel.template as<T>(), I, att_out_.template as<T>(), H, 0.f,
+                   inter_.template as<T>(), I, algo_intermediate_);
+    end(CUBERT_B200_K_GEMM, 0);
+    begin(CUBERT_B200_K_BIAS_GELU);
+    KERNEL_CHECK(K<T>::bias_gelu(inter_.template as<T>(), L.inter_bias.template as<T>(), B, I, inter_.template as<T>(), st));
+    end(CUBERT_B200_K_BIAS_GELU, 2 * (int64_t) B * I * e + I * e);
+
+    begin(CUBERT_B200_K_GEMM);
+    blas_->gemm<T>(false, false, H, B, I, 1.f, L.out_kernel.template as<T>(), H, inter_.template as<T>(), I, 0.f,
+                   dense_out_.template as<T>(), H, algo_output_);
+    end(CUBERT_B200_K_GEMM, 0);
+    begin(CUBERT_B200_K_BIAS_RESIDUAL_LN);
+    KERNEL_CHECK(K<T>::bias_residual_ln(dense_out_.template as<T>(), L.out_bias.template as<T>(), att_out_.template as<T>(),
+                                        L.out_ln_gamma.template as<T>(), L.out_ln_beta.template as<T>(), B, H, y, st));
+    end(CUBERT_B200_K_BIAS_RESIDUAL_LN, 3 * (int64_t) B * H * e + 3 * H * e);
+}
+
 // Pooler and classifier over the whole batch (src/cuBERT/op_bert/BertPooler.cpp:62-77,93-96;
 // src/cuBERT/op_out/AdditionalOutputLayer.cpp:44-66).
 template <typename T>
-void Bert<T>::forward_heads(size_t batch_size, const int8_t *d_mask, size_t packed) {
+void Bert<T>::forward_heads(size_t batch_size, const int8_t *d_mask, size_t packed, bool compact_first_rows) {
     const int B = (int) batch_size, S = (int) seq_length, H = (int) hidden_size;
     const int64_t R = (int64_t) B * S;
     const int64_t N = packed > 0 ? (int64_t) packed : R;
@@ -637,7 +743,9 @@ void Bert<T>::forward_heads(size_t batch_size, const int8_t *d_mask, size_t pack
     if (has_pooler_dense_) {
         const T *first = x;       // first token of every sequence: rows S apart, or gathered when packed
         int first_ld = H * S;
-        if (packed > 0) {
+        if (compact_first_rows) {
+            first_ld = H;         // the last layer ran on the first tokens only: one row per sequence
+        } else if (packed > 0) {
             KERNEL_CHECK(cubk_embed_gather_i32(first_index_.template as<int32_t>(), B, x, (int) N, H, (int) e,
                                                first_rows_.get(), nullptr, st));
             first = first_rows_.template as<T>();

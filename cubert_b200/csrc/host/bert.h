@@ -93,21 +93,26 @@ private:
     // products and the softmax keep the [batch, seq] layout, with rows scattered in and gathered out.
     // A masked position never influences an unmasked one (its keys get probability exactly 0), so
     // pooled_output, logits and probs are the same as in the full computation.
+    // `heads_only`: only pooled_output / logits / probs will be read and the pooler is the first-token
+    // one, so the LAST encoder layer is evaluated for the first token of every sequence alone: its
+    // attention has one query per sequence (keys and values still come from all positions) and its
+    // attention-output, LayerNorm and feed-forward steps run on `batch` rows instead of batch * seq.
     void forward(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments,
-                 size_t packed);
-    // its three parts: embeddings, a range of encoder layers on a range of sequences, pooler + classifier
+                 size_t packed, bool heads_only = false);
+    // its parts: embeddings, a range of encoder layers on a range of sequences, pooler + classifier
     void forward_embed(size_t batch_size, const int32_t *d_ids, const int8_t *d_segments, size_t packed);
     void forward_layers(size_t l_begin, size_t l_end, size_t b0, size_t nb, size_t batch_size, const int8_t *d_mask,
                         size_t packed);
-    void forward_heads(size_t batch_size, const int8_t *d_mask, size_t packed);
+    void forward_last_layer_first_tokens(size_t batch_size, const int8_t *d_mask, size_t packed);
+    void forward_heads(size_t batch_size, const int8_t *d_mask, size_t packed, bool compact_first_rows = false);
 
     // The forward pass as a CUDA graph, captured on first use per (batch size, input addresses) and
     // replayed afterwards: about 125 kernel launches collapse into one graph launch, which removes
     // the per-launch gaps that dominate small batches. Off while per-kernel timing is on, or with
     // the environment variable CUBERT_CUDA_GRAPH=0.
     void run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments,
-             size_t packed);
-    enum Phase { kWholePass = 0, kHeadLayers, kTailLayers, kHeads };
+             size_t packed, bool heads_only = false);
+    enum Phase { kWholePass = 0, kWholePassHeadsOnly, kHeadLayers, kTailLayers, kHeads };
     struct GraphKey {
         size_t batch, packed;
         const void *ids, *mask, *segments;
@@ -154,6 +159,9 @@ private:
     bool skip_padding_ = true;
     int32_t *h_token_index_ = nullptr;   // [max_batch * seq + max_batch]: packed list, then first-token slots
     DeviceBuffer token_index_, first_index_, qkv_packed_, ctx_packed_, first_rows_;
+    // last layer on first tokens only: row b * seq of every sequence, and one-query pointer arrays
+    bool prune_last_layer_ = true;
+    DeviceBuffer first_index_full_, score1_ptrs_, ctx1_ptrs_;
     size_t build_token_index(size_t batch_size, const int8_t *input_mask);
     T *sequence_output_ = nullptr;
 

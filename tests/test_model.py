@@ -343,7 +343,9 @@ def test_padding_is_skipped_without_changing_the_results(model_files, oracle, ct
     rows = (kept + 63) // 64 * 64
     assert rows < B * S
     e = 4 if ct == model.ComputeType.FLOAT else 2
-    assert prof["bias_gelu"]["bytes"] == cfg["layers"] * (2 * rows * cfg["intermediate"] * e + cfg["intermediate"] * e)
+    # packed rows in every layer but the last, which runs on the B first tokens only
+    assert prof["bias_gelu"]["bytes"] == (cfg["layers"] - 1) * (2 * rows * cfg["intermediate"] * e + cfg["intermediate"] * e) + \
+        (2 * B * cfg["intermediate"] * e + cfg["intermediate"] * e)
 
     full = _run(m, ids, mask, seg, cfg)                         # asks for sequence_output: no skipping
     tol = 1e-5 if ct == model.ComputeType.FLOAT else 4e-3
@@ -379,6 +381,56 @@ def test_through_the_references_own_python_wrapper(model_files, reference_python
     assert rel_err(new_output.logits, g["logits"]) < 1e-5
     assert rel_err(new_output.sequence_output, g["sequence_output"]) < 1e-5
     del m
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ct", [model.ComputeType.FLOAT, model.ComputeType.HALF])
+@pytest.mark.parametrize("name,batch,seq,skip", [("small", 80, 32, "0"), ("small", 67, 32, "1"), ("tiny", 40, 64, "0")])
+def test_last_layer_on_first_tokens_only(model_files, oracle, ct, name, batch, seq, skip, monkeypatch):
+    """When only pooled_output / logits / probs are asked for, the last encoder layer runs for the first
+    token of every sequence alone (one attention query per sequence, batch rows through the feed-forward
+    part). Same operations on fewer rows: the answers must be those of the full pass, with and without
+    padding skipping, full and ragged masks, and after graph replay."""
+    path, cfg, var = model_files[name]
+    lengths = (3, seq) if skip == "1" else "full"
+    ids, mask, seg, _ = synthetic.random_inputs(cfg, batch, seq, 29, lengths=lengths, segments="random")
+    dt = np.float32 if ct == model.ComputeType.FLOAT else np.float16
+    tol = 1e-5 if ct == model.ComputeType.FLOAT else 4e-3
+    monkeypatch.setenv("CUBERT_SKIP_PADDING", skip)
+    m = model.Model(path, batch, seq, cfg["layers"], cfg["heads"], ct)
+    monkeypatch.setenv("CUBERT_PRUNE_LAST_LAYER", "0")
+    full = model.Model(path, batch, seq, cfg["layers"], cfg["heads"], ct)
+
+    def heads(mm):
+        out = model.Output()
+        out.pooled_output = np.zeros((batch, cfg["hidden"]), dt)
+        out.logits = np.zeros((batch, cfg["num_labels"]), dt)
+        out.probs = np.zeros((batch, cfg["num_labels"]), dt)
+        mm.compute_m(ids, mask, seg, out)
+        return out
+
+    m.profile_read()
+    m.profile_enable(True)
+    heads(m)
+    prof = m.profile_read()
+    m.profile_enable(False)
+    e = 4 if ct == model.ComputeType.FLOAT else 2
+    last = 2 * batch * cfg["intermediate"] * e + cfg["intermediate"] * e
+    assert (prof["bias_gelu"]["bytes"] - last) % (cfg["layers"] - 1) == 0      # the last layer saw `batch` rows
+    want = heads(full)
+    for _ in range(3):
+        got = heads(m)
+        for k in ("pooled_output", "logits", "probs"):
+            assert rel_err(getattr(got, k), getattr(want, k)) < tol, k
+    if ct == model.ComputeType.FLOAT:
+        truth = oracle.bert_forward(var, synthetic.model_geometry(cfg, seq), ids, mask, seg)
+        for k in ("pooled_output", "logits", "probs"):
+            assert rel_err(getattr(got, k), truth[k]) < 1e-5, k
+    # asking for a per-position output afterwards takes the full pass again
+    allout = _run(m, ids, mask, seg, cfg)
+    assert rel_err(allout["pooled_output"], want.pooled_output) < tol
+    m.close()
+    full.close()
 
 
 @pytest.mark.gpu

@@ -93,7 +93,7 @@ def build_host(force=False, verbose=True):
     objs, changed = _compile("host", ["-I" + os.path.join(CSRC, "host")], force, verbose)
     if changed or _mtime(HOST_LIB) < _mtime(kernel_lib):
         _run([NVCC] + ARCH_FLAGS + ["-shared", "-cudart", "shared", "-ccbin", HOST_CXX, "-o", HOST_LIB] + objs +
-             ["-L" + LIBDIR, "-lcubert_kernels", "-lcublas", "-lcublasLt",
+             ["-L" + LIBDIR, "-lcubert_kernels", "-lcublas", "-lcublasLt", "-ldl",
               "-Xlinker", "-rpath,$ORIGIN", "-Xlinker", "-rpath," + os.path.join(CUDA_HOME, "lib64")])
     return HOST_LIB
 

@@ -1,5 +1,7 @@
 #include "bert.h"
 
+#include <nvtx3/nvToolsExt.h>
+
 #include <cmath>
 #include <cstring>
 #include <iostream>
@@ -309,9 +311,14 @@ cudaEvent_t Bert<T>::take_event() {
     return e;
 }
 
+// NVTX range names per kernel family (visible to ncu --nvtx and other CUPTI tools; a no-op otherwise)
+static const char *const kFamilyNames[CUBERT_B200_K_COUNT] = {
+    "embed_ln", "bias_residual_ln", "bias_gelu", "masked_softmax", "bias_tanh", "mean_pool",
+    "logits_probs", "half_to_float", "gemm", "event_overhead"};
+
 template <typename T>
 void Bert<T>::begin(int family) {
-    (void) family;
+    nvtxRangePushA(kFamilyNames[family]);
     if (profiling_) {
         open_start_ = take_event();
         CUDA_CHECK(cudaEventRecord(open_start_, stream_));
@@ -320,6 +327,7 @@ void Bert<T>::begin(int family) {
 
 template <typename T>
 void Bert<T>::end(int family, int64_t bytes) {
+    nvtxRangePop();
     launches_[family] += 1;
     bytes_[family] += bytes;
     if (profiling_) {

@@ -1,0 +1,98 @@
+// Host-only harness for the model-file reader and the tokenizer, built by tests/test_host_sanitizers.py
+// with -fsanitize=address,undefined. It reads a list of commands from stdin, one per line:
+//   graph <float|half> <path>      open a frozen graph; prints "ok <tensors> <checksum>" or "rejected: <why>"
+//   tok <lower 0|1> <vocab path> <max_seq_length> <hex of UTF-8 text>    prints "ok <ids...>" or "rejected: <why>"
+// A malformed input must end in "rejected" (a C++ exception), never in a sanitizer report or a crash.
+#include <cstdint>
+#include <cstdio>
+#include <exception>
+#include <iostream>
+#include <memory>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "frozen_graph.h"
+#include "runtime.h"
+#include "tokenizer.h"
+
+// runtime.cpp names this symbol of the kernel library, which this host-only program does not link
+extern "C" const char *cubk_last_cuda_error(void) {
+    return "";
+}
+
+namespace {
+
+template <typename T>
+void open_graph(const std::string &path) {
+    cubert::FrozenGraph<T> g(path.c_str());
+    double sum = 0.0;
+    size_t n = 0;
+    for (const auto &kv : g.var) {
+        std::vector<float> f(kv.second.size());
+        cubert::convert(kv.second.data(), f.data(), f.size());
+        for (float v : f) {
+            sum += v;
+        }
+        ++n;
+    }
+    std::printf("ok %zu %.6e %zu %zu %zu %zu %zu\n", n, sum, g.vocab_size, g.type_vocab_size, g.hidden_size,
+                g.intermediate_size, g.num_labels);
+}
+
+std::string unhex(const std::string &h) {
+    std::string out;
+    for (size_t i = 0; i + 1 < h.size(); i += 2) {
+        out.push_back((char) std::stoi(h.substr(i, 2), nullptr, 16));
+    }
+    return out;
+}
+
+}  // namespace
+
+int main() {
+    std::string line;
+    std::unique_ptr<cubert::FullTokenizer> tokenizer;
+    std::string tokenizer_key;
+    while (std::getline(std::cin, line)) {
+        std::istringstream in(line);
+        std::string cmd;
+        in >> cmd;
+        try {
+            if (cmd == "graph") {
+                std::string type, path;
+                in >> type >> path;
+                if (type == "half") {
+                    open_graph<__half>(path);
+                } else {
+                    open_graph<float>(path);
+                }
+            } else if (cmd == "tok") {
+                int lower = 1;
+                std::string vocab, hex;
+                size_t max_len = 0;
+                in >> lower >> vocab >> max_len >> hex;
+                const std::string key = vocab + (lower ? "|1" : "|0");
+                if (key != tokenizer_key) {
+                    tokenizer.reset(new cubert::FullTokenizer(vocab.c_str(), lower != 0));
+                    tokenizer_key = key;
+                }
+                const std::string text = unhex(hex);
+                std::vector<int> ids(max_len);
+                std::vector<int8_t> mask(max_len), seg(max_len);
+                tokenizer->encode(max_len, text.c_str(), nullptr, ids.data(), mask.data(), seg.data());
+                std::printf("ok");
+                for (int id : ids) {
+                    std::printf(" %d", id);
+                }
+                std::printf("\n");
+            } else if (!cmd.empty()) {
+                std::printf("rejected: unknown command\n");
+            }
+        } catch (const std::exception &e) {
+            std::printf("rejected: %s\n", e.what());
+        }
+        std::fflush(stdout);
+    }
+    return 0;
+}

@@ -455,3 +455,117 @@ def test_argument_checks_and_empty_inputs():
     assert lib.cubk_masked_softmax_f32(x.data_ptr(), None, 0, 1, 8, 1.0, x.data_ptr(), s) == 0
     assert lib.cubk_mean_pool_f32(x.data_ptr(), 0, 4, 8, x.data_ptr(), None, 0, s) == 0
     torch.cuda.synchronize()
+
+
+# ============================================================================ guard bands around every buffer
+# compute-sanitizer is not available for these kernels, so out-of-bounds writes are looked for the
+# plain way: every input and output sits between two bands of a sentinel value, and the bands (and the
+# inputs) must be untouched after the launch.
+
+class _Guarded:
+    PAD = 128          # elements; keeps the payload 16-byte aligned for every dtype used here
+
+    def __init__(self, shape, dtype, fill=None, misalign=0):
+        n = int(np.prod(shape))
+        self.sentinel = 113
+        self.buf = torch.full((n + 2 * self.PAD + misalign,), self.sentinel, dtype=dtype, device="cuda")
+        self.view = self.buf[self.PAD + misalign: self.PAD + misalign + n].view(*shape)
+        if fill is not None:
+            self.view.copy_(fill.to(dtype))
+        self.before = self.view.clone()
+        self.lo, self.hi = self.PAD + misalign, self.PAD + misalign + n
+
+    def bands_intact(self):
+        return bool((self.buf[:self.lo] == self.sentinel).all() and (self.buf[self.hi:] == self.sentinel).all())
+
+    def unchanged(self):
+        return self.bands_intact() and torch.equal(self.view, self.before)
+
+
+@pytest.mark.parametrize("t", DTYPES)
+@pytest.mark.parametrize("rows,ch,misalign", [(1, 8, 0), (3, 768, 0), (37, 776, 0), (5, 3072, 0), (9, 4096, 0), (2, 8200, 0),
+                                              (7, 33, 0), (4, 100, 1), (3, 768, 1)])
+def test_row_kernels_stay_inside_their_buffers(t, rows, ch, misalign):
+    dt = G.TORCH_DTYPE[t]
+    g = torch.Generator(device="cuda").manual_seed(rows * 7919 + ch)
+    rnd = lambda *shape: torch.randn(*shape, device="cuda", generator=g)  # noqa: E731
+    x, res = _Guarded((rows, ch), dt, rnd(rows, ch), misalign), _Guarded((rows, ch), dt, rnd(rows, ch), misalign)
+    bias, gamma, beta = (_Guarded((ch,), dt, rnd(ch), misalign) for _ in range(3))
+    out = _Guarded((rows, ch), dt, None, misalign)
+    inputs = (x, res, bias, gamma, beta)
+    kernels.check(G.fn("bias_residual_ln", t)(G.ptr(x.view), G.ptr(bias.view), G.ptr(res.view), G.ptr(gamma.view),
+                                              G.ptr(beta.view), rows, ch, G.ptr(out.view), G.stream()))
+    torch.cuda.synchronize()
+    assert out.bands_intact() and all(i.unchanged() for i in inputs), "bias_residual_ln"
+    assert torch.isfinite(out.view.float()).all()
+    for name in ("bias_gelu", "bias_tanh"):
+        out = _Guarded((rows, ch), dt, None, misalign)
+        kernels.check(G.fn(name, t)(G.ptr(x.view), G.ptr(bias.view), rows, ch, G.ptr(out.view), G.stream()))
+        torch.cuda.synchronize()
+        assert out.bands_intact() and all(i.unchanged() for i in inputs), name
+    # in place: the bands of the one buffer
+    y = _Guarded((rows, ch), dt, x.view, misalign)
+    kernels.check(G.fn("bias_gelu", t)(G.ptr(y.view), G.ptr(bias.view), rows, ch, G.ptr(y.view), G.stream()))
+    torch.cuda.synchronize()
+    assert y.bands_intact() and bias.unchanged()
+
+
+@pytest.mark.parametrize("t", DTYPES)
+@pytest.mark.parametrize("batch,heads,seq", [(1, 1, 8), (3, 2, 32), (2, 12, 128), (2, 3, 512), (1, 2, 2048), (2, 2, 40),
+                                             (5, 1, 7), (2, 2, 264)])
+def test_softmax_and_pool_stay_inside_their_buffers(t, batch, heads, seq):
+    dt = G.TORCH_DTYPE[t]
+    g = torch.Generator(device="cuda").manual_seed(batch * 31 + seq)
+    rows = batch * seq * heads
+    scores = _Guarded((rows, seq), dt, torch.randn(rows, seq, device="cuda", generator=g) * 3)
+    mask = _Guarded((batch, seq), torch.int8, (torch.rand(batch, seq, device="cuda", generator=g) > 0.3).to(torch.int8))
+    out = _Guarded((rows, seq), dt)
+    kernels.check(G.fn("masked_softmax", t)(G.ptr(scores.view), G.ptr(mask.view), rows, seq * heads, seq, 0.125,
+                                            G.ptr(out.view), G.stream()))
+    torch.cuda.synchronize()
+    assert out.bands_intact() and scores.unchanged() and mask.unchanged()
+    assert torch.allclose(out.view.float().sum(dim=1), torch.ones(rows, device="cuda"), atol=2e-2 if t == "f16" else 1e-4)
+    # mean pool over [batch, seq, hidden] with the library's own scratch sizing
+    hidden = 8 * heads * 4
+    x = _Guarded((batch, seq, hidden), dt, torch.randn(batch, seq, hidden, device="cuda", generator=g))
+    pooled = _Guarded((batch, hidden), dt)
+    need = kernels.load().cubk_mean_pool_scratch_bytes(batch, seq, hidden)
+    scratch = _Guarded((max(need // 4, 1),), torch.float32)
+    kernels.check(G.fn("mean_pool", t)(G.ptr(x.view), batch, seq, hidden, G.ptr(pooled.view), G.ptr(scratch.view), need,
+                                       G.stream()))
+    torch.cuda.synchronize()
+    assert pooled.bands_intact() and scratch.bands_intact() and x.unchanged()
+
+
+@pytest.mark.parametrize("t", DTYPES)
+@pytest.mark.parametrize("staged", ["0", "1"])
+@pytest.mark.parametrize("batch,seq,hidden,vocab", [(1, 1, 8, 3), (3, 5, 768, 50), (2, 7, 1024, 9), (9, 3, 40, 4), (4, 4, 4096, 6)])
+def test_embedding_kernels_stay_inside_their_buffers(t, staged, batch, seq, hidden, vocab, monkeypatch):
+    monkeypatch.setenv("CUBK_BULK_COPY", staged)
+    dt = G.TORCH_DTYPE[t]
+    g = torch.Generator(device="cuda").manual_seed(hidden + vocab)
+    rnd = lambda *shape: torch.randn(*shape, device="cuda", generator=g) * 0.1  # noqa: E731
+    word, pos, typ = _Guarded((vocab, hidden), dt, rnd(vocab, hidden)), _Guarded((seq, hidden), dt, rnd(seq, hidden)), \
+        _Guarded((2, hidden), dt, rnd(2, hidden))
+    gamma, beta = _Guarded((hidden,), dt, 1 + rnd(hidden)), _Guarded((hidden,), dt, rnd(hidden))
+    ids = _Guarded((batch, seq), torch.int32, torch.randint(-2, vocab + 2, (batch, seq), device="cuda", generator=g))
+    seg = _Guarded((batch, seq), torch.int8, torch.randint(-1, 3, (batch, seq), device="cuda", generator=g))
+    status = _Guarded((1,), torch.int32, torch.zeros(1))
+    out = _Guarded((batch, seq, hidden), dt)
+    kernels.check(G.fn("embed_ln", t)(G.ptr(ids.view), G.ptr(seg.view), G.ptr(word.view), G.ptr(pos.view), G.ptr(typ.view),
+                                      G.ptr(gamma.view), G.ptr(beta.view), batch, seq, hidden, vocab, 2, G.ptr(out.view),
+                                      G.ptr(status.view), G.stream()))
+    torch.cuda.synchronize()
+    assert out.bands_intact() and status.bands_intact()
+    assert all(i.unchanged() for i in (word, pos, typ, gamma, beta, ids, seg))
+    assert torch.isfinite(out.view.float()).all()
+    # plain gather and its inverse
+    rows = _Guarded((batch * seq, hidden), dt)
+    kernels.check(kernels.load().cubk_embed_gather_i32(G.ptr(ids.view), batch * seq, G.ptr(word.view), vocab, hidden,
+                                                       word.view.element_size(), G.ptr(rows.view), G.ptr(status.view),
+                                                       G.stream()))
+    table2 = _Guarded((vocab, hidden), dt, word.view)
+    kernels.check(kernels.load().cubk_scatter_rows(G.ptr(ids.view), batch * seq, G.ptr(rows.view), hidden,
+                                                   word.view.element_size(), G.ptr(table2.view), vocab, G.stream()))
+    torch.cuda.synchronize()
+    assert rows.bands_intact() and table2.bands_intact() and word.unchanged() and ids.unchanged()

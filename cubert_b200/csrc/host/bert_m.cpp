@@ -18,6 +18,7 @@ BertM<T>::BertM(const char *model_file, size_t max_batch_size_, size_t seq_lengt
         throw std::invalid_argument("No GPU device detected");
     }
     std::cerr << "Found GPU count: " << count << std::endl;
+    failing_replica = env_int("CUBERT_INJECT_REPLICA_FAILURE", -1);
     int per_gpu = env_int("CUBERT_NUM_MODELS_PER_GPU", 1);
     if (per_gpu < 1) {
         per_gpu = 1;
@@ -83,6 +84,9 @@ unsigned int BertM<T>::compute(size_t batch_size, int *input_ids, int8_t *input_
     const unsigned int choice = (unsigned int) (rr.fetch_add(1) % bert_instances.size());
     Bert<T> *bert = bert_instances[choice].get();
     std::lock_guard<std::mutex> lg(*mutex_instances[choice]);
+    if ((int) choice == failing_replica) {
+        throw RuntimeError("injected failure on replica " + std::to_string(choice));
+    }
     // Only when no per-position output is wanted may the replica skip padding tokens; when one is
     // wanted, its device-to-host copy overlaps the computation (Bert::compute_output).
     bert->compute_output(batch_size, input_ids, input_mask, segment_ids, output, output_to_float);

@@ -41,6 +41,9 @@ private:
     // The reference counts in a uint8_t, which skews the rotation whenever 256 is not a multiple
     // of the replica count (src/cuBERT/BertM.h:44); a wide counter keeps it even.
     std::atomic<uint64_t> rr;
+    // Host-side fault injection for tests: calls routed to this replica fail with a RuntimeError before
+    // anything reaches its GPU (CUBERT_INJECT_REPLICA_FAILURE=<replica>; -1, the default, injects nothing).
+    int failing_replica = -1;
 };
 
 }  // namespace cubert

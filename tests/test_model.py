@@ -243,6 +243,33 @@ def test_error_behaviour(model_files, tmp_path):
 
 
 @pytest.mark.gpu
+def test_a_failing_replica_does_not_stop_the_others(model_files, oracle, monkeypatch):
+    """Failure made on the host (no GPU fault): with three replicas on the GPU and replica 1 set to fail,
+    every third call reports a runtime error through the status API, the other calls keep giving the
+    right answers, and the model closes cleanly."""
+    path, cfg, var = model_files["tiny"]
+    monkeypatch.setenv("CUBERT_NUM_MODELS_PER_GPU", "3")
+    monkeypatch.setenv("CUBERT_INJECT_REPLICA_FAILURE", "1")
+    m = model.Model(path, 4, 16, cfg["layers"], cfg["heads"])
+    replicas = m.info["replicas"]
+    assert replicas % 3 == 0
+    ids, mask, seg, _ = synthetic.random_inputs(cfg, 4, 16, 3, lengths=(2, 16))
+    ref = oracle.bert_forward(var, synthetic.model_geometry(cfg, 16), ids, mask, seg)
+    outcomes = []
+    for call in range(4 * replicas):
+        out = np.zeros((4, cfg["num_labels"]), np.float32)
+        try:
+            m.compute(ids, mask, seg, out, model.OutputType.PROBS)
+            assert rel_err(out, ref["probs"]) < 1e-5
+            outcomes.append("ok")
+        except RuntimeError as e:
+            assert "injected failure on replica 1" in str(e)
+            outcomes.append("failed")
+    assert outcomes == [("failed" if c % replicas == 1 else "ok") for c in range(4 * replicas)]
+    m.close()
+
+
+@pytest.mark.gpu
 def test_device_resident_forward_and_profile(model_files):
     import torch
     path, cfg, var = model_files["small"]

@@ -129,3 +129,44 @@ def test_tokenize_compute_equals_compute_on_the_encoded_ids(tmp_path):
     assert np.array_equal(got.logits, want.logits) and np.array_equal(got.sequence_output, want.sequence_output)
     m.close()
     tk.close()
+
+
+@pytest.mark.gpu
+def test_large_batches_are_tokenized_on_several_threads_with_the_same_result(tmp_path, monkeypatch):
+    """Batches of 16 texts or more are split over host threads; every row must equal the single-text
+    encoding, pairs and single sentences, with CUBERT_TOKENIZER_THREADS at its default and at 1."""
+    from cubert_b200 import frozen_graph, synthetic
+    cfg = synthetic.config("tiny", vocab=len(VOCAB))
+    path = str(tmp_path / "m.pb")
+    frozen_graph.write_frozen_graph(path, synthetic.random_weights(cfg, 22))
+    (tmp_path / "vocab.txt").write_text("\n".join(VOCAB) + "\n")
+    tk = model.Tokenizer(str(tmp_path / "vocab.txt"))
+    rng = np.random.default_rng(5)
+    pieces = ["un", "want", "wanted", "running", "runn", "wa", ",", "é", "UNwantéd", "x"]
+    B, S = 203, 24
+    text_a = [" ".join(rng.choice(pieces, size=int(rng.integers(1, 30)))) for _ in range(B)]
+    text_b = [" ".join(rng.choice(pieces, size=int(rng.integers(1, 10)))) for _ in range(B)]
+    rows = [tk.encode(a, b, S) for a, b in zip(text_a, text_b)]
+    ids, mask, seg = (np.stack([r[i] for r in rows]) for i in range(3))
+    for threads in (None, "1", "3"):
+        if threads is None:
+            monkeypatch.delenv("CUBERT_TOKENIZER_THREADS", raising=False)
+        else:
+            monkeypatch.setenv("CUBERT_TOKENIZER_THREADS", threads)
+        m = model.Model(path, B, S, cfg["layers"], cfg["heads"])
+        want, got = model.Output(), model.Output()
+        want.pooled_output = np.zeros((B, 64), np.float32)
+        got.pooled_output = np.zeros((B, 64), np.float32)
+        m.compute_m(ids, mask, seg, want)
+        m.tokenize_compute_m(tk, text_a, text_b, got)
+        assert np.array_equal(got.pooled_output, want.pooled_output), threads
+        single = model.Output()
+        single.pooled_output = np.zeros((B, 64), np.float32)
+        rows_a = [tk.encode(a, None, S) for a in text_a]
+        m.compute_m(*(np.stack([r[i] for r in rows_a]) for i in range(3)), single)
+        got_a = model.Output()
+        got_a.pooled_output = np.zeros((B, 64), np.float32)
+        m.tokenize_compute_m(tk, text_a, None, got_a)
+        assert np.array_equal(got_a.pooled_output, single.pooled_output), threads
+        m.close()
+    tk.close()

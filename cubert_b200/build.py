@@ -74,7 +74,21 @@ def _compile(sub, extra_flags, force, verbose):
     return objs, bool(jobs)
 
 
+def _up_to_date(lib, subs, extra=()):
+    """True when `lib` exists and is newer than every source and header it is built from (the object
+    files need not exist: a tree that was copied without its build folder is not recompiled)."""
+    if not os.path.exists(lib):
+        return False
+    deps = [os.path.abspath(__file__)] + [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE)] + list(extra)
+    for sub in subs:
+        srcs, hdrs = _sources(sub)
+        deps += srcs + hdrs
+    return _mtime(lib) >= max(_mtime(d) for d in deps)
+
+
 def build_kernels(force=False, verbose=True):
+    if not force and _up_to_date(KERNEL_LIB, ["kernels"]):
+        return KERNEL_LIB
     objs, changed = _compile("kernels", [], force, verbose)
     if not objs:
         raise RuntimeError("no kernel sources under %s" % CSRC)
@@ -90,6 +104,8 @@ def build_host(force=False, verbose=True):
     if not srcs:
         return None
     kernel_lib = build_kernels(force=False, verbose=verbose)
+    if not force and _up_to_date(HOST_LIB, ["host"], [kernel_lib]):
+        return HOST_LIB
     objs, changed = _compile("host", ["-I" + os.path.join(CSRC, "host")], force, verbose)
     if changed or _mtime(HOST_LIB) < _mtime(kernel_lib):
         _run([NVCC] + ARCH_FLAGS + ["-shared", "-cudart", "shared", "-ccbin", HOST_CXX, "-o", HOST_LIB] + objs +

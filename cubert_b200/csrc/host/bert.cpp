@@ -833,8 +833,11 @@ void Bert<T>::compute_output(size_t batch_size, const int *input_ids, const int8
     const bool per_position = out->sequence_output != nullptr || out->embedding_output != nullptr;
     const size_t S = seq_length, H = hidden_size, L = num_hidden_layers;
     const size_t tokens = batch_size * S;
+    // worth it when the tail can be split (sequence_output of a large request) or when embedding_output,
+    // which is final right after K1, can leave during the whole encoder
+    const bool splittable = out->sequence_output != nullptr && tokens >= kMinChunkedTokens && L > 0 && tail_chunks_ > 1;
     if (!per_position || profiling_ || batch_size == 0 || batch_size > max_batch_size ||
-        tokens * H * sizeof(T) < kMinOverlapBytes || (tail_chunks_ <= 1 && out->embedding_output == nullptr)) {
+        tokens * H * sizeof(T) < kMinOverlapBytes || !(splittable || out->embedding_output != nullptr)) {
         compute(batch_size, input_ids, input_mask, segment_ids, per_position);
         output(batch_size, out, to_float);
         return;
@@ -874,7 +877,7 @@ void Bert<T>::compute_output(size_t batch_size, const int *input_ids, const int8
         CUDA_CHECK(cudaEventRecord(embed_ready_, stream_));
     }
     size_t chunks = 1;
-    if (out->sequence_output != nullptr && tokens >= kMinChunkedTokens && L > 0) {
+    if (splittable) {
         chunks = (size_t) tail_chunks_ < batch_size ? (size_t) tail_chunks_ : batch_size;
     }
     const size_t tail = chunks > 1 ? ((size_t) tail_layers_ < L ? (size_t) tail_layers_ : L) : 0;

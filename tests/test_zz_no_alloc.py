@@ -9,7 +9,6 @@ the caller's input and output buffers.
 Collected last on purpose (file name), so that a run stopping at the first failure has already run
 every other test; it must pass alone in a fresh process as well as after the others.
 """
-import numpy as np
 import pytest
 import torch
 

@@ -44,13 +44,32 @@ int range_lookup(const CategoryRange (&table)[N], uint32_t cp) {
 }
 
 int category_class(uint32_t cp) {
+    if (cp < 0x80) {  // ASCII: looked up once per process
+        static const struct AsciiClasses {
+            unsigned char cls[0x80];
+            AsciiClasses() {
+                for (uint32_t c = 0; c < 0x80; ++c) {
+                    cls[c] = (unsigned char) range_lookup(kCategoryRanges, c);
+                }
+            }
+        } ascii;
+        return ascii.cls[cp];
+    }
     if (cp >= 0x110000) {
         return CLS_C;
     }
     return range_lookup(kCategoryRanges, cp);
 }
 
+// combining class; nothing below U+0300 has one
+inline int combining_class(uint32_t cp) {
+    return cp < 0x300 ? 0 : range_lookup(kCcc, cp);
+}
+
 uint32_t to_lower(uint32_t cp) {
+    if (cp < 0x80) {
+        return (cp >= 'A' && cp <= 'Z') ? cp + 32 : cp;
+    }
     const CodePair *end = kLower + sizeof(kLower) / sizeof(kLower[0]);
     const CodePair *it = std::lower_bound(kLower, end, cp, [](const CodePair &p, uint32_t v) { return p.from < v; });
     return (it != end && it->from == cp) ? it->to : cp;
@@ -113,6 +132,10 @@ void utf8_append(uint32_t cp, std::string *out) {
 }
 
 void decompose(uint32_t cp, std::u32string *out) {
+    if (cp < 0xC0) {  // no canonical decomposition below U+00C0
+        out->push_back(cp);
+        return;
+    }
     // Hangul syllables decompose arithmetically (Unicode chapter 3.12)
     if (cp >= 0xAC00 && cp <= 0xD7A3) {
         const uint32_t s = cp - 0xAC00;
@@ -189,16 +212,16 @@ bool utf8_nfd(const char *text, std::u32string *out) {
     // canonical ordering: stable sort of every run of non-starters by combining class
     size_t i = 0;
     while (i < out->size()) {
-        if (range_lookup(kCcc, (*out)[i]) == 0) {
+        if (combining_class((*out)[i]) == 0) {
             ++i;
             continue;
         }
         size_t j = i;
-        while (j < out->size() && range_lookup(kCcc, (*out)[j]) != 0) {
+        while (j < out->size() && combining_class((*out)[j]) != 0) {
             ++j;
         }
         std::stable_sort(out->begin() + i, out->begin() + j,
-                         [](char32_t a, char32_t b) { return range_lookup(kCcc, a) < range_lookup(kCcc, b); });
+                         [](char32_t a, char32_t b) { return combining_class(a) < combining_class(b); });
         i = j;
     }
     return true;
@@ -236,14 +259,17 @@ void BasicTokenizer::tokenize(const char *text, std::vector<std::string> *output
         if (do_lower_case_) {
             cp = to_lower(cp);
         }
-        const int cls = category_class(cp);
-        if (cp == 0 || cp == 0xfffd || is_control(cp)) {
+        const int cls = category_class(cp);  // the four tests below are is_control / is_whitespace / is_punctuation
+        const bool space_char = cp == ' ' || cp == '\t' || cp == '\n' || cp == '\r';
+        const bool ascii_punct = (cp >= 33 && cp <= 47) || (cp >= 58 && cp <= 64) || (cp >= 91 && cp <= 96) ||
+                                 (cp >= 123 && cp <= 126);
+        if (cp == 0 || cp == 0xfffd || (cls == CLS_C && !space_char)) {
             // dropped
         } else if (do_lower_case_ && cls == CLS_MN) {
             // accent stripped
-        } else if (is_whitespace(cp)) {
+        } else if (space_char || cls == CLS_ZS) {
             new_token = true;
-        } else if (is_punctuation(cp) || is_chinese_char(cp)) {
+        } else if (ascii_punct || cls == CLS_P || is_chinese_char(cp)) {
             output_tokens->emplace_back();
             utf8_append(cp, &output_tokens->back());
             new_token = true;
@@ -270,14 +296,16 @@ void WordpieceTokenizer::tokenize(const std::string &token, std::vector<std::str
     const size_t mark = output_tokens->size();
     for (size_t start = 0; start < token.size();) {
         bool is_bad = true;
+        std::string piece = start > 0 ? "##" : "";
+        piece.append(token, start, std::string::npos);  // the longest candidate; one byte shorter every round
         for (size_t end = token.size(); start < end; --end) {
-            std::string piece = start > 0 ? "##" + token.substr(start, end - start) : token.substr(start, end - start);
             if (vocab_->count(piece)) {
                 is_bad = false;
                 output_tokens->push_back(std::move(piece));
                 start = end;
                 break;
             }
+            piece.pop_back();
         }
         if (is_bad) {
             output_tokens->resize(mark);

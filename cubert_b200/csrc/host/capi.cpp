@@ -86,8 +86,8 @@ void encode_batch(void *model, void *tokenizer, int batch_size, const char **tex
         }
     };
     // Texts are independent and the tokenizer is read-only: large batches are split over a few host
-    // threads (a text of 100 words costs about 80 us, a 256-text batch 20 ms on one thread, several times
-    // the forward pass). CUBERT_TOKENIZER_THREADS caps the count (default 8; 1 = the calling thread only).
+    // threads (a text of 100 words costs about 27 us, a 256-text batch 7 ms on one thread, as much as the
+    // forward pass). CUBERT_TOKENIZER_THREADS caps the count (default 8; 1 = the calling thread only).
     int threads = cubert::env_int("CUBERT_TOKENIZER_THREADS", 8);
     const int hw = (int) std::thread::hardware_concurrency();
     threads = std::min(threads, hw > 0 ? hw : 1);

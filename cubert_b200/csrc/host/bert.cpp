@@ -47,6 +47,8 @@ const T *find(const std::unordered_map<std::string, const T *> &var, const std::
     return it->second;
 }
 
+constexpr size_t kMaxStagedInputBytes = 64 * 1024;  // one staged copy of the whole input span up to this size
+
 template <typename T>
 void upload(DeviceBuffer &dst, const T *src, size_t count) {
     dst.allocate(count * sizeof(T));
@@ -171,9 +173,16 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
     }
 
     // ---- inputs, activations
-    ids_.allocate(sizeof(int32_t) * R);
-    mask_.allocate(sizeof(int8_t) * R);
-    segments_.allocate(sizeof(int8_t) * R);
+    {
+        const size_t mask_at = (sizeof(int32_t) * R + 15) / 16 * 16, seg_at = mask_at + (R + 15) / 16 * 16;
+        inputs_.allocate(seg_at + R);
+        ids_ = inputs_.template as<int32_t>();
+        mask_ = inputs_.template as<int8_t>() + mask_at;
+        segments_ = inputs_.template as<int8_t>() + seg_at;
+        if (inputs_.bytes() <= kMaxStagedInputBytes) {
+            CUDA_CHECK(cudaMallocHost(reinterpret_cast<void **>(&h_inputs_), inputs_.bytes()));
+        }
+    }
     status_.allocate(sizeof(uint32_t));
     calibration_.allocate(sizeof(float));
     CUDA_CHECK(cudaMemset(status_.get(), 0, sizeof(uint32_t)));
@@ -293,6 +302,9 @@ Bert<T>::~Bert() {
     if (h_token_index_ != nullptr) {
         cudaFreeHost(h_token_index_);
     }
+    if (h_inputs_ != nullptr) {
+        cudaFreeHost(h_inputs_);
+    }
     if (stream_ != nullptr) {
         cudaStreamDestroy(stream_);
     }
@@ -406,6 +418,25 @@ size_t Bert<T>::build_token_index(size_t batch_size, const int8_t *input_mask) {
     return padded;
 }
 
+// Host inputs to the device. When the model's whole input span is small (serving-size models), the three
+// arrays are gathered in a pinned staging buffer laid out like the device buffer and go over in ONE copy;
+// three copies from pageable caller memory each pay the driver's own staging. Otherwise three copies.
+template <typename T>
+void Bert<T>::upload_inputs(size_t tokens, const int *input_ids, const int8_t *input_mask, const int8_t *segment_ids) {
+    if (h_inputs_ != nullptr) {
+        const size_t mask_at = (size_t) (mask_ - inputs_.template as<int8_t>());
+        const size_t seg_at = (size_t) (segments_ - inputs_.template as<int8_t>());
+        std::memcpy(h_inputs_, input_ids, sizeof(int32_t) * tokens);
+        std::memcpy(h_inputs_ + mask_at, input_mask, tokens);
+        std::memcpy(h_inputs_ + seg_at, segment_ids, tokens);
+        CUDA_CHECK(cudaMemcpyAsync(inputs_.get(), h_inputs_, seg_at + tokens, cudaMemcpyHostToDevice, stream_));
+        return;
+    }
+    CUDA_CHECK(cudaMemcpyAsync(ids_, input_ids, sizeof(int32_t) * tokens, cudaMemcpyHostToDevice, stream_));
+    CUDA_CHECK(cudaMemcpyAsync(mask_, input_mask, sizeof(int8_t) * tokens, cudaMemcpyHostToDevice, stream_));
+    CUDA_CHECK(cudaMemcpyAsync(segments_, segment_ids, sizeof(int8_t) * tokens, cudaMemcpyHostToDevice, stream_));
+}
+
 template <typename T>
 void Bert<T>::compute(size_t batch_size, const int *input_ids, const int8_t *input_mask,
                       const int8_t *segment_ids, bool all_positions) {
@@ -419,9 +450,7 @@ void Bert<T>::compute(size_t batch_size, const int *input_ids, const int8_t *inp
     }
     CUDA_CHECK(cudaSetDevice(device_));
     const size_t n = batch_size * seq_length;
-    CUDA_CHECK(cudaMemcpyAsync(ids_.get(), input_ids, sizeof(int32_t) * n, cudaMemcpyHostToDevice, stream_));
-    CUDA_CHECK(cudaMemcpyAsync(mask_.get(), input_mask, sizeof(int8_t) * n, cudaMemcpyHostToDevice, stream_));
-    CUDA_CHECK(cudaMemcpyAsync(segments_.get(), segment_ids, sizeof(int8_t) * n, cudaMemcpyHostToDevice, stream_));
+    upload_inputs(n, input_ids, input_mask, segment_ids);
     size_t packed = 0;
     if (!all_positions && skip_padding_) {
         packed = build_token_index(batch_size, input_mask);
@@ -435,8 +464,7 @@ void Bert<T>::compute(size_t batch_size, const int *input_ids, const int8_t *inp
     // the last layer for first tokens only: when nothing per-position is wanted and the request is large
     // enough for the saved rows to outweigh one extra gather launch
     const bool heads_only = !all_positions && prune_last_layer_ && (packed > 0 || n >= kMinPositionsForPacking);
-    run(batch_size, ids_.template as<int32_t>(), mask_.template as<int8_t>(), segments_.template as<int8_t>(), packed,
-        heads_only);
+    run(batch_size, ids_, mask_, segments_, packed, heads_only);
 }
 
 template <typename T>
@@ -858,12 +886,10 @@ void Bert<T>::compute_output(size_t batch_size, const int *input_ids, const int8
         float_staging_small_.allocate(sizeof(float) * max_batch_size * (H > num_labels ? H : num_labels));
     }
 
-    CUDA_CHECK(cudaMemcpyAsync(ids_.get(), input_ids, sizeof(int32_t) * tokens, cudaMemcpyHostToDevice, stream_));
-    CUDA_CHECK(cudaMemcpyAsync(mask_.get(), input_mask, sizeof(int8_t) * tokens, cudaMemcpyHostToDevice, stream_));
-    CUDA_CHECK(cudaMemcpyAsync(segments_.get(), segment_ids, sizeof(int8_t) * tokens, cudaMemcpyHostToDevice, stream_));
-    const int32_t *d_ids = ids_.template as<int32_t>();
-    const int8_t *d_mask = mask_.template as<int8_t>();
-    const int8_t *d_seg = segments_.template as<int8_t>();
+    upload_inputs(tokens, input_ids, input_mask, segment_ids);
+    const int32_t *d_ids = ids_;
+    const int8_t *d_mask = mask_;
+    const int8_t *d_seg = segments_;
 
     // ---- everything that computes goes to the compute stream first ...
     forward_embed(batch_size, d_ids, d_seg, 0);

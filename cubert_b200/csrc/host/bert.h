@@ -150,7 +150,13 @@ private:
     DeviceBuffer pooler_kernel_, pooler_bias_, output_weights_, output_bias_;
 
     // inputs and activations (shared by all layers)
-    DeviceBuffer ids_, mask_, segments_, status_, calibration_;
+    // input_ids (int32), input_mask (int8) and segment_ids (int8) of a request live in ONE device buffer at
+    // fixed offsets; small models' requests arrive through one pinned staging buffer and one copy
+    DeviceBuffer inputs_, status_, calibration_;
+    int32_t *ids_ = nullptr;
+    int8_t *mask_ = nullptr, *segments_ = nullptr;
+    unsigned char *h_inputs_ = nullptr;  // pinned twin of inputs_, only when the whole span is small
+    void upload_inputs(size_t tokens, const int *input_ids, const int8_t *input_mask, const int8_t *segment_ids);
     DeviceBuffer embedding_, hidden_[2], qkv_, scores_, context_, dense_out_, att_out_, inter_;
     DeviceBuffer pooled_, logits_, probs_, pool_scratch_, float_staging_;
     DeviceBuffer q_ptrs_, k_ptrs_, v_ptrs_, score_ptrs_, ctx_ptrs_;

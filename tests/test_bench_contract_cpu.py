@@ -1,0 +1,76 @@
+"""bench.py's contract, as far as it can be checked without a GPU: the workload table, the clock-sample
+parser, and the reference arm (`--impl reference`), which runs the reference's CPU build (or the C oracle)
+on the host cores and must print ONE JSON line with the agreed keys."""
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _bench_module():
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(ROOT, "bench.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_workload_table():
+    bench = _bench_module()
+    assert bench.WORKLOAD is bench.WORKLOADS["base_seq128"]          # the headline workload is the default
+    for name, w in bench.WORKLOADS.items():
+        for key in ("model", "seq", "batch", "seed", "scaling", "outputs", "metric", "text"):
+            assert key in w, (name, key)
+        assert w["scaling"] in ("weak", "strong")
+    assert bench.WORKLOADS["base_seq128"]["seq"] == 128 and bench.WORKLOADS["base_seq128"]["batch"] == 256
+    assert bench.WORKLOADS["large_seq512"]["scaling"] == "strong"
+    assert set(bench.NCU_TRAFFIC_BYTES) >= {"bias_gelu", "bias_residual_ln", "masked_softmax", "embed_ln"}
+
+
+def test_clock_samples_are_parsed(tmp_path):
+    bench = _bench_module()
+    sampler = bench.ClockSampler.__new__(bench.ClockSampler)
+    sampler.path = str(tmp_path / "clocks.csv")
+    with open(sampler.path, "w") as f:
+        f.write("0, 345, 1965, 140.2, 0x0000000000000000, Not Active, Not Active, Not Active, Not Active\n")
+        f.write("0, 1650, 1965, 980.5, 0x0000000000000004, Not Active, Not Active, Not Active, Active\n")
+        f.write("0, 1590, 1965, 990.1, 0x0000000000000004, Not Active, Not Active, Not Active, Active\n")
+        f.write("garbage line\n")
+
+    class Done:
+        def terminate(self):
+            pass
+
+        def wait(self, timeout=None):
+            return 0
+
+    sampler.proc = Done()
+    sampler.out = open(os.devnull, "w")
+    got = sampler.stop()
+    assert got["sm_mhz"] == 1620.0 and got["sm_max_mhz"] == 1965.0       # median of the samples under load
+    assert got["reasons"] == ["sw_power_cap"] and got["samples"] == 3
+
+
+@pytest.mark.parametrize("workload", ["base_seq128", "base_seq32_f32"])
+def test_reference_arm_prints_one_contract_line(workload):
+    env = dict(os.environ, CUBERT_BENCH_CPU_THREADS="4")
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1",
+                           "--warmup", "1", "--workload", workload], stdout=subprocess.PIPE, stderr=subprocess.PIPE,
+                          universal_newlines=True, env=env, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [l for l in proc.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    line = json.loads(lines[0])
+    assert line["impl"] == "reference" and line["value"] > 0 and line["unit"] == "sequences/s"
+    assert line["higher_is_better"] is True and line["data"] == "synthetic" and line["vs_baseline"] is None
+    assert line["metric"] == _bench_module().WORKLOADS[workload]["metric"]
+    assert "workload" in line["config"]
+    base = line["cpu_baseline"]
+    assert base["kind"] in ("reference", "port") and base["cores"] == 4 and base["value"] == line["value"]
+    assert "sample" in base
+    assert line["e2e"] == {"value": line["value"], "unit": line["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert line["gpu_launches"] == 0

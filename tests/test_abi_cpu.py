@@ -60,3 +60,36 @@ def test_reference_cython_wrapper_binds_to_this_library(reference_python_wrapper
             cuBERT.OutputType.EMBEDDING_OUTPUT, cuBERT.OutputType.PROBS) == (0, 1, 2, 3, 4)
     with pytest.raises(ValueError, match="model file not found"):   # std::invalid_argument through `except +`
         cuBERT.Model("/no/such/model.pb", 8, 32, 12, 12)
+
+
+def test_headers_are_plain_c_and_a_c_program_links(tmp_path):
+    """The boundary is a C ABI: every header under include/ must compile as C99 (and as C++), and a C
+    program that names entry points of both libraries must link against them (no GPU needed to link)."""
+    import shutil
+    import subprocess
+    from cubert_b200 import build as native
+    if shutil.which("gcc") is None:
+        pytest.skip("no gcc")
+    native.build_all(verbose=False)
+    inc = os.path.join(ROOT, "include")
+    for header in sorted(os.listdir(inc)):
+        for compiler, std in (("gcc", "-std=c99"), ("g++", "-std=c++11")):
+            proc = subprocess.run([compiler, std, "-pedantic", "-Wall", "-Werror", "-I" + inc, "-x",
+                                   "c" if compiler == "gcc" else "c++", "-fsyntax-only", "-"],
+                                  input='#include "%s"\n' % header, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                                  universal_newlines=True)
+            assert proc.returncode == 0, (header, compiler, proc.stdout)
+    src = tmp_path / "link.c"
+    src.write_text('#include <stdio.h>\n#include "cuBERT.h"\n#include "cubert_b200.h"\n#include "cubert_kernels.h"\n'
+                   "int main(void) {\n"
+                   '    printf("%d %p %p %p\\n", cubk_version(), (void *) cuBERT_open, (void *) cubert_b200_compute_m,\n'
+                   "           (void *) cubk_masked_softmax_f16);\n"
+                   "    return cubk_bias_gelu_f32(0, 0, 0, 0, 0, 0) == CUBK_ERR_INVALID_ARG ? 0 : 1;\n}\n")
+    exe = str(tmp_path / "link")
+    lib = os.path.join(ROOT, "cubert_b200", "lib")
+    proc = subprocess.run(["gcc", "-std=c99", "-I" + inc, str(src), "-L" + lib, "-lcuBERT", "-lcubert_kernels",
+                           "-Wl,-rpath," + lib, "-o", exe], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                          universal_newlines=True)
+    assert proc.returncode == 0, proc.stdout
+    run = subprocess.run([exe], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, universal_newlines=True)
+    assert run.returncode == 0, run.stdout          # argument validation happens before any CUDA call

@@ -1,6 +1,6 @@
 """Isolated sweep of the fused kernels (BASELINE config 2): achieved HBM GB/s per kernel and shape.
 
-    python -m cubert_b200.sweep [--quick] [--only ln,gelu,softmax,embed,pool] [--dtype f16,f32]
+    python -m cubert_b200.sweep [--quick] [--large] [--only ln,gelu,softmax,embed,pool] [--dtype f16,f32]
                                 [--iters N] [--json out.json]
 
 Each case is timed with CUDA events on the launching stream: `iters` back-to-back launches
@@ -191,7 +191,7 @@ def case_pool(t, batch, seq, hidden, iters):
                 sec=sec, sets=n)
 
 
-def run(only=None, dtypes=("f16", "f32"), quick=False, iters=20):
+def run(only=None, dtypes=("f16", "f32"), quick=False, iters=20, large=False):
     kernels.load()
     peak, peak_kind = measured_peak_gbs()
     rows_list = [4096, 65536] if quick else [4096, 32768, 65536, 1048576]
@@ -200,6 +200,21 @@ def run(only=None, dtypes=("f16", "f32"), quick=False, iters=20):
     def want(k):
         return only is None or k in only
 
+    if large:
+        # the shapes of BERT-large at seq 512 (hidden 1024, intermediate 4096, 16 heads), 64 sequences
+        for t in dtypes:
+            if want("ln"):
+                results.append(case_ln(t, 65536, 1024, iters))
+            if want("gelu"):
+                results.append(case_gelu(t, 65536, 4096, iters))
+            if want("softmax"):
+                results.append(case_softmax(t, 64, 512, iters, heads=16))
+            if want("embed"):
+                results.append(case_embed(t, 64, 512, iters, hidden=1024, vocab=30522))
+            if want("pool"):
+                results.append(case_pool(t, 64, 512, 1024, iters))
+            torch.cuda.empty_cache()
+        dtypes = ()
     for t in dtypes:
         if want("ln"):
             for ch in (768, 3072):
@@ -238,12 +253,13 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", default=None)
     ap.add_argument("--no-graph", action="store_true", help="time plain stream launches instead of a graph replay")
+    ap.add_argument("--large", action="store_true", help="the BERT-large / seq 512 shapes instead of the config-2 sweep")
     a = ap.parse_args()
     global USE_GRAPH
     USE_GRAPH = not a.no_graph
     if not torch.cuda.is_available():
         sys.exit("cubert_b200.sweep needs a CUDA device")
-    results, peak, kind = run(a.only.split(",") if a.only else None, a.dtype.split(","), a.quick, a.iters)
+    results, peak, kind = run(a.only.split(",") if a.only else None, a.dtype.split(","), a.quick, a.iters, a.large)
     print("peak HBM %.0f GB/s (%s)" % (peak, kind))
     print("%-18s %-4s %-22s %10s %10s %8s %5s" % ("kernel", "dt", "shape", "us", "GB/s", "frac", "sets"))
     for r in results:

@@ -39,7 +39,8 @@ def request_stream(cfg, n, seq, seed):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--requests", type=int, default=100000)
-    ap.add_argument("--clients", type=int, default=0, help="client threads (default: 2 per replica)")
+    ap.add_argument("--clients", type=int, default=0,
+                    help="closed-loop client threads (default: one per replica; more only queue behind the replicas)")
     ap.add_argument("--dtype", default="f16", choices=["f16", "f32"])
     ap.add_argument("--seed", type=int, default=5)
     ap.add_argument("--distinct", type=int, default=2048, help="distinct requests generated; the stream cycles over them")
@@ -56,7 +57,7 @@ def main():
     m = model.Model(path, 32, seq, cfg["layers"], cfg["heads"], ct)
     os.unlink(path)
     replicas = m.info["replicas"]
-    clients = a.clients or 2 * replicas
+    clients = a.clients or replicas
     reqs = request_stream(cfg, min(a.distinct, a.requests), seq, a.seed)
     out_dtype = np.float16 if a.dtype == "f16" else np.float32
 

@@ -5,6 +5,18 @@
 
 namespace cubert {
 
+namespace {
+// Name, compute capability, bus id and memory of a GPU, in the form the reference prints them
+// (src/cuBERT/common.cpp:117-126).
+void describe_device(int device) {
+    cudaDeviceProp prop;
+    CUDA_CHECK(cudaGetDeviceProperties(&prop, device));
+    std::cerr << "Found device " << device << " with properties:\n  name: " << prop.name << " major: " << prop.major
+              << " minor: " << prop.minor << "\n  pciBusID: " << prop.pciBusID
+              << "\n  totalMemory: " << prop.totalGlobalMem << std::endl;
+}
+}  // namespace
+
 template <typename T>
 BertM<T>::BertM(const char *model_file, size_t max_batch_size_, size_t seq_length_, size_t num_hidden_layers,
                 size_t num_attention_heads)
@@ -30,51 +42,39 @@ BertM<T>::BertM(const char *model_file, size_t max_batch_size_, size_t seq_lengt
     }
     const size_t num_labels = graph.has("output_weights") ? graph.num_labels : 0;
 
-    for (int i = 0; i < count * per_gpu; ++i) {
-        const int device = i % count;  // replicas of one GPU are spread over the rotation
-        auto start = std::chrono::high_resolution_clock::now();
-        if (i < count) {
-            cudaDeviceProp prop;
-            CUDA_CHECK(cudaGetDeviceProperties(&prop, device));
-            std::cerr << "Found device " << device << " with properties:\n  name: " << prop.name
-                      << " major: " << prop.major << " minor: " << prop.minor << "\n  pciBusID: " << prop.pciBusID
-                      << "\n  totalMemory: " << prop.totalGlobalMem << std::endl;
+    const int total = count * per_gpu;
+    bert_instances.reserve((size_t) total);
+    mutex_instances.reserve((size_t) total);
+    for (int replica = 0; replica < total; ++replica) {
+        const int device = replica % count;  // the replicas of one GPU are spread over the rotation
+        const auto t0 = std::chrono::steady_clock::now();
+        if (replica < count) {
+            describe_device(device);
         }
         bert_instances.emplace_back(new Bert<T>(var, max_batch_size, seq_length, graph.vocab_size,
                                                 graph.type_vocab_size, graph.hidden_size, num_hidden_layers,
                                                 num_attention_heads, graph.intermediate_size, num_labels,
                                                 device));
         mutex_instances.emplace_back(new std::mutex());
-        auto finish = std::chrono::high_resolution_clock::now();
-        std::cerr << "device setup: " << device << ". Took "
-                  << std::chrono::duration_cast<std::chrono::milliseconds>(finish - start).count()
-                  << " milliseconds." << std::endl;
+        const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0);
+        // the reference's progress line (src/cuBERT/BertM.cpp:47-50), kept for tools that parse it
+        std::cerr << "device setup: " << device << ". Took " << ms.count() << " milliseconds." << std::endl;
     }
 }
 
 template <typename T>
 unsigned int BertM<T>::compute(size_t batch_size, int *input_ids, int8_t *input_mask, int8_t *segment_ids,
                                void *output, cuBERT_OutputType output_type) {
-    cuBERT_Output out;
-    switch (output_type) {
-        case cuBERT_LOGITS:
-            out.logits = output;
-            break;
-        case cuBERT_PROBS:
-            out.probs = output;
-            break;
-        case cuBERT_POOLED_OUTPUT:
-            out.pooled_output = output;
-            break;
-        case cuBERT_EMBEDDING_OUTPUT:
-            out.embedding_output = output;
-            break;
-        case cuBERT_SEQUENCE_OUTPUT:
-            out.sequence_output = output;
-            break;
-        default:
-            throw std::invalid_argument("invalid output type");
+    // the output type selects one field of cuBERT_Output (enum values 0..4, include/cuBERT.h)
+    static void *cuBERT_Output::*const kField[] = {&cuBERT_Output::logits, &cuBERT_Output::pooled_output,
+                                                   &cuBERT_Output::sequence_output, &cuBERT_Output::embedding_output,
+                                                   &cuBERT_Output::probs};
+    const int which = (int) output_type;
+    if (which < 0 || which >= (int) (sizeof(kField) / sizeof(kField[0]))) {
+        throw std::invalid_argument("invalid output type");
     }
+    cuBERT_Output out;
+    out.*kField[which] = output;
     return compute(batch_size, input_ids, input_mask, segment_ids, &out, false);
 }
 

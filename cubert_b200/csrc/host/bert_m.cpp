@@ -20,7 +20,7 @@ void describe_device(int device) {
 template <typename T>
 BertM<T>::BertM(const char *model_file, size_t max_batch_size_, size_t seq_length_, size_t num_hidden_layers,
                 size_t num_attention_heads)
-    : seq_length(seq_length_), max_batch_size(max_batch_size_), graph(model_file), rr(0) {
+    : seq_length(seq_length_), max_batch_size(max_batch_size_), weights_(model_file), calls_(0) {
     int count = 0;
     if (cudaGetDeviceCount(&count) != cudaSuccess) {
         (void) cudaGetLastError();
@@ -37,25 +37,25 @@ BertM<T>::BertM(const char *model_file, size_t max_batch_size_, size_t seq_lengt
     }
 
     std::unordered_map<std::string, const T *> var;
-    for (auto &kv : graph.var) {
+    for (auto &kv : weights_.var) {
         var[kv.first] = kv.second.data();
     }
-    const size_t num_labels = graph.has("output_weights") ? graph.num_labels : 0;
+    const size_t num_labels = weights_.has("output_weights") ? weights_.num_labels : 0;
 
     const int total = count * per_gpu;
-    bert_instances.reserve((size_t) total);
-    mutex_instances.reserve((size_t) total);
+    replicas_.reserve((size_t) total);
+    locks_.reserve((size_t) total);
     for (int replica = 0; replica < total; ++replica) {
         const int device = replica % count;  // the replicas of one GPU are spread over the rotation
         const auto t0 = std::chrono::steady_clock::now();
         if (replica < count) {
             describe_device(device);
         }
-        bert_instances.emplace_back(new Bert<T>(var, max_batch_size, seq_length, graph.vocab_size,
-                                                graph.type_vocab_size, graph.hidden_size, num_hidden_layers,
-                                                num_attention_heads, graph.intermediate_size, num_labels,
+        replicas_.emplace_back(new Bert<T>(var, max_batch_size, seq_length, weights_.vocab_size,
+                                                weights_.type_vocab_size, weights_.hidden_size, num_hidden_layers,
+                                                num_attention_heads, weights_.intermediate_size, num_labels,
                                                 device));
-        mutex_instances.emplace_back(new std::mutex());
+        locks_.emplace_back(new std::mutex());
         const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0);
         // the reference's progress line (src/cuBERT/BertM.cpp:47-50), kept for tools that parse it
         std::cerr << "device setup: " << device << ". Took " << ms.count() << " milliseconds." << std::endl;
@@ -81,9 +81,9 @@ unsigned int BertM<T>::compute(size_t batch_size, int *input_ids, int8_t *input_
 template <typename T>
 unsigned int BertM<T>::compute(size_t batch_size, int *input_ids, int8_t *input_mask, int8_t *segment_ids,
                                cuBERT_Output *output, bool output_to_float) {
-    const unsigned int choice = (unsigned int) (rr.fetch_add(1) % bert_instances.size());
-    Bert<T> *bert = bert_instances[choice].get();
-    std::lock_guard<std::mutex> lg(*mutex_instances[choice]);
+    const unsigned int choice = (unsigned int) (calls_.fetch_add(1) % replicas_.size());
+    Bert<T> *bert = replicas_[choice].get();
+    std::lock_guard<std::mutex> lg(*locks_[choice]);
     if ((int) choice == failing_replica) {
         throw RuntimeError("injected failure on replica " + std::to_string(choice));
     }

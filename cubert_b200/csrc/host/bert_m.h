@@ -28,19 +28,19 @@ public:
     unsigned int compute(size_t batch_size, int *input_ids, int8_t *input_mask, int8_t *segment_ids,
                          cuBERT_Output *output, bool output_to_float);
 
-    size_t replicas() const { return bert_instances.size(); }
-    Bert<T> *replica(size_t i) { return bert_instances.at(i).get(); }
+    size_t replicas() const { return replicas_.size(); }
+    Bert<T> *replica(size_t i) { return replicas_.at(i).get(); }
 
     size_t seq_length;
     size_t max_batch_size;
 
 private:
-    FrozenGraph<T> graph;
-    std::vector<std::unique_ptr<Bert<T>>> bert_instances;
-    std::vector<std::unique_ptr<std::mutex>> mutex_instances;
+    FrozenGraph<T> weights_;
+    std::vector<std::unique_ptr<Bert<T>>> replicas_;
+    std::vector<std::unique_ptr<std::mutex>> locks_;
     // The reference counts in a uint8_t, which skews the rotation whenever 256 is not a multiple
     // of the replica count (src/cuBERT/BertM.h:44); a wide counter keeps it even.
-    std::atomic<uint64_t> rr;
+    std::atomic<uint64_t> calls_;
     // Host-side fault injection for tests: calls routed to this replica fail with a RuntimeError before
     // anything reaches its GPU (CUBERT_INJECT_REPLICA_FAILURE=<replica>; -1, the default, injects nothing).
     int failing_replica = -1;

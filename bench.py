@@ -74,12 +74,33 @@ L2_NOTE = ("no explicit L2 flush: one step streams the model's weights (218 MB o
            "far more than the 126 MB L2")
 
 
+def device_for_rank(visible, local_rank):
+    """The entry of a CUDA_VISIBLE_DEVICES list (None or "" = every GPU of the machine, in order) that a
+    rank works on: its own entry, or its own number when the list is absent or too short. Entries may be
+    indices or GPU UUIDs; the entry is returned as the string to put into CUDA_VISIBLE_DEVICES."""
+    ids = [v.strip() for v in (visible or "").split(",") if v.strip() != ""]
+    if ids and local_rank < len(ids):
+        return ids[local_rank]
+    return str(local_rank)
+
+
+def narrow_to_one_gpu(env, local_rank):
+    """Restrict the process to one GPU, whatever the launcher left visible: the library builds a replica
+    on every GPU it can see (as the reference does), and a bench process times exactly one. This holds
+    for a single process on a multi-GPU machine just as for one rank of many. The list the process
+    inherited is kept in CUBERT_BENCH_PARENT_VISIBLE. Returns the chosen entry."""
+    if "CUBERT_BENCH_PARENT_VISIBLE" not in env:
+        env["CUBERT_BENCH_PARENT_VISIBLE"] = env.get("CUDA_VISIBLE_DEVICES", "")
+    chosen = device_for_rank(env["CUBERT_BENCH_PARENT_VISIBLE"], local_rank)
+    env["CUDA_VISIBLE_DEVICES"] = chosen
+    return chosen
+
+
 def physical_gpu_index():
+    """nvidia-smi index of this rank's GPU (for the clock samples)."""
     vis = os.environ.get("CUBERT_BENCH_PARENT_VISIBLE", os.environ.get("CUDA_VISIBLE_DEVICES", ""))
-    ids = [v for v in vis.split(",") if v.strip() != ""]
-    if ids and LOCAL_RANK < len(ids) and ids[LOCAL_RANK].isdigit():
-        return int(ids[LOCAL_RANK])
-    return LOCAL_RANK
+    d = device_for_rank(vis, LOCAL_RANK)
+    return int(d) if d.isdigit() else LOCAL_RANK
 
 
 class ClockSampler:
@@ -242,9 +263,9 @@ def run_reference_arm(args):
 
 def run_ours(args):
     # one replica per process: restrict the library to this rank's GPU before CUDA starts
-    if WORLD > 1:
-        os.environ["CUBERT_BENCH_PARENT_VISIBLE"] = os.environ.get("CUDA_VISIBLE_DEVICES", "")
-        os.environ["CUDA_VISIBLE_DEVICES"] = str(physical_gpu_index())
+    # (also when this is the only process: on a machine with several GPUs the library would otherwise
+    # build a replica on each of them)
+    narrow_to_one_gpu(os.environ, LOCAL_RANK)
     import numpy as np
     from cubert_b200 import model, synthetic
     model.load()  # before torch: the process then binds the toolkit's cuBLAS, not the older one torch bundles
@@ -282,7 +303,10 @@ def run_ours(args):
     m = model.Model(path, B, S, cfg["layers"], cfg["heads"],
                     model.ComputeType.HALF if half else model.ComputeType.FLOAT)
     os.unlink(path)
-    assert m.info["replicas"] == 1, "one replica per process expected, got %d" % m.info["replicas"]
+    if m.info["replicas"] != 1:
+        sys.exit("bench.py times one replica per process; the library built %d (CUDA_VISIBLE_DEVICES=%r, "
+                 "CUBERT_NUM_MODELS_PER_GPU=%r)" % (m.info["replicas"], os.environ.get("CUDA_VISIBLE_DEVICES"),
+                                                    os.environ.get("CUBERT_NUM_MODELS_PER_GPU")))
 
     # every rank works on its own batch of the seeded stream
     ids, mask, seg, lens = synthetic.random_inputs(cfg, B, S, replicas.stream_seed(WORKLOAD["seed"], RANK),

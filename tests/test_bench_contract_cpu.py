@@ -74,3 +74,24 @@ def test_reference_arm_prints_one_contract_line(workload):
     assert "sample" in base
     assert line["e2e"] == {"value": line["value"], "unit": line["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert line["gpu_launches"] == 0
+
+
+def test_a_bench_process_sees_one_gpu_whatever_the_launcher_left_visible():
+    """The library builds a replica on every visible GPU, a bench process times one: the process narrows
+    CUDA_VISIBLE_DEVICES to its own entry, also when it is the only process on an 8-GPU machine."""
+    bench = _bench_module()
+    # a single process, WORLD_SIZE unset, eight GPUs visible (explicitly or by default)
+    env = {"CUDA_VISIBLE_DEVICES": "0,1,2,3,4,5,6,7"}
+    assert bench.narrow_to_one_gpu(env, 0) == "0" and env["CUDA_VISIBLE_DEVICES"] == "0"
+    assert env["CUBERT_BENCH_PARENT_VISIBLE"] == "0,1,2,3,4,5,6,7"
+    env = {}
+    assert bench.narrow_to_one_gpu(env, 0) == "0" and env["CUDA_VISIBLE_DEVICES"] == "0"
+    # a launcher that hands out a subset: rank 1 of four on GPUs 4..7
+    env = {"CUDA_VISIBLE_DEVICES": "4,5,6,7"}
+    assert bench.narrow_to_one_gpu(env, 1) == "5" and env["CUDA_VISIBLE_DEVICES"] == "5"
+    # narrowing twice (a re-entered process) keeps the first choice
+    assert bench.narrow_to_one_gpu(env, 1) == "5"
+    # ranks without a list take their own number; UUID entries pass through
+    assert bench.device_for_rank("", 3) == "3" and bench.device_for_rank(None, 0) == "0"
+    assert bench.device_for_rank("GPU-aaaa,GPU-bbbb", 1) == "GPU-bbbb"
+    assert bench.device_for_rank("2", 5) == "5"

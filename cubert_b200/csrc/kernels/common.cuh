@@ -12,6 +12,9 @@ namespace cubk {
 // ---------------------------------------------------------------- launch status
 void set_last_error(cudaError_t err);
 
+// Current value of a CUBK_OPT_* switch (environment default, or what cubk_set_option stored).
+int option(int id);
+
 inline int check_launch() {
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) {
@@ -125,35 +128,45 @@ struct Vec<__half> {
 // Blackwell executes add/mul/fma on two float32 values with one instruction (.f32x2); the
 // kernels below are short of issue slots rather than of FP32 lanes, so halving the
 // instruction count of the arithmetic is what buys bandwidth.
+#ifdef CUBK_F32X2_ASM
 __device__ __forceinline__ uint64_t pack_f2(float2 a) {
     uint64_t r;
     asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a.x), "f"(a.y));
     return r;
 }
-
 __device__ __forceinline__ float2 unpack_f2(uint64_t r) {
     float2 a;
     asm("mov.b64 {%0, %1}, %2;" : "=f"(a.x), "=f"(a.y) : "l"(r));
     return a;
 }
-
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
     uint64_t d;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(pack_f2(a)), "l"(pack_f2(b)), "l"(pack_f2(c)));
     return unpack_f2(d);
 }
-
 __device__ __forceinline__ float2 add2(float2 a, float2 b) {
     uint64_t d;
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack_f2(a)), "l"(pack_f2(b)));
     return unpack_f2(d);
 }
-
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) {
     uint64_t d;
     asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack_f2(a)), "l"(pack_f2(b)));
     return unpack_f2(d);
 }
+#else
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    return __ffma2_rn(a, b, c);
+}
+
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    return __fadd2_rn(a, b);
+}
+
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    return __fmul2_rn(a, b);
+}
+#endif
 
 __device__ __forceinline__ float2 splat2(float a) {
     return make_float2(a, a);
@@ -196,6 +209,57 @@ struct Vec2<__half> {
         return make_uint4(w[0], w[1], w[2], w[3]);
     }
 };
+
+// float32 + binary16 in one instruction (PTX add.rn.f32.f16: the binary16 operand is widened exactly,
+// the sum is rounded once, as convert-then-add would): v[e] += float(h[e]) for the 8 halves of a vector.
+__device__ __forceinline__ float add_f32_f16(uint16_t h, float c) {
+    float d;
+    asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"(h), "f"(c));
+    return d;
+}
+
+__device__ __forceinline__ void accumulate_halves(const uint4 &raw, float2 (&v)[4]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint16_t lo, hi;
+        asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(w[i]));
+        v[i] = make_float2(add_f32_f16(lo, v[i].x), add_f32_f16(hi, v[i].y));
+    }
+}
+
+// v += float(raw) for one 16-byte vector of storage type T. MIXED picks the one-instruction
+// binary16 form above over convert + packed add (same result bit for bit).
+template <typename T, bool MIXED>
+__device__ __forceinline__ void accumulate_vec(const uint4 &raw, float2 (&v)[Vec2<T>::PAIRS]);
+
+template <>
+__device__ __forceinline__ void accumulate_vec<float, false>(const uint4 &raw, float2 (&v)[2]) {
+    float2 t[2];
+    Vec2<float>::unpack(raw, t);
+    v[0] = __fadd2_rn(v[0], t[0]);
+    v[1] = __fadd2_rn(v[1], t[1]);
+}
+
+template <>
+__device__ __forceinline__ void accumulate_vec<float, true>(const uint4 &raw, float2 (&v)[2]) {
+    accumulate_vec<float, false>(raw, v);
+}
+
+template <>
+__device__ __forceinline__ void accumulate_vec<__half, false>(const uint4 &raw, float2 (&v)[4]) {
+    float2 t[4];
+    Vec2<__half>::unpack(raw, t);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[i] = __fadd2_rn(v[i], t[i]);
+    }
+}
+
+template <>
+__device__ __forceinline__ void accumulate_vec<__half, true>(const uint4 &raw, float2 (&v)[4]) {
+    accumulate_halves(raw, v);
+}
 
 // Streaming 128-bit load: data that is read once (activations, scores).
 __device__ __forceinline__ uint4 ld_stream(const void *p) {
@@ -282,14 +346,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return done != 0;
 }
 
-// Waits for the phase with the given parity to complete, giving up after kMaxBarrierPolls polls
-// (each poll may itself block for a hardware-defined short time). Returns false on give-up.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Waits for the phase with the given parity to complete. The wait is bounded twice over: by a
+// deadline on the GPU's nanosecond timer (kBarrierWaitNs; read every 64 polls, so a wait that
+// completes at once never reads it) and by a poll count (which alone bounds the short waits of the
+// self-test). Returns false on give-up.
 constexpr uint32_t kMaxBarrierPolls = 1u << 22;
+constexpr uint64_t kBarrierWaitNs = 200ull * 1000 * 1000;  // 0.2 s: five orders above a copy's latency
 
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, uint32_t polls = kMaxBarrierPolls) {
+    uint64_t deadline = 0;
     for (uint32_t i = 0; i < polls; ++i) {
         if (mbar_try_wait(bar, parity)) {
             return true;
+        }
+        if ((i & 63u) == 63u) {
+            const uint64_t now = global_timer_ns();
+            if (deadline == 0) {
+                deadline = now + kBarrierWaitNs;
+            } else if (now > deadline) {
+                return false;
+            }
         }
     }
     return false;

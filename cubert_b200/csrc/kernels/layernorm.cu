@@ -13,8 +13,6 @@
 //
 // HBM traffic per row: K2 reads x and residual and writes out (3 * C * e bytes);
 // K1 reads one gathered word row and writes out (2 * H * e bytes) plus 5 index bytes.
-#include <stdlib.h>
-
 #include "common.cuh"
 
 namespace cubk {
@@ -501,6 +499,297 @@ embed_ln_bulk_kernel(const int32_t *ids, const int8_t *segment_ids, const T *wor
     }
 }
 
+// ------------------------------------------------------------------ K2 / K1 for rows of exactly 32 * VPT vectors
+// The shapes BERT runs (hidden 768 and 1024 in either storage type) fill a warp exactly, so these
+// kernels carry no per-vector bounds predicate and no zero fill; row addresses are vector pointers
+// advanced by a constant; the mean uses a precomputed 1 / channels and the scale one rsqrt
+// (MUFU.RSQ, 2 ulp; the reference's GPU body uses rsqrtf as well, op/LayerNorm.cu:70). A warp works
+// on RPP rows per pass: their shuffle reductions interleave, and gamma / beta / bias are read from
+// shared memory once per pass instead of once per row.
+constexpr int kRowsBlock = 256;
+
+template <typename T, int VPT, int RPP>
+__device__ __forceinline__ void normalise_store_rows(float2 (&v)[RPP][VPT][Vec2<T>::PAIRS], int lane, float inv_channels,
+                                                     const float4 *s_gamma, const float4 *s_beta, uint4 *(&dst)[RPP],
+                                                     const bool (&live)[RPP]) {
+    constexpr int PAIRS = Vec2<T>::PAIRS;
+    constexpr int NVEC = 32 * VPT;
+    float sum[RPP];
+#pragma unroll
+    for (int p = 0; p < RPP; ++p) {
+        float2 s2 = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+#pragma unroll
+            for (int e = 0; e < PAIRS; ++e) {
+                s2 = add2(s2, v[p][k][e]);
+            }
+        }
+        sum[p] = s2.x + s2.y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int p = 0; p < RPP; ++p) {
+            sum[p] += __shfl_xor_sync(0xffffffffu, sum[p], o, 32);
+        }
+    }
+    float sq[RPP];
+#pragma unroll
+    for (int p = 0; p < RPP; ++p) {
+        const float2 neg_mean = splat2(-sum[p] * inv_channels);
+        float2 q2 = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+#pragma unroll
+            for (int e = 0; e < PAIRS; ++e) {
+                v[p][k][e] = add2(v[p][k][e], neg_mean);  // keep the centred value
+                q2 = fma2(v[p][k][e], v[p][k][e], q2);
+            }
+        }
+        sq[p] = q2.x + q2.y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int p = 0; p < RPP; ++p) {
+            sq[p] += __shfl_xor_sync(0xffffffffu, sq[p], o, 32);
+        }
+    }
+    float2 rstd[RPP];
+#pragma unroll
+    for (int p = 0; p < RPP; ++p) {
+        rstd[p] = splat2(rsqrtf(fmaf(sq[p], inv_channels, kLayerNormEps)));
+    }
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int idx = lane + 32 * k;
+        float2 g[PAIRS], b[PAIRS];
+        load_param<T>(s_gamma, NVEC, idx, g);
+        load_param<T>(s_beta, NVEC, idx, b);
+#pragma unroll
+        for (int p = 0; p < RPP; ++p) {
+            float2 o[PAIRS];
+#pragma unroll
+            for (int e = 0; e < PAIRS; ++e) {
+                o[e] = fma2(mul2(g[e], rstd[p]), v[p][k][e], b[e]);  // beta + (gamma * rstd) * (t - mean)
+            }
+            if (live[p]) {
+                dst[p][idx] = Vec2<T>::pack(o);
+            }
+        }
+    }
+}
+
+// K2. PREFETCH: the next pass's rows are requested before the current ones are reduced.
+template <typename T, int VPT, int RPP, bool PREFETCH, bool MIXED>
+__global__ void __launch_bounds__(kRowsBlock)
+bias_residual_ln_rows_kernel(const T *x, const T *bias, const T *residual, const T *gamma, const T *beta, T *out,
+                             int64_t rows, float inv_channels) {
+    constexpr int EPV = Vec<T>::EPV;
+    constexpr int PAIRS = Vec2<T>::PAIRS;
+    constexpr int NVEC = 32 * VPT;
+    constexpr int WARPS = kRowsBlock / 32;
+    extern __shared__ float4 s_params[];
+    const float4 *s_gamma = s_params;
+    const float4 *s_beta = s_params + (EPV / 4) * NVEC;
+    const float4 *s_bias = s_params + 2 * (EPV / 4) * NVEC;
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const uint4 *xv = reinterpret_cast<const uint4 *>(x) + lane;
+    const uint4 *rv = reinterpret_cast<const uint4 *>(residual) + lane;
+    uint4 *ov = reinterpret_cast<uint4 *>(out);
+    const int64_t stride = (int64_t) gridDim.x * (WARPS * RPP);
+    int64_t row = ((int64_t) blockIdx.x * WARPS + warp) * RPP;
+
+    uint4 rx[RPP][VPT], rr[RPP][VPT];
+    auto issue_loads = [&](int64_t r0) {
+#pragma unroll
+        for (int p = 0; p < RPP; ++p) {
+            const int64_t r = r0 + p < rows ? r0 + p : rows - 1;  // a row past the end repeats the last one
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                rx[p][k] = __ldcs(xv + r * NVEC + 32 * k);
+                rr[p][k] = __ldcs(rv + r * NVEC + 32 * k);
+            }
+        }
+    };
+    // The first rows' loads go out before the parameters are staged, so that the two latencies overlap.
+    if (PREFETCH && row < rows) {
+        issue_loads(row);
+    }
+    stage_param<T>(gamma, s_params, NVEC, threadIdx.x, kRowsBlock);
+    stage_param<T>(beta, s_params + (EPV / 4) * NVEC, NVEC, threadIdx.x, kRowsBlock);
+    stage_param<T>(bias, s_params + 2 * (EPV / 4) * NVEC, NVEC, threadIdx.x, kRowsBlock);
+    __syncthreads();
+
+    for (; row < rows; row += stride) {
+        if (!PREFETCH) {
+            issue_loads(row);
+        }
+        float2 v[RPP][VPT][PAIRS];
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            float2 b[PAIRS];
+            load_param<T>(s_bias, NVEC, lane + 32 * k, b);
+#pragma unroll
+            for (int p = 0; p < RPP; ++p) {
+#pragma unroll
+                for (int e = 0; e < PAIRS; ++e) {
+                    v[p][k][e] = b[e];
+                }
+                accumulate_vec<T, MIXED>(rx[p][k], v[p][k]);  // (x + bias)
+                accumulate_vec<T, MIXED>(rr[p][k], v[p][k]);  //          + residual
+            }
+        }
+        uint4 *dst[RPP];
+        bool live[RPP];
+#pragma unroll
+        for (int p = 0; p < RPP; ++p) {
+            live[p] = row + p < rows;
+            dst[p] = ov + (row + p) * NVEC;
+        }
+        // The raw registers are free again: fetch the next rows while these are reduced.
+        if (PREFETCH && row + stride < rows) {
+            issue_loads(row + stride);
+        }
+        normalise_store_rows<T, VPT, RPP>(v, lane, inv_channels, s_gamma, s_beta, dst, live);
+    }
+}
+
+// K1. Tokens are walked position-major as in embed_ln_kernel (the position row stays in registers
+// as float32 while a warp works through sequences at one position); the token-type rows sit in shared
+// memory beside gamma and beta (float32, up to kMaxTypeRowsSmem of them); the token indices are read
+// two steps ahead and the gathered word row one step ahead of the row being normalised.
+constexpr int kMaxTypeRowsSmem = 4;
+
+template <typename T, int VPT, bool MIXED, int MIN_BLOCKS>
+__global__ void __launch_bounds__(kRowsBlock, MIN_BLOCKS)
+embed_ln_rows_kernel(const int32_t *ids, const int8_t *segment_ids, const T *word, const T *pos, const T *type,
+                     const T *gamma, const T *beta, T *out, uint32_t tokens, uint32_t batch, uint32_t seq, int vocab,
+                     int type_vocab, uint32_t *status, float inv_hidden) {
+    constexpr int EPV = Vec<T>::EPV;
+    constexpr int PAIRS = Vec2<T>::PAIRS;
+    constexpr int NVEC = 32 * VPT;
+    constexpr int WARPS = kRowsBlock / 32;
+    constexpr int PV = (EPV / 4) * NVEC;  // float4 per staged row
+    extern __shared__ float4 s_params[];
+    const float4 *s_gamma = s_params;
+    const float4 *s_beta = s_params + PV;
+    const float4 *s_type = s_params + 2 * PV;
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const uint4 *wv = reinterpret_cast<const uint4 *>(word) + lane;
+    const uint4 *pv = reinterpret_cast<const uint4 *>(pos) + lane;
+    uint4 *ov = reinterpret_cast<uint4 *>(out);
+
+    // even split of the position-major index range j = s * batch + b over all warps of the grid
+    const uint32_t total_warps = gridDim.x * WARPS;
+    const uint32_t w = blockIdx.x * WARPS + warp;
+    const uint32_t share = tokens / total_warps;
+    const uint32_t extra = tokens - share * total_warps;
+    const uint32_t j_begin = w * share + min(w, extra);
+    const uint32_t j_count = share + (w < extra ? 1u : 0u);
+
+    // (s, b) of the step whose indices are fetched next; token = b * seq + s
+    uint32_t fs = j_begin / batch;
+    uint32_t fb = j_begin - fs * batch;
+    uint32_t fetched = 0;
+    int id_q = 0, seg_q = 0;       // indices of the row after the one in flight
+    auto fetch_indices = [&]() {   // reads the indices of step `fetched`, if there is one
+        if (fetched < j_count) {
+            const uint32_t token = fb * seq + fs;
+            id_q = ids[token];
+            seg_q = segment_ids[token];
+            if (++fb == batch) {
+                fb = 0;
+                ++fs;
+            }
+        }
+        ++fetched;
+    };
+    uint4 rw[VPT];
+    int seg_in_flight = 0;
+    auto issue_word_row = [&]() {  // requests word[id_q]; its segment id travels with it
+        int wid = id_q, tid = seg_q;
+        uint32_t bad = 0;
+        if (wid < 0 || wid >= vocab) {
+            bad |= CUBK_STATUS_BAD_TOKEN_ID;
+            wid = min(max(wid, 0), vocab - 1);
+        }
+        if (tid < 0 || tid >= type_vocab) {
+            bad |= CUBK_STATUS_BAD_SEGMENT_ID;
+            tid = min(max(tid, 0), type_vocab - 1);
+        }
+        if (bad != 0 && status != nullptr && lane == 0) {
+            atomicOr(status, bad);
+        }
+        seg_in_flight = tid;
+        const uint4 *src = wv + (size_t) wid * NVEC;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            rw[k] = __ldg(src + 32 * k);
+        }
+    };
+
+    fetch_indices();
+    if (j_count > 0) {
+        issue_word_row();
+    }
+    fetch_indices();
+    stage_param<T>(gamma, s_params, NVEC, threadIdx.x, kRowsBlock);
+    stage_param<T>(beta, s_params + PV, NVEC, threadIdx.x, kRowsBlock);
+    for (int t = 0; t < type_vocab; ++t) {
+        stage_param<T>(type + (size_t) t * (NVEC * EPV), s_params + (2 + t) * PV, NVEC, threadIdx.x, kRowsBlock);
+    }
+    __syncthreads();
+
+    float2 pos_row[VPT][PAIRS];
+    uint32_t s = j_begin / batch;
+    uint32_t b = j_begin - s * batch;
+    bool new_pos = true;
+    for (uint32_t step = 0; step < j_count; ++step) {
+        if (new_pos) {  // uniform within the warp
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                Vec2<T>::unpack(__ldg(pv + (size_t) s * NVEC + 32 * k), pos_row[k]);
+            }
+        }
+        const float4 *s_trow = s_type + seg_in_flight * PV;
+        float2 v[1][VPT][PAIRS];
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            float2 t[PAIRS];
+            load_param<T>(s_trow, NVEC, lane + 32 * k, t);
+#pragma unroll
+            for (int e = 0; e < PAIRS; ++e) {
+                v[0][k][e] = pos_row[k][e];
+            }
+            accumulate_vec<T, MIXED>(rw[k], v[0][k]);  // (word + pos)
+#pragma unroll
+            for (int e = 0; e < PAIRS; ++e) {
+                v[0][k][e] = add2(v[0][k][e], t[e]);   //             + type, the reference's order
+            }
+        }
+        uint4 *dst[1] = {ov + ((size_t) b * seq + s) * NVEC};
+        const bool live[1] = {true};
+        // the raw registers are free again: request the next word row, then the indices after it
+        if (step + 1 < j_count) {
+            issue_word_row();
+        }
+        fetch_indices();
+        new_pos = false;
+        if (++b == batch) {
+            b = 0;
+            ++s;
+            new_pos = true;
+        }
+        normalise_store_rows<T, VPT, 1>(v, lane, inv_hidden, s_gamma, s_beta, dst, live);
+    }
+}
+
 // The give-up path of the bounded barrier wait, on its own: one warp waits for a phase that nothing
 // will ever complete (no copy is issued, no thread arrives), runs out of its `polls` and reports it
 // the way the staged kernels do. Nothing is in flight, so there is nothing to drain.
@@ -615,14 +904,50 @@ constexpr size_t kMaxParamSmem = 47 * 1024;  // dynamic + static stay below the 
 // Whether K1 stages its word rows through shared memory. Measured on B200 (hidden 768): with float32
 // rows (3 KB) and 32768 tokens the staged kernel takes 30 us against 33 us, with 4096 tokens 8.4 us
 // against 7.6 us, and with binary16 rows (1.5 KB) 25 us against 22 us, where the per-row instruction
-// cost rather than the bytes in flight sets the pace. So: rows of 2 KB or more and at least 16384 tokens.
-// CUBK_BULK_COPY=0 / =1 in the environment forces the choice (read on every call).
+// cost rather than the bytes in flight sets the pace. So: rows of 2 KB or more and at least 16384 tokens,
+// unless CUBK_OPT_EMBED_STAGED_ROWS forces the choice.
 static bool use_bulk_rows(size_t row_bytes, int64_t tokens) {
-    const char *v = getenv("CUBK_BULK_COPY");
-    if (v != nullptr && (v[0] == '0' || v[0] == '1')) {
-        return v[0] == '1';
+    const int forced = option(CUBK_OPT_EMBED_STAGED_ROWS);
+    if (forced == 0 || forced == 1) {
+        return forced == 1;
     }
     return row_bytes >= 2048 && tokens >= 16384;
+}
+
+static int k2_variant() {
+    return option(CUBK_OPT_EXACT_WIDTH_ROWS);
+}
+
+static int k1_variant() {
+    return option(CUBK_OPT_EXACT_WIDTH_EMBED);
+}
+
+// Launch of the exact-width K2 for one VPT; false = this variant / width is not built.
+template <typename T, int VPT>
+bool launch_ln_rows(int variant, const T *x, const T *bias, const T *residual, const T *gamma, const T *beta, T *out,
+                    int64_t rows, int channels, cudaStream_t stream) {
+    const size_t smem = sizeof(float) * 3 * (size_t) channels;
+    const float inv = 1.f / (float) channels;
+#define ROWS_LAUNCH(RPP, PREFETCH, MIXED)                                                                  \
+    {                                                                                                      \
+        static OccupancyCache cache;                                                                       \
+        auto kernel = bias_residual_ln_rows_kernel<T, VPT, RPP, PREFETCH, MIXED>;                          \
+        int64_t grid = (rows + (kRowsBlock / 32) * RPP - 1) / ((kRowsBlock / 32) * RPP);                   \
+        const int resident = resident_blocks(kernel, kRowsBlock, smem, &cache);                            \
+        if (grid > resident) grid = resident;                                                              \
+        kernel<<<(unsigned) grid, kRowsBlock, smem, stream>>>(x, bias, residual, gamma, beta, out, rows, inv); \
+        return true;                                                                                       \
+    }
+    constexpr bool HALF = sizeof(T) == 2;
+    switch (variant) {
+        case 1: ROWS_LAUNCH(1, true, false)
+        case 2: ROWS_LAUNCH(1, true, HALF)
+        case 3: ROWS_LAUNCH(2, false, false)
+        case 4: ROWS_LAUNCH(2, false, HALF)
+        case 5: ROWS_LAUNCH(2, true, false)
+        default: return false;
+    }
+#undef ROWS_LAUNCH
 }
 
 template <typename T>
@@ -642,6 +967,21 @@ int bias_residual_ln(const T *x, const T *bias, const T *residual, const T *gamm
                         (bias == nullptr || aligned16(bias)) && (residual == nullptr || aligned16(residual));
     if (vec_ok) {
         const int nvec = channels / EPV;
+        if (bias != nullptr && residual != nullptr && nvec % 32 == 0 && k2_variant() > 0) {
+            bool launched = false;
+            switch (nvec / 32) {
+                case 1: launched = launch_ln_rows<T, 1>(k2_variant(), x, bias, residual, gamma, beta, out, rows, channels, stream); break;
+                case 2: launched = launch_ln_rows<T, 2>(k2_variant(), x, bias, residual, gamma, beta, out, rows, channels, stream); break;
+                case 3: launched = launch_ln_rows<T, 3>(k2_variant(), x, bias, residual, gamma, beta, out, rows, channels, stream); break;
+                case 4: launched = launch_ln_rows<T, 4>(k2_variant(), x, bias, residual, gamma, beta, out, rows, channels, stream); break;
+                case 6: launched = launch_ln_rows<T, 6>(k2_variant(), x, bias, residual, gamma, beta, out, rows, channels, stream); break;
+                case 8: launched = launch_ln_rows<T, 8>(k2_variant(), x, bias, residual, gamma, beta, out, rows, channels, stream); break;
+                default: break;
+            }
+            if (launched) {
+                return check_launch();
+            }
+        }
 #define LAUNCH(TPR, VPT, BLOCK, PERSISTENT)                                                           \
     {                                                                                                 \
         static OccupancyCache cache;                                                                  \
@@ -703,6 +1043,40 @@ bool launch_embed_bulk_depth(const int32_t *ids, const int8_t *segment_ids, cons
                                         hidden, nvec, vocab, type_vocab, status, stream);
 }
 
+// Launch of the exact-width K1 for one VPT; false = this variant is not built.
+template <typename T, int VPT>
+bool launch_embed_rows(int variant, const int32_t *ids, const int8_t *segment_ids, const T *word, const T *pos,
+                       const T *type, const T *gamma, const T *beta, T *out, int64_t tokens, int batch, int seq,
+                       int hidden, int vocab, int type_vocab, uint32_t *status, cudaStream_t stream) {
+    const size_t smem = sizeof(float) * (2 + (size_t) type_vocab) * (size_t) hidden;
+    if (smem > kMaxParamSmem) {
+        return false;
+    }
+    const float inv = 1.f / (float) hidden;
+#define ROWS_LAUNCH(MIXED, MIN_BLOCKS)                                                                     \
+    {                                                                                                      \
+        static OccupancyCache cache;                                                                       \
+        auto kernel = embed_ln_rows_kernel<T, VPT, MIXED, MIN_BLOCKS>;                                     \
+        int64_t grid = (tokens + (kRowsBlock / 32) - 1) / (kRowsBlock / 32);                               \
+        const int resident = resident_blocks(kernel, kRowsBlock, smem, &cache);                            \
+        if (grid > resident) grid = resident;                                                              \
+        kernel<<<(unsigned) grid, kRowsBlock, smem, stream>>>(ids, segment_ids, word, pos, type, gamma,    \
+                                                              beta, out, (uint32_t) tokens,                \
+                                                              (uint32_t) batch, (uint32_t) seq, vocab,     \
+                                                              type_vocab, status, inv);                    \
+        return true;                                                                                       \
+    }
+    constexpr bool HALF = sizeof(T) == 2;
+    switch (variant) {
+        case 1: ROWS_LAUNCH(false, 1)
+        case 2: ROWS_LAUNCH(HALF, 1)
+        case 3: ROWS_LAUNCH(false, (HALF && VPT == 3 ? 3 : 1))
+        case 4: ROWS_LAUNCH(HALF, (HALF && VPT == 3 ? 3 : 1))
+        default: return false;
+    }
+#undef ROWS_LAUNCH
+}
+
 template <typename T>
 int embed_ln(const int32_t *ids, const int8_t *segment_ids, const T *word, const T *pos, const T *type,
              const T *gamma, const T *beta, int batch, int seq, int hidden, int vocab, int type_vocab,
@@ -739,6 +1113,21 @@ int embed_ln(const int32_t *ids, const int8_t *segment_ids, const T *word, const
             else if (nvec <= 192) { BULK(6); }
             else { BULK(8); }
 #undef BULK
+            if (launched) {
+                return check_launch();
+            }
+        }
+        if (nvec % 32 == 0 && type_vocab <= kMaxTypeRowsSmem && k1_variant() > 0) {
+            bool launched = false;
+            switch (nvec / 32) {
+                case 1: launched = launch_embed_rows<T, 1>(k1_variant(), ids, segment_ids, word, pos, type, gamma, beta, out, tokens, batch, seq, hidden, vocab, type_vocab, status, stream); break;
+                case 2: launched = launch_embed_rows<T, 2>(k1_variant(), ids, segment_ids, word, pos, type, gamma, beta, out, tokens, batch, seq, hidden, vocab, type_vocab, status, stream); break;
+                case 3: launched = launch_embed_rows<T, 3>(k1_variant(), ids, segment_ids, word, pos, type, gamma, beta, out, tokens, batch, seq, hidden, vocab, type_vocab, status, stream); break;
+                case 4: launched = launch_embed_rows<T, 4>(k1_variant(), ids, segment_ids, word, pos, type, gamma, beta, out, tokens, batch, seq, hidden, vocab, type_vocab, status, stream); break;
+                case 6: launched = launch_embed_rows<T, 6>(k1_variant(), ids, segment_ids, word, pos, type, gamma, beta, out, tokens, batch, seq, hidden, vocab, type_vocab, status, stream); break;
+                case 8: launched = launch_embed_rows<T, 8>(k1_variant(), ids, segment_ids, word, pos, type, gamma, beta, out, tokens, batch, seq, hidden, vocab, type_vocab, status, stream); break;
+                default: break;
+            }
             if (launched) {
                 return check_launch();
             }

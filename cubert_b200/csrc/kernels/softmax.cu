@@ -10,8 +10,6 @@
 // additive float terms once (in registers for short rows, in shared memory for long ones) and
 // reused for every row of that entry; the reference's score-sized broadcast mask tensor never exists. Arithmetic is
 // float32 issued as packed .f32x2. HBM traffic: one read and one write of the score matrix.
-#include <stdlib.h>
-
 #include "common.cuh"
 
 namespace cubk {
@@ -236,10 +234,9 @@ masked_softmax_generic_kernel(const T *scores, const int8_t *mask, T *out, int64
 // Inside a BERT step, where the GEMMs hold the GPU at its power cap (SM clock 1.3-1.6 GHz), the lower
 // register count wins: BERT-large seq 512 binary16 1621 -> 1496 us per launch, BERT-base seq 128
 // 34.1 -> 32.7 us. Timed alone at 1.9 GHz the register variant is ahead (1353 against 1410 us on the
-// same 8.6 GB). CUBK_SOFTMAX_MASK_SMEM=0 selects the register variant.
+// same 8.6 GB). CUBK_OPT_SOFTMAX_MASK_SMEM = 0 selects the register variant.
 static bool mask_in_smem() {
-    const char *v = getenv("CUBK_SOFTMAX_MASK_SMEM");
-    return v == nullptr || v[0] != '0';
+    return option(CUBK_OPT_SOFTMAX_MASK_SMEM) != 0;
 }
 
 template <typename T>

@@ -22,6 +22,10 @@ STATIC_POOL_SCRATCH_BYTES = 512 * 1024
 STATUS_BAD_TOKEN_ID = 1
 STATUS_BAD_SEGMENT_ID = 2
 STATUS_COPY_TIMEOUT = 4
+OPT_EMBED_STAGED_ROWS = 0
+OPT_SOFTMAX_MASK_SMEM = 1
+OPT_EXACT_WIDTH_ROWS = 2
+OPT_EXACT_WIDTH_EMBED = 3
 
 _P = C.c_void_p
 _I = C.c_int
@@ -33,6 +37,8 @@ _Z = C.c_size_t
 _SIGNATURES = {
     "cubk_version": (_I, []),
     "cubk_last_cuda_error": (C.c_char_p, []),
+    "cubk_set_option": (_I, [_I, _I]),
+    "cubk_get_option": (_I, [_I, _P]),
     "cubk_copy_timeouts": (_I, [_P]),
     "cubk_selftest_copy_wait_timeout": (_I, [C.c_uint, _P, _P]),
     "cubk_embed_ln_{t}": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P]),
@@ -92,6 +98,20 @@ def check(rc):
     if rc != CUBK_OK:
         detail = load().cubk_last_cuda_error().decode() if rc == CUBK_ERR_LAUNCH else ""
         raise KernelError("cubk call failed with status %d %s" % (rc, detail))
+
+
+def set_option(option, value):
+    """Change a process-wide tuning switch (OPT_*); returns the value it had."""
+    old = C.c_int(0)
+    check(load().cubk_get_option(option, C.byref(old)))
+    check(load().cubk_set_option(option, int(value)))
+    return old.value
+
+
+def get_option(option):
+    v = C.c_int(0)
+    check(load().cubk_get_option(option, C.byref(v)))
+    return v.value
 
 
 def copy_timeouts():

@@ -50,9 +50,31 @@ extern "C" {
 int cubk_version(void);
 const char *cubk_last_cuda_error(void);
 
+/* Process-wide tuning switches. Each starts from an environment variable (read once, when the library
+ * first needs any switch) and can be changed at run time; a change applies to launches made after it.
+ * They select between kernels that compute the same result, so they matter to benchmarks and tests only.
+ * No counterpart in the reference.
+ *   CUBK_OPT_EMBED_STAGED_ROWS  (env CUBK_BULK_COPY)          -1 = by shape (default), 0 = never, 1 = whenever it
+ *                               fits: cubk_embed_ln_* fetches the gathered word rows into shared memory with
+ *                               asynchronous bulk copies instead of register loads
+ *   CUBK_OPT_SOFTMAX_MASK_SMEM  (env CUBK_SOFTMAX_MASK_SMEM)  1 (default) = long rows of cubk_masked_softmax_* keep
+ *                               their additive mask terms in shared memory, 0 = in registers
+ *   CUBK_OPT_EXACT_WIDTH_ROWS   (env CUBK_EXACT_WIDTH_ROWS)   1 (default) = cubk_bias_residual_ln_* uses the kernel
+ *                               specialised for rows of exactly 32, 64, 96, 128, 192 or 256 16-byte vectors when
+ *                               the shape allows, 0 = always the general kernel
+ *   CUBK_OPT_EXACT_WIDTH_EMBED  (env CUBK_EXACT_WIDTH_EMBED)  the same for cubk_embed_ln_*
+ * Both return CUBK_ERR_INVALID_ARG for an unknown switch or a value outside its range. */
+#define CUBK_OPT_EMBED_STAGED_ROWS 0
+#define CUBK_OPT_SOFTMAX_MASK_SMEM 1
+#define CUBK_OPT_EXACT_WIDTH_ROWS  2
+#define CUBK_OPT_EXACT_WIDTH_EMBED 3
+#define CUBK_OPT_COUNT             4
+int cubk_set_option(int option, int value);
+int cubk_get_option(int option, int *value);
+
 /* Warps, on the current device and since the library was loaded, that gave up waiting for one of the
- * asynchronous global-to-shared copies the row kernels (cubk_embed_ln_*, cubk_bias_residual_ln_*) stage
- * their inputs with. Every such wait is bounded; a warp that gives up stops writing rows. Expected to
+ * asynchronous global-to-shared copies the staged variant of cubk_embed_ln_* fetches its word rows
+ * with. Every such wait is bounded; a warp that gives up stops writing rows. Expected to
  * stay 0. Synchronises with the device. No counterpart in the reference. */
 int cubk_copy_timeouts(unsigned int *count);
 
@@ -147,7 +169,7 @@ int cubk_bias_tanh_f16(const void *x, const void *bias, int64_t rows, int channe
  * out[b,c] = (sum_s x[b,s,c]) / seq   (every position counts; the mask is ignored)
  * Replaces reduce_mean_1<T> (src/cuBERT/op_bert/BertPooler.h:14-16, op_bert/BertPooler.cu:35-66).
  * When batch is small the sequence axis is split over several thread blocks and the float32
- * partial sums go through `scratch` (device memory, 256-byte aligned, at least
+ * partial sums go through `scratch` (device memory, 16-byte aligned, at least
  * cubk_mean_pool_scratch_bytes(batch, seq, hidden) bytes; may be NULL when that is 0). */
 size_t cubk_mean_pool_scratch_bytes(int batch, int seq, int hidden);
 int cubk_mean_pool_f32(const float *x, int batch, int seq, int hidden, float *out,

@@ -44,6 +44,22 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
+@pytest.fixture
+def kernel_options():
+    """Setter for the kernel library's tuning switches (cubk_set_option); the values a test changes are put
+    back when it ends."""
+    from cubert_b200 import kernels
+    saved = {}
+
+    def set_option(option, value):
+        old = kernels.set_option(option, value)
+        saved.setdefault(option, old)
+
+    yield set_option
+    for option, old in saved.items():
+        kernels.set_option(option, old)
+
+
 @pytest.fixture(scope="session")
 def oracle():
     from oracle import bindings

@@ -113,12 +113,17 @@ def test_kat_classifier(kats):
 # ============================================================================ K2 bias + residual + LayerNorm
 
 LN_SHAPES = [(2, 3), (5, 5), (7, 6), (1, 8), (33, 768), (17, 1024), (9, 3072), (5, 4096), (6, 200), (3, 1000),
-             (4, 8192), (3, 8200), (130, 64), (257, 96)]
+             (4, 8192), (3, 8200), (130, 64), (257, 96), (9001, 768), (4099, 1024), (5003, 256), (1, 1536), (7, 2048)]
 
 
+@pytest.mark.parametrize("exact_width", [1, 0])   # the kernel for rows that fill a warp exactly / the general one
 @pytest.mark.parametrize("t", DTYPES)
 @pytest.mark.parametrize("rows,ch", LN_SHAPES)
-def test_bias_residual_ln(oracle, t, rows, ch):
+def test_bias_residual_ln(oracle, t, rows, ch, exact_width, kernel_options):
+    vectors = ch // (4 if t == "f32" else 8)
+    if exact_width == 0 and not (ch % 8 == 0 and vectors % 32 == 0 and vectors // 32 in (1, 2, 3, 4, 6, 8)):
+        pytest.skip("this width takes the general kernel either way")
+    kernel_options(kernels.OPT_EXACT_WIDTH_ROWS, exact_width)
     rng = np.random.default_rng(rows * 7919 + ch)
     x, xh = _prep(rng.standard_normal((rows, ch)), t)
     r, rh = _prep(rng.standard_normal((rows, ch)), t)
@@ -127,6 +132,7 @@ def test_bias_residual_ln(oracle, t, rows, ch):
     be, beh = _prep(0.1 * rng.standard_normal(ch), t)
     ref = oracle.layer_norm_(rh, xh + bh[None, :], beh, gh)
     _check(G.bias_residual_ln(x, b, r, g, be, t), ref, t, 1.0, "ln")
+    _check(G.bias_residual_ln(x.clone(), b, r, g, be, t, inplace=True), ref, t, 1.0, "ln in place, all operands")
     # in place, and without bias / residual
     ref2 = oracle.layer_norm_(rh, xh, beh, gh)
     _check(G.bias_residual_ln(x.clone(), None, r, g, be, t, inplace=True), ref2, t, 1.0, "ln in place")
@@ -237,13 +243,13 @@ def _mask(rng, batch, seq, kind):
 @pytest.mark.parametrize("t", DTYPES)
 @pytest.mark.parametrize("kind", ["prefix", "random", "empty_row", "none"])
 @pytest.mark.parametrize("batch,heads,seq", SOFTMAX_SHAPES)
-def test_masked_softmax(oracle, t, kind, batch, heads, seq, mask_terms, monkeypatch):
+def test_masked_softmax(oracle, t, kind, batch, heads, seq, mask_terms, kernel_options):
     if mask_terms == "registers":
         if seq // (4 if t == "f32" else 8) <= 8:
             pytest.skip("rows this short keep their mask terms in registers either way")
-        monkeypatch.setenv("CUBK_SOFTMAX_MASK_SMEM", "0")
+        kernel_options(kernels.OPT_SOFTMAX_MASK_SMEM, 0)
     else:
-        monkeypatch.delenv("CUBK_SOFTMAX_MASK_SMEM", raising=False)
+        kernel_options(kernels.OPT_SOFTMAX_MASK_SMEM, 1)
     rng = np.random.default_rng(batch * 1000 + heads * 100 + seq)
     x, xh = _prep(rng.standard_normal((batch, seq, heads, seq)) * 3, t)
     mask = _mask(rng, batch, seq, kind)
@@ -286,13 +292,20 @@ def test_masked_softmax(oracle, t, kind, batch, heads, seq, mask_terms, monkeypa
 
 # ============================================================================ K1 embedding + add + LayerNorm
 
-@pytest.mark.parametrize("staged", ["0", "1"])   # register-resident rows / word rows staged through shared memory
+def _choose_embed_kernel(kernel_options, which):
+    kernel_options(kernels.OPT_EMBED_STAGED_ROWS, 1 if which == "staged" else 0)
+    kernel_options(kernels.OPT_EXACT_WIDTH_EMBED, 0 if which == "general" else 1)
+
+
+# which kernel takes the shapes that fit it: the general register-resident one, the one for rows that fill a warp
+# exactly, or the one with word rows staged through shared memory
+@pytest.mark.parametrize("staged", ["general", "exact", "staged"])
 @pytest.mark.parametrize("t", DTYPES)
 @pytest.mark.parametrize("batch,seq,hidden,vocab", [(2, 4, 3, 5), (3, 7, 10, 11), (4, 32, 768, 2000), (2, 128, 1024, 3000),
                                                     (1, 16, 200, 50), (2, 5, 4096, 30), (5, 9, 32, 7), (300, 64, 256, 999),
                                                     (7, 33, 1536, 100)])
-def test_embed_ln(oracle, t, batch, seq, hidden, vocab, staged, monkeypatch):
-    monkeypatch.setenv("CUBK_BULK_COPY", staged)
+def test_embed_ln(oracle, t, batch, seq, hidden, vocab, staged, kernel_options):
+    _choose_embed_kernel(kernel_options, staged)
     gave_up_before = kernels.copy_timeouts()
     rng = np.random.default_rng(hidden + vocab)
     word, wh = _prep(rng.standard_normal((vocab, hidden)) * 0.02, t)
@@ -311,10 +324,11 @@ def test_embed_ln(oracle, t, batch, seq, hidden, vocab, staged, monkeypatch):
 
 
 @pytest.mark.parametrize("t", DTYPES)
-def test_embed_ln_sweep_shape_with_the_default_kernel_choice(oracle, t, monkeypatch):
+def test_embed_ln_sweep_shape_with_the_default_kernel_choice(oracle, t, kernel_options):
     """256 x 128 tokens, hidden 768, vocabulary 21128: float32 takes the staged kernel by default,
     binary16 the register-resident one; every token of the even split over warps is checked."""
-    monkeypatch.delenv("CUBK_BULK_COPY", raising=False)
+    kernel_options(kernels.OPT_EMBED_STAGED_ROWS, -1)
+    kernel_options(kernels.OPT_EXACT_WIDTH_EMBED, 1)
     gave_up_before = kernels.copy_timeouts()
     batch, seq, hidden, vocab = 256, 128, 768, 21128
     rng = np.random.default_rng(1)
@@ -349,9 +363,9 @@ def test_a_copy_wait_that_runs_out_is_reported_and_leaves_the_context_usable():
     assert torch.isfinite(y).all() and torch.cuda.current_stream().query() is not None
 
 
-@pytest.mark.parametrize("staged", ["0", "1"])
-def test_embed_out_of_range_ids_are_clamped_and_flagged(oracle, staged, monkeypatch):
-    monkeypatch.setenv("CUBK_BULK_COPY", staged)
+@pytest.mark.parametrize("staged", ["general", "exact", "staged"])
+def test_embed_out_of_range_ids_are_clamped_and_flagged(oracle, staged, kernel_options):
+    _choose_embed_kernel(kernel_options, staged)
     rng = np.random.default_rng(0)
     vocab, hidden, seq = 10, 768, 4
     word = rng.standard_normal((vocab, hidden)).astype(np.float32)
@@ -538,10 +552,10 @@ def test_softmax_and_pool_stay_inside_their_buffers(t, batch, heads, seq):
 
 
 @pytest.mark.parametrize("t", DTYPES)
-@pytest.mark.parametrize("staged", ["0", "1"])
+@pytest.mark.parametrize("staged", ["general", "exact", "staged"])
 @pytest.mark.parametrize("batch,seq,hidden,vocab", [(1, 1, 8, 3), (3, 5, 768, 50), (2, 7, 1024, 9), (9, 3, 40, 4), (4, 4, 4096, 6)])
-def test_embedding_kernels_stay_inside_their_buffers(t, staged, batch, seq, hidden, vocab, monkeypatch):
-    monkeypatch.setenv("CUBK_BULK_COPY", staged)
+def test_embedding_kernels_stay_inside_their_buffers(t, staged, batch, seq, hidden, vocab, kernel_options):
+    _choose_embed_kernel(kernel_options, staged)
     dt = G.TORCH_DTYPE[t]
     g = torch.Generator(device="cuda").manual_seed(hidden + vocab)
     rnd = lambda *shape: torch.randn(*shape, device="cuda", generator=g) * 0.1  # noqa: E731

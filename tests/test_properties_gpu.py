@@ -123,10 +123,11 @@ def test_gather_then_scatter_is_the_identity(dtype, rows, width, n, seed):
 
 @settings(**SETTINGS)
 @given(t=DT, batch=st.integers(1, 6), seq=st.integers(1, 20), hidden=st.sampled_from([8, 64, 200, 768, 1000, 4096]),
-       vocab=st.integers(1, 50), seed=st.integers(0, 2 ** 31 - 1), staged=st.sampled_from(["0", "1"]))
+       vocab=st.integers(1, 50), seed=st.integers(0, 2 ** 31 - 1),
+       staged=st.sampled_from(["general", "exact", "staged"]))
 def test_embed_ln(oracle, t, batch, seq, hidden, vocab, seed, staged):
-    import os
-    os.environ["CUBK_BULK_COPY"] = staged
+    saved = (kernels.set_option(kernels.OPT_EMBED_STAGED_ROWS, 1 if staged == "staged" else 0),
+             kernels.set_option(kernels.OPT_EXACT_WIDTH_EMBED, 0 if staged == "general" else 1))
     try:
         rng = np.random.default_rng(seed)
         word, wh = _prep(rng.standard_normal((vocab, hidden)) * 0.05, t)
@@ -141,4 +142,5 @@ def test_embed_ln(oracle, t, batch, seq, hidden, vocab, seed, staged):
         _close(got, oracle.bert_embeddings(ids, seg, wh, ph, th, beh, gh), t)
         assert int(status.item()) == 0
     finally:
-        os.environ.pop("CUBK_BULK_COPY", None)
+        kernels.set_option(kernels.OPT_EMBED_STAGED_ROWS, saved[0])
+        kernels.set_option(kernels.OPT_EXACT_WIDTH_EMBED, saved[1])

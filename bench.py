@@ -329,14 +329,14 @@ def run_ours(args):
 
     # ---- device-resident: `value` (the forward pass replayed as one CUDA graph, the library's default)
     for _ in range(args.warmup):
-        m.forward_device(0, B, d_ids.data_ptr(), d_mask.data_ptr(), d_seg.data_ptr())
+        m.forward_device(0, B, d_ids.data_ptr(), d_mask.data_ptr(), d_seg.data_ptr(), host_mask=np_mask)
     m.synchronize(0)
     m.profile_read(0)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     start.record(stream)
     for _ in range(args.steps):
-        m.forward_device(0, B, d_ids.data_ptr(), d_mask.data_ptr(), d_seg.data_ptr())
+        m.forward_device(0, B, d_ids.data_ptr(), d_mask.data_ptr(), d_seg.data_ptr(), host_mask=np_mask)
     stop.record(stream)
     m.synchronize(0)
     barrier()
@@ -351,7 +351,7 @@ def run_ours(args):
     barrier()
     p_start.record(stream)
     for _ in range(args.steps):
-        m.forward_device(0, B, d_ids.data_ptr(), d_mask.data_ptr(), d_seg.data_ptr())
+        m.forward_device(0, B, d_ids.data_ptr(), d_mask.data_ptr(), d_seg.data_ptr(), host_mask=np_mask)
     p_stop.record(stream)
     m.synchronize(0)
     barrier()

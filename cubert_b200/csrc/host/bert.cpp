@@ -2,6 +2,7 @@
 
 #include <nvtx3/nvToolsExt.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 #include <iostream>
@@ -22,6 +23,7 @@ struct K<float> {
     static constexpr auto bias_residual_ln = cubk_bias_residual_ln_f32;
     static constexpr auto bias_gelu = cubk_bias_gelu_f32;
     static constexpr auto masked_softmax = cubk_masked_softmax_f32;
+    static constexpr auto masked_softmax_extents = cubk_masked_softmax_extents_f32;
     static constexpr auto bias_tanh = cubk_bias_tanh_f32;
     static constexpr auto mean_pool = cubk_mean_pool_f32;
     static constexpr auto logits_probs = cubk_logits_probs_f32;
@@ -33,6 +35,7 @@ struct K<__half> {
     static constexpr auto bias_residual_ln = cubk_bias_residual_ln_f16;
     static constexpr auto bias_gelu = cubk_bias_gelu_f16;
     static constexpr auto masked_softmax = cubk_masked_softmax_f16;
+    static constexpr auto masked_softmax_extents = cubk_masked_softmax_extents_f16;
     static constexpr auto bias_tanh = cubk_bias_tanh_f16;
     static constexpr auto mean_pool = cubk_mean_pool_f16;
     static constexpr auto logits_probs = cubk_logits_probs_f16;
@@ -96,6 +99,7 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
     tail_layers_ = tail_layers_ < 0 ? 0 : tail_layers_;
     CUDA_CHECK(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
     CUDA_CHECK(cudaEventCreateWithFlags(&embed_ready_, cudaEventDisableTiming));
+    CUDA_CHECK(cudaEventCreateWithFlags(&staging_read_, cudaEventDisableTiming));
     for (cudaEvent_t &ev : chunk_ready_) {
         CUDA_CHECK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
     }
@@ -242,6 +246,18 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
             cp[b * heads + h] = context_.template as<T>() + b * S * H + h * d;
         }
     }
+    skip_masked_keys_ = env_int("CUBERT_SKIP_MASKED_KEYS", 1) != 0 && S >= 64;
+    if (skip_masked_keys_) {
+        // extents in steps of 32 keys, or of an eighth of the sequence when that is more (at most 8 groups)
+        key_granule_ = (int) ((S / 8 + 31) / 32 * 32);
+        key_granule_ = key_granule_ < 32 ? 32 : key_granule_;
+        seq_extent_.assign(B, (int32_t) S);
+        CUDA_CHECK(cudaMallocHost(reinterpret_cast<void **>(&h_plan_), sizeof(int32_t) * 2 * B));
+        plan_dev_.allocate(sizeof(int32_t) * 2 * B);
+        for (DeviceBuffer *sorted : {&q_sorted_, &k_sorted_, &v_sorted_, &score_sorted_, &ctx_sorted_}) {
+            sorted->allocate(sizeof(void *) * B * heads);
+        }
+    }
     upload(q_ptrs_, qp.data(), qp.size());
     upload(k_ptrs_, kp.data(), kp.size());
     upload(v_ptrs_, vp.data(), vp.size());
@@ -298,6 +314,12 @@ Bert<T>::~Bert() {
         if (ev != nullptr) {
             cudaEventDestroy(ev);
         }
+    }
+    if (staging_read_ != nullptr) {
+        cudaEventDestroy(staging_read_);
+    }
+    if (h_plan_ != nullptr) {
+        cudaFreeHost(h_plan_);
     }
     if (h_token_index_ != nullptr) {
         cudaFreeHost(h_token_index_);
@@ -392,6 +414,7 @@ size_t Bert<T>::build_token_index(size_t batch_size, const int8_t *input_mask) {
     if (R < kMinPositionsForPacking) {
         return 0;
     }
+    wait_for_staging();
     int32_t *list = h_token_index_;
     int32_t *first = h_token_index_ + max_batch_size * S;
     size_t n = 0;
@@ -399,13 +422,25 @@ size_t Bert<T>::build_token_index(size_t batch_size, const int8_t *input_mask) {
         first[b] = (int32_t) n;  // position 0 is always kept: the pooler reads it
         list[n++] = (int32_t) (b * S);
         const int8_t *m = input_mask + b * S;
+        bool any = m[0] != 0;
         for (size_t s = 1; s < S; ++s) {
             if (m[s] != 0) {
                 list[n++] = (int32_t) (b * S + s);
+                any = true;
             }
         }
+        if (!any) {
+            // No key of this sequence is kept: the reference then attends to ALL its positions uniformly
+            // (every score gets the same -10000), so none of them may be dropped. Rare (the empty rows that
+            // fill a fixed batch): the whole request takes the unpacked pass.
+            return 0;
+        }
     }
-    size_t padded = (n + 63) / 64 * 64;
+    // Rounded up to a sixteenth of the request (at least 64): the tail repeats the last token, which costs
+    // up to 6 % more rows and keeps the number of distinct packed lengths, hence of captured graphs, small.
+    size_t step = (R / 16 + 63) / 64 * 64;
+    step = step < 64 ? 64 : step;
+    size_t padded = (n + step - 1) / step * step;
     if (padded > R) {
         padded = R;
     }
@@ -418,18 +453,122 @@ size_t Bert<T>::build_token_index(size_t batch_size, const int8_t *input_mask) {
     return padded;
 }
 
+// Before the host rewrites a pinned staging buffer: the copy that last read it has finished.
+template <typename T>
+void Bert<T>::wait_for_staging() {
+    if (staging_in_flight_) {
+        CUDA_CHECK(cudaEventSynchronize(staging_read_));
+        staging_in_flight_ = false;
+    }
+}
+
+// ------------------------------------------------------------------ attention over kept keys only
+constexpr size_t kMinPositionsForKeyPlan = 2048;
+
+template <typename T>
+void Bert<T>::build_key_plan(size_t batch_size, const int8_t *input_mask) {
+    plan_ = KeyPlan();
+    const size_t S = seq_length;
+    if (!skip_masked_keys_ || input_mask == nullptr || batch_size * S < kMinPositionsForKeyPlan) {
+        return;
+    }
+    const int granule = key_granule_;
+    int count[kMaxKeyGroups + 2] = {};
+    const int buckets = (int) ((S + granule - 1) / granule);   // extent = bucket * granule, capped at S
+    if (buckets > kMaxKeyGroups) {
+        return;
+    }
+    int64_t columns = 0;
+    uint64_t hash = 1469598103934665603ull;
+    for (size_t b = 0; b < batch_size; ++b) {
+        const int8_t *m = input_mask + b * S;
+        int last = (int) S - 1;
+        while (last >= 0 && m[last] == 0) {
+            --last;
+        }
+        int extent = last < 0 ? (int) S : (last / granule + 1) * granule;
+        extent = extent > (int) S ? (int) S : extent;
+        seq_extent_[b] = extent;
+        count[(extent + granule - 1) / granule] += 1;
+        columns += extent;
+        hash = (hash ^ (uint64_t) extent) * 1099511628211ull;
+    }
+    if (columns * 10 > (int64_t) batch_size * (int64_t) S * 9) {
+        return;  // under a tenth of the key columns is padding: the extra launches would cost more
+    }
+    wait_for_staging();
+    // counting sort: groups in order of growing extent
+    int first[kMaxKeyGroups + 2] = {};
+    int groups = 0, at = 0;
+    for (int k = 1; k <= buckets; ++k) {
+        first[k] = at;
+        if (count[k] > 0) {
+            plan_.start[groups] = at;
+            plan_.extent[groups] = k * granule > (int) S ? (int) S : k * granule;
+            ++groups;
+        }
+        at += count[k];
+    }
+    plan_.start[groups] = at;
+    int32_t *order = h_plan_;
+    int32_t *extents = h_plan_ + max_batch_size;
+    for (size_t b = 0; b < batch_size; ++b) {
+        const int k = (seq_extent_[b] + granule - 1) / granule;
+        order[first[k]++] = (int32_t) b;
+        extents[b] = seq_extent_[b];
+    }
+    plan_.groups = groups;
+    plan_.key_columns = columns;
+    plan_.signature = hash == 0 ? 1 : hash;
+    plan_.active = true;
+    CUDA_CHECK(cudaMemcpyAsync(plan_dev_.get(), h_plan_, sizeof(int32_t) * batch_size, cudaMemcpyHostToDevice, stream_));
+    CUDA_CHECK(cudaMemcpyAsync(plan_dev_.template as<int32_t>() + max_batch_size, extents, sizeof(int32_t) * batch_size,
+                               cudaMemcpyHostToDevice, stream_));
+    CUDA_CHECK(cudaEventRecord(staging_read_, stream_));
+    staging_in_flight_ = true;
+}
+
+// The five pointer arrays of the batched attention products, rows permuted into the plan's sorted order
+// (a row = the `heads` pointers of one sequence, gathered as 2 * heads 32-bit words).
+template <typename T>
+void Bert<T>::sort_attention_pointers(size_t batch_size) {
+    if (!plan_.active) {
+        return;
+    }
+    const int heads = (int) num_attention_heads;
+    const int32_t *order = plan_dev_.template as<int32_t>();
+    const DeviceBuffer *from[5] = {&q_ptrs_, &k_ptrs_, &v_ptrs_, &score_ptrs_, &ctx_ptrs_};
+    DeviceBuffer *to[5] = {&q_sorted_, &k_sorted_, &v_sorted_, &score_sorted_, &ctx_sorted_};
+    for (int i = 0; i < 5; ++i) {
+        KERNEL_CHECK(cubk_embed_gather_i32(order, (int64_t) batch_size, from[i]->get(), (int) max_batch_size, 2 * heads, 4,
+                                           to[i]->get(), nullptr, stream_));
+    }
+}
+
+template <typename T>
+int Bert<T>::range_extent(size_t b0, size_t nb) const {
+    int e = 0;
+    for (size_t b = b0; b < b0 + nb; ++b) {
+        e = seq_extent_[b] > e ? seq_extent_[b] : e;
+    }
+    return e;
+}
+
 // Host inputs to the device. When the model's whole input span is small (serving-size models), the three
 // arrays are gathered in a pinned staging buffer laid out like the device buffer and go over in ONE copy;
 // three copies from pageable caller memory each pay the driver's own staging. Otherwise three copies.
 template <typename T>
 void Bert<T>::upload_inputs(size_t tokens, const int *input_ids, const int8_t *input_mask, const int8_t *segment_ids) {
     if (h_inputs_ != nullptr) {
+        wait_for_staging();
         const size_t mask_at = (size_t) (mask_ - inputs_.template as<int8_t>());
         const size_t seg_at = (size_t) (segments_ - inputs_.template as<int8_t>());
         std::memcpy(h_inputs_, input_ids, sizeof(int32_t) * tokens);
         std::memcpy(h_inputs_ + mask_at, input_mask, tokens);
         std::memcpy(h_inputs_ + seg_at, segment_ids, tokens);
         CUDA_CHECK(cudaMemcpyAsync(inputs_.get(), h_inputs_, seg_at + tokens, cudaMemcpyHostToDevice, stream_));
+        CUDA_CHECK(cudaEventRecord(staging_read_, stream_));
+        staging_in_flight_ = true;
         return;
     }
     CUDA_CHECK(cudaMemcpyAsync(ids_, input_ids, sizeof(int32_t) * tokens, cudaMemcpyHostToDevice, stream_));
@@ -459,8 +598,11 @@ void Bert<T>::compute(size_t batch_size, const int *input_ids, const int8_t *inp
                                        cudaMemcpyHostToDevice, stream_));
             CUDA_CHECK(cudaMemcpyAsync(first_index_.get(), h_token_index_ + max_batch_size * seq_length,
                                        sizeof(int32_t) * batch_size, cudaMemcpyHostToDevice, stream_));
+            CUDA_CHECK(cudaEventRecord(staging_read_, stream_));
+            staging_in_flight_ = true;
         }
     }
+    build_key_plan(batch_size, input_mask);
     // the last layer for first tokens only: when nothing per-position is wanted and the request is large
     // enough for the saved rows to outweigh one extra gather launch
     const bool heads_only = !all_positions && prune_last_layer_ && (packed > 0 || n >= kMinPositionsForPacking);
@@ -469,7 +611,7 @@ void Bert<T>::compute(size_t batch_size, const int *input_ids, const int8_t *inp
 
 template <typename T>
 void Bert<T>::compute_device(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask,
-                             const int8_t *d_segments) {
+                             const int8_t *d_segments, const int8_t *host_mask) {
     if (batch_size > max_batch_size) {
         throw std::invalid_argument("batch_size > max_batch_size");
     } else if (batch_size == 0) {
@@ -479,6 +621,7 @@ void Bert<T>::compute_device(size_t batch_size, const int32_t *d_ids, const int8
         throw std::invalid_argument("null input");
     }
     CUDA_CHECK(cudaSetDevice(device_));
+    build_key_plan(batch_size, host_mask);
     run(batch_size, d_ids, d_mask, d_segments, 0);
 }
 
@@ -487,7 +630,8 @@ constexpr size_t kMaxCachedGraphs = 256;
 template <typename T>
 void Bert<T>::run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments,
                   size_t packed, bool heads_only) {
-    const GraphKey key{batch_size, packed, d_ids, d_mask, d_segments, heads_only ? kWholePassHeadsOnly : kWholePass, 0, 0};
+    const GraphKey key{batch_size, packed, d_ids, d_mask, d_segments, heads_only ? kWholePassHeadsOnly : kWholePass, 0, 0,
+                       plan_.signature};
     run_graph(key, [&] { forward(batch_size, d_ids, d_mask, d_segments, packed, heads_only); });
 }
 
@@ -501,13 +645,32 @@ void Bert<T>::run_graph(const GraphKey &key, const std::function<void()> &body) 
         return;
     }
     auto it = graphs_.find(key);
+    if (it != graphs_.end() && key.keys != 0 &&
+        (it->second.extents.size() != key.batch ||
+         !std::equal(it->second.extents.begin(), it->second.extents.end(), seq_extent_.begin()))) {
+        body();  // another set of key extents with the same hash: never replay a graph of other shapes
+        return;
+    }
     if (it == graphs_.end()) {
         if (graphs_.size() >= kMaxCachedGraphs) {
-            body();
-            return;
+            // make room: the least recently used graph goes
+            auto oldest = graphs_.begin();
+            for (auto e = graphs_.begin(); e != graphs_.end(); ++e) {
+                if (e->second.last_use < oldest->second.last_use) {
+                    oldest = e;
+                }
+            }
+            if (oldest->second.exec != nullptr) {
+                cudaGraphExecDestroy(oldest->second.exec);
+            }
+            graphs_.erase(oldest);
         }
         it = graphs_.emplace(key, GraphEntry()).first;
+        if (key.keys != 0) {
+            it->second.extents.assign(seq_extent_.begin(), seq_extent_.begin() + (long) key.batch);
+        }
     }
+    it->second.last_use = ++graph_clock_;
     GraphEntry &g = it->second;
     if (g.exec != nullptr) {
         for (int k = 0; k < CUBERT_B200_K_COUNT; ++k) {
@@ -556,6 +719,12 @@ template <typename T>
 void Bert<T>::forward(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments,
                       size_t packed, bool heads_only) {
     forward_embed(batch_size, d_ids, d_segments, packed);
+    sort_attention_pointers(batch_size);
+    if (packed > 0) {
+        // Rows of the [batch, seq] Q/K/V buffer that this pass never writes (dropped padding) are multiplied
+        // by probabilities that are exactly 0: they must hold finite numbers, whatever earlier requests left.
+        CUDA_CHECK(cudaMemsetAsync(qkv_.get(), 0, sizeof(T) * batch_size * seq_length * 3 * hidden_size, stream_));
+    }
     if (heads_only && prune_last_layer_) {
         forward_layers(0, num_hidden_layers - 1, 0, batch_size, batch_size, d_mask, packed);
         forward_last_layer_first_tokens(batch_size, d_mask, packed);
@@ -594,7 +763,6 @@ void Bert<T>::forward_embed(size_t batch_size, const int32_t *d_ids, const int8_
 template <typename T>
 void Bert<T>::forward_layers(size_t l_begin, size_t l_end, size_t b0, size_t nb, size_t batch_size,
                              const int8_t *d_mask, size_t packed) {
-    (void) batch_size;
     const int B = (int) nb, S = (int) seq_length, H = (int) hidden_size, I = (int) intermediate_size;
     const int heads = (int) num_attention_heads, d = H / heads;
     const int64_t R = (int64_t) B * S;      // rows of the [batch, seq] layout in this range
@@ -614,6 +782,18 @@ void Bert<T>::forward_layers(size_t l_begin, size_t l_end, size_t b0, size_t nb,
     T *inter = inter_.template as<T>() + row0 * I;
     const size_t p0 = b0 * (size_t) heads;  // first entry of the range in the pointer arrays
 
+    // key columns the attention works on (see KeyPlan)
+    const bool grouped = plan_.active && b0 == 0 && nb == batch_size;
+    const int keys = plan_.active && !grouped ? range_extent(b0, nb) : S;
+    const int32_t *extents = plan_.active ? plan_dev_.template as<int32_t>() + max_batch_size + b0 : nullptr;
+    int64_t key_columns = R;   // sum over the range's sequences of the key columns K4 moves
+    if (plan_.active) {
+        key_columns = 0;
+        for (size_t b = b0; b < b0 + nb; ++b) {
+            key_columns += seq_extent_[b];
+        }
+    }
+
     for (size_t l = l_begin; l < l_end; ++l) {
         Layer &L = layers_[l];
         const T *x = l == 0 ? (packed > 0 ? hidden_[1].template as<T>() : embedding_.template as<T>() + row0 * H)
@@ -632,22 +812,49 @@ void Bert<T>::forward_layers(size_t l_begin, size_t l_end, size_t b0, size_t nb,
         }
 
         // scores[b, i, h, j] = (1/sqrt(d)) * sum_c K[b,j,h,c] * Q[b,i,h,c]   (op_att/BatchMatMul.cpp:57-68)
+        // With a key plan only the key columns j below each sequence's extent exist: one product per group
+        // of equal extent over the sorted pointer arrays, or (a range of sequences) the range's largest extent.
         begin(CUBERT_B200_K_GEMM);
-        blas_->gemm_batched<T>(true, false, S, S, d, att_scale, k_ptrs_.template as<const T *>() + p0, 3 * H,
-                               q_ptrs_.template as<const T *>() + p0, 3 * H, 0.f, score_ptrs_.template as<T *>() + p0, S * heads,
-                               B * heads, algo_qk_);
+        if (grouped) {
+            for (int g = 0; g < plan_.groups; ++g) {
+                const size_t at = (size_t) plan_.start[g] * heads;
+                const int count = (plan_.start[g + 1] - plan_.start[g]) * heads;
+                blas_->gemm_batched<T>(true, false, plan_.extent[g], S, d, att_scale, k_sorted_.template as<const T *>() + at,
+                                       3 * H, q_sorted_.template as<const T *>() + at, 3 * H, 0.f,
+                                       score_sorted_.template as<T *>() + at, S * heads, count, algo_qk_);
+            }
+        } else {
+            blas_->gemm_batched<T>(true, false, keys, S, d, att_scale, k_ptrs_.template as<const T *>() + p0, 3 * H,
+                                   q_ptrs_.template as<const T *>() + p0, 3 * H, 0.f, score_ptrs_.template as<T *>() + p0,
+                                   S * heads, B * heads, algo_qk_);
+        }
         end(CUBERT_B200_K_GEMM, 0);
 
         // K4: mask + softmax in place over rows [B*S*heads, S]
         begin(CUBERT_B200_K_MASKED_SOFTMAX);
-        KERNEL_CHECK(K<T>::masked_softmax(scores, mask, R * heads, (int64_t) S * heads, S, 1.0f, scores, st));
-        end(CUBERT_B200_K_MASKED_SOFTMAX, 2 * R * heads * S * e + R);
+        if (plan_.active) {
+            KERNEL_CHECK(K<T>::masked_softmax_extents(scores, mask, extents, grouped ? 0 : keys, R * heads, (int64_t) S * heads,
+                                                      S, 1.0f, scores, st));
+        } else {
+            KERNEL_CHECK(K<T>::masked_softmax(scores, mask, R * heads, (int64_t) S * heads, S, 1.0f, scores, st));
+        }
+        end(CUBERT_B200_K_MASKED_SOFTMAX, 2 * key_columns * S * heads * e + R);
 
         // context[b, i, h, c] = sum_j V[b,j,h,c] * P[b,i,h,j]   (op_att/BatchMatMul.cpp:124-135)
         begin(CUBERT_B200_K_GEMM);
-        blas_->gemm_batched<T>(false, false, d, S, S, 1.f, v_ptrs_.template as<const T *>() + p0, 3 * H,
-                               score_ptrs_.template as<const T *>() + p0, S * heads, 0.f, ctx_ptrs_.template as<T *>() + p0, H,
-                               B * heads, algo_qkv_);
+        if (grouped) {
+            for (int g = 0; g < plan_.groups; ++g) {
+                const size_t at = (size_t) plan_.start[g] * heads;
+                const int count = (plan_.start[g + 1] - plan_.start[g]) * heads;
+                blas_->gemm_batched<T>(false, false, d, S, plan_.extent[g], 1.f, v_sorted_.template as<const T *>() + at, 3 * H,
+                                       score_sorted_.template as<const T *>() + at, S * heads, 0.f,
+                                       ctx_sorted_.template as<T *>() + at, H, count, algo_qkv_);
+            }
+        } else {
+            blas_->gemm_batched<T>(false, false, d, S, keys, 1.f, v_ptrs_.template as<const T *>() + p0, 3 * H,
+                                   score_ptrs_.template as<const T *>() + p0, S * heads, 0.f, ctx_ptrs_.template as<T *>() + p0,
+                                   H, B * heads, algo_qkv_);
+        }
         end(CUBERT_B200_K_GEMM, 0);
 
         // attention output projection, then K2: LayerNorm(dense + bias + layer input)
@@ -887,12 +1094,14 @@ void Bert<T>::compute_output(size_t batch_size, const int *input_ids, const int8
     }
 
     upload_inputs(tokens, input_ids, input_mask, segment_ids);
+    build_key_plan(batch_size, input_mask);
     const int32_t *d_ids = ids_;
     const int8_t *d_mask = mask_;
     const int8_t *d_seg = segments_;
 
     // ---- everything that computes goes to the compute stream first ...
     forward_embed(batch_size, d_ids, d_seg, 0);
+    sort_attention_pointers(batch_size);
     const void *embedding_src = embedding_.get();
     if (out->embedding_output != nullptr) {
         if (convert) {
@@ -909,7 +1118,7 @@ void Bert<T>::compute_output(size_t batch_size, const int *input_ids, const int8
     const size_t tail = chunks > 1 ? ((size_t) tail_layers_ < L ? (size_t) tail_layers_ : L) : 0;
     const size_t per_chunk = (batch_size + chunks - 1) / chunks;
     if (L - tail > 0) {
-        const GraphKey key{batch_size, 0, d_ids, d_mask, d_seg, kHeadLayers, 0, L - tail};
+        const GraphKey key{batch_size, 0, d_ids, d_mask, d_seg, kHeadLayers, 0, L - tail, plan_.signature};
         run_graph(key, [&] { forward_layers(0, L - tail, 0, batch_size, batch_size, d_mask, 0); });
     }
     size_t used = 0;
@@ -920,7 +1129,7 @@ void Bert<T>::compute_output(size_t batch_size, const int *input_ids, const int8
         }
         const size_t nb = batch_size - b0 < per_chunk ? batch_size - b0 : per_chunk;
         if (tail > 0) {
-            const GraphKey key{batch_size, 0, d_ids, d_mask, d_seg, kTailLayers, b0, nb};
+            const GraphKey key{batch_size, 0, d_ids, d_mask, d_seg, kTailLayers, b0, nb, plan_.signature};
             run_graph(key, [&] { forward_layers(L - tail, L, b0, nb, batch_size, d_mask, 0); });
         }
         if (out->sequence_output != nullptr) {
@@ -934,7 +1143,7 @@ void Bert<T>::compute_output(size_t batch_size, const int *input_ids, const int8
         used = c + 1;
     }
     {
-        const GraphKey key{batch_size, 0, d_ids, d_mask, d_seg, kHeads, 0, 0};
+        const GraphKey key{batch_size, 0, d_ids, d_mask, d_seg, kHeads, 0, 0, 0};
         run_graph(key, [&] { forward_heads(batch_size, d_mask, 0); });
     }
     auto small = [&](void *dst, const T *src, size_t count) {

@@ -48,8 +48,10 @@ public:
     void compute(size_t batch_size, const int *input_ids, const int8_t *input_mask, const int8_t *segment_ids,
                  bool all_positions = true);
 
-    // Forward pass on inputs already in this replica's device memory.
-    void compute_device(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments);
+    // Forward pass on inputs already in this replica's device memory. `host_mask`, when the caller has a
+    // host copy of d_mask, lets the replica leave masked key columns out of the attention (see KeyPlan).
+    void compute_device(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments,
+                        const int8_t *host_mask = nullptr);
 
     // Copy the non-NULL outputs to the host and wait for them (src/cuBERT/Bert.cpp:185-208).
     // With to_float, a binary16 model converts on the device first (Bert.cpp:218-259 does it on the host).
@@ -118,18 +120,22 @@ private:
         const void *ids, *mask, *segments;
         int phase;        // which part of the pass the graph holds
         size_t b0, nb;    // kTailLayers: the sequences it covers
+        uint64_t keys;    // KeyPlan::signature (0 = every key column), which fixes the attention products' shapes
         bool operator<(const GraphKey &o) const {
-            return std::tie(batch, packed, ids, mask, segments, phase, b0, nb) <
-                   std::tie(o.batch, o.packed, o.ids, o.mask, o.segments, o.phase, o.b0, o.nb);
+            return std::tie(batch, packed, ids, mask, segments, phase, b0, nb, keys) <
+                   std::tie(o.batch, o.packed, o.ids, o.mask, o.segments, o.phase, o.b0, o.nb, o.keys);
         }
     };
     struct GraphEntry {
         cudaGraphExec_t exec = nullptr;
         int seen = 0;  // calls with this key so far; the first runs eagerly, the second captures
+        uint64_t last_use = 0;  // for eviction of the least recently used graph when the cache is full
+        std::vector<int32_t> extents;  // the key extents the graph was captured with (guards against a hash collision)
         std::array<int64_t, CUBERT_B200_K_COUNT> launches{};  // launches per family inside the graph
     };
     void run_graph(const GraphKey &key, const std::function<void()> &body);
     std::map<GraphKey, GraphEntry> graphs_;
+    uint64_t graph_clock_ = 0;
     bool use_graphs_ = true;
 
     // profiling: brackets one launch with events when enabled, always counts
@@ -170,6 +176,38 @@ private:
     DeviceBuffer first_index_full_, score1_ptrs_, ctx1_ptrs_;
     size_t build_token_index(size_t batch_size, const int8_t *input_mask);
     T *sequence_output_ = nullptr;
+
+    // Attention over kept keys only. When the host sees the mask, every sequence gets a key extent: the
+    // position after its last kept key, rounded up to a multiple of key_granule_ (the whole sequence when no
+    // key is kept, the reference's uniform attention). Key columns from the extent on are masked, so their
+    // probabilities are exactly 0: the Q.K^T product need not compute them, K4 need not read or write them
+    // and the P.V product need not multiply them. Sequences are grouped by extent (a counting sort); each
+    // group runs the two batched products with its own extent over pointer arrays in sorted order, and K4
+    // reads the per-sequence extents. A range of sequences (the sub-batches of compute_output) uses the
+    // largest extent of the range. Off with CUBERT_SKIP_MASKED_KEYS=0, for requests under 2048 positions,
+    // and when less than a tenth of the key columns would be dropped.
+    static constexpr int kMaxKeyGroups = 16;
+    struct KeyPlan {
+        bool active = false;
+        int groups = 0;
+        int start[kMaxKeyGroups + 1] = {};   // first sorted sequence of each group, and the end
+        int extent[kMaxKeyGroups] = {};      // key columns of each group
+        uint64_t signature = 0;              // hash of the per-sequence extents (never 0 when active)
+        int64_t key_columns = 0;             // sum of the extents
+    };
+    KeyPlan plan_;
+    bool skip_masked_keys_ = true;
+    int key_granule_ = 32;
+    std::vector<int32_t> seq_extent_;        // per sequence, batch order (host)
+    int32_t *h_plan_ = nullptr;              // pinned: sorted order [max_batch], extents [max_batch]
+    DeviceBuffer plan_dev_;                  // the same on the device
+    DeviceBuffer q_sorted_, k_sorted_, v_sorted_, score_sorted_, ctx_sorted_;  // pointer arrays in sorted order
+    void build_key_plan(size_t batch_size, const int8_t *input_mask);
+    void sort_attention_pointers(size_t batch_size);   // device side of the plan; part of the forward pass
+    int range_extent(size_t b0, size_t nb) const;
+    cudaEvent_t staging_read_ = nullptr;     // after the last copy out of the pinned staging buffers
+    bool staging_in_flight_ = false;
+    void wait_for_staging();
 
     // overlapped output copies
     static constexpr size_t kMaxTailChunks = 8;

@@ -36,6 +36,9 @@ BertM<T>::BertM(const char *model_file, size_t max_batch_size_, size_t seq_lengt
         per_gpu = 1;
     }
 
+    // every array a replica uploads has the size its geometry says, before anything reads it
+    weights_.validate(seq_length, num_hidden_layers, num_attention_heads);
+
     std::unordered_map<std::string, const T *> var;
     for (auto &kv : weights_.var) {
         var[kv.first] = kv.second.data();

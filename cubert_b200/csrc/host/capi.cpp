@@ -413,6 +413,20 @@ int cubert_b200_forward_device(void *model, int compute_type, int replica, int b
     });
 }
 
+int cubert_b200_forward_device_masked(void *model, int compute_type, int replica, int batch_size,
+                                      const int32_t *input_ids, const int8_t *input_mask, const int8_t *segment_ids,
+                                      const int8_t *host_input_mask) {
+    return guarded([&] {
+        if (batch_size < 0) {
+            throw std::invalid_argument("negative batch_size");
+        }
+        with_model(model, compute_type, [&](auto *m) {
+            m->replica((size_t) replica)->compute_device((size_t) batch_size, input_ids, input_mask, segment_ids,
+                                                         host_input_mask);
+        });
+    });
+}
+
 int cubert_b200_device_outputs(void *model, int compute_type, int replica, cuBERT_Output *outputs) {
     return guarded([&] {
         if (outputs == nullptr) {

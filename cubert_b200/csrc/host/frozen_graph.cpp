@@ -254,6 +254,67 @@ FrozenGraph<T>::FrozenGraph(const char *filename) {
 }
 
 template <typename T>
+void FrozenGraph<T>::validate(size_t seq_length, size_t num_hidden_layers, size_t num_attention_heads) const {
+    const size_t H = hidden_size, I = intermediate_size;
+    auto fail = [](const std::string &why) { throw std::invalid_argument("model file invalid: " + why); };
+    if (H == 0 || vocab_size == 0 || type_vocab_size == 0 || seq_length == 0 || num_attention_heads == 0 ||
+        H % num_attention_heads != 0 || (num_hidden_layers > 0 && I == 0)) {
+        fail("geometry");
+    }
+    auto count_of = [&](const std::string &name) -> size_t {
+        auto it = var.find(name);
+        if (it == var.end()) {
+            fail("no tensor named " + name);
+        }
+        return it->second.size();
+    };
+    auto expect = [&](const std::string &name, size_t count) {
+        if (count_of(name) != count) {
+            fail(name + " has " + std::to_string(count_of(name)) + " elements, expected " + std::to_string(count));
+        }
+    };
+    expect("bert/embeddings/word_embeddings", vocab_size * H);
+    expect("bert/embeddings/token_type_embeddings", type_vocab_size * H);
+    const size_t positions = count_of("bert/embeddings/position_embeddings");
+    if (positions % H != 0 || positions / H < seq_length) {
+        fail("position_embeddings holds " + std::to_string(positions / H) + " rows, seq_length is " +
+             std::to_string(seq_length));
+    }
+    expect("bert/embeddings/LayerNorm/gamma", H);
+    expect("bert/embeddings/LayerNorm/beta", H);
+    for (size_t l = 0; l < num_hidden_layers; ++l) {
+        const std::string p = "bert/encoder/layer_" + std::to_string(l);
+        for (const char *which : {"query", "key", "value"}) {
+            expect(p + "/attention/self/" + which + "/kernel", H * H);
+            expect(p + "/attention/self/" + which + "/bias", H);
+        }
+        expect(p + "/attention/output/dense/kernel", H * H);
+        expect(p + "/attention/output/dense/bias", H);
+        expect(p + "/attention/output/LayerNorm/gamma", H);
+        expect(p + "/attention/output/LayerNorm/beta", H);
+        expect(p + "/intermediate/dense/kernel", H * I);
+        expect(p + "/intermediate/dense/bias", I);
+        expect(p + "/output/dense/kernel", I * H);
+        expect(p + "/output/dense/bias", H);
+        expect(p + "/output/LayerNorm/gamma", H);
+        expect(p + "/output/LayerNorm/beta", H);
+    }
+    if (has("bert/pooler/dense/kernel")) {
+        expect("bert/pooler/dense/kernel", H * H);
+        expect("bert/pooler/dense/bias", H);
+    }
+    if (has("output_weights")) {
+        if (num_labels == 0) {
+            fail("output_weights without labels");
+        }
+        expect("output_weights", num_labels * H);
+        if (has("output_bias")) {
+            expect("output_bias", num_labels);
+        }
+    }
+}
+
+template <typename T>
 const T *FrozenGraph<T>::data(const std::string &name) const {
     auto it = var.find(name);
     if (it == var.end()) {

@@ -31,6 +31,13 @@ public:
     size_t num_labels = 1;  // reference default when there is no output_weights (tensorflow/Graph.h:23)
 
     bool has(const std::string &name) const { return var.count(name) != 0; }
+
+    // Checks that every tensor a BERT of this geometry reads is present with exactly the element count
+    // the geometry implies (the shapes in the file and the caller's seq_length, layer and head counts
+    // are otherwise taken on trust, and a replica copies `count` elements from each array): throws
+    // std::invalid_argument("model file invalid: ...") on the first mismatch. The position table may
+    // have more rows than seq_length. The reference does not check (src/cuBERT/Bert.cpp:17-53).
+    void validate(size_t seq_length, size_t num_hidden_layers, size_t num_attention_heads) const;
     const T *data(const std::string &name) const;  // throws std::invalid_argument if absent
 };
 

@@ -25,8 +25,8 @@ struct OptionSpec {
 static const OptionSpec kOptionSpecs[CUBK_OPT_COUNT] = {
     {"CUBK_BULK_COPY", -1, -1, 1},          // CUBK_OPT_EMBED_STAGED_ROWS
     {"CUBK_SOFTMAX_MASK_SMEM", 1, 0, 1},    // CUBK_OPT_SOFTMAX_MASK_SMEM
-    {"CUBK_EXACT_WIDTH_ROWS", 1, 0, 9},     // CUBK_OPT_EXACT_WIDTH_ROWS
-    {"CUBK_EXACT_WIDTH_EMBED", 1, 0, 9},    // CUBK_OPT_EXACT_WIDTH_EMBED
+    {"CUBK_EXACT_WIDTH_ROWS", 1, 0, 1},     // CUBK_OPT_EXACT_WIDTH_ROWS
+    {"CUBK_EXACT_WIDTH_EMBED", 1, 0, 1},    // CUBK_OPT_EXACT_WIDTH_EMBED
 };
 
 static std::atomic<int> g_options[CUBK_OPT_COUNT];

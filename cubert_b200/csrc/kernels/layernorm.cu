@@ -503,86 +503,53 @@ embed_ln_bulk_kernel(const int32_t *ids, const int8_t *segment_ids, const T *wor
 // The shapes BERT runs (hidden 768 and 1024 in either storage type) fill a warp exactly, so these
 // kernels carry no per-vector bounds predicate and no zero fill; row addresses are vector pointers
 // advanced by a constant; the mean uses a precomputed 1 / channels and the scale one rsqrt
-// (MUFU.RSQ, 2 ulp; the reference's GPU body uses rsqrtf as well, op/LayerNorm.cu:70). A warp works
-// on RPP rows per pass: their shuffle reductions interleave, and gamma / beta / bias are read from
-// shared memory once per pass instead of once per row.
+// (MUFU.RSQ, 2 ulp; the reference's GPU body uses rsqrtf as well, op/LayerNorm.cu:70); binary16
+// inputs enter the float32 sums through add.f32.f16 (one instruction per element instead of a
+// conversion and an add). About half the instructions per row of the general kernels above
+// (6.7 M against 13.1 M warp instructions on 32768 x 768 binary16), which is what keeps them on the
+// memory roofline when the SM clock drops under the power cap inside a BERT step.
 constexpr int kRowsBlock = 256;
 
-template <typename T, int VPT, int RPP>
-__device__ __forceinline__ void normalise_store_rows(float2 (&v)[RPP][VPT][Vec2<T>::PAIRS], int lane, float inv_channels,
-                                                     const float4 *s_gamma, const float4 *s_beta, uint4 *(&dst)[RPP],
-                                                     const bool (&live)[RPP]) {
+template <typename T, int VPT>
+__device__ __forceinline__ void normalise_store_row(float2 (&v)[VPT][Vec2<T>::PAIRS], int lane, float inv_channels,
+                                                    const float4 *s_gamma, const float4 *s_beta, uint4 *dst) {
     constexpr int PAIRS = Vec2<T>::PAIRS;
     constexpr int NVEC = 32 * VPT;
-    float sum[RPP];
+    float2 s2 = make_float2(0.f, 0.f);
 #pragma unroll
-    for (int p = 0; p < RPP; ++p) {
-        float2 s2 = make_float2(0.f, 0.f);
+    for (int k = 0; k < VPT; ++k) {
 #pragma unroll
-        for (int k = 0; k < VPT; ++k) {
-#pragma unroll
-            for (int e = 0; e < PAIRS; ++e) {
-                s2 = add2(s2, v[p][k][e]);
-            }
-        }
-        sum[p] = s2.x + s2.y;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-        for (int p = 0; p < RPP; ++p) {
-            sum[p] += __shfl_xor_sync(0xffffffffu, sum[p], o, 32);
+        for (int e = 0; e < PAIRS; ++e) {
+            s2 = add2(s2, v[k][e]);
         }
     }
-    float sq[RPP];
+    const float2 neg_mean = splat2(-group_sum<32>(s2.x + s2.y) * inv_channels);
+    float2 q2 = make_float2(0.f, 0.f);
 #pragma unroll
-    for (int p = 0; p < RPP; ++p) {
-        const float2 neg_mean = splat2(-sum[p] * inv_channels);
-        float2 q2 = make_float2(0.f, 0.f);
+    for (int k = 0; k < VPT; ++k) {
 #pragma unroll
-        for (int k = 0; k < VPT; ++k) {
-#pragma unroll
-            for (int e = 0; e < PAIRS; ++e) {
-                v[p][k][e] = add2(v[p][k][e], neg_mean);  // keep the centred value
-                q2 = fma2(v[p][k][e], v[p][k][e], q2);
-            }
-        }
-        sq[p] = q2.x + q2.y;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-        for (int p = 0; p < RPP; ++p) {
-            sq[p] += __shfl_xor_sync(0xffffffffu, sq[p], o, 32);
+        for (int e = 0; e < PAIRS; ++e) {
+            v[k][e] = add2(v[k][e], neg_mean);  // keep the centred value
+            q2 = fma2(v[k][e], v[k][e], q2);
         }
     }
-    float2 rstd[RPP];
-#pragma unroll
-    for (int p = 0; p < RPP; ++p) {
-        rstd[p] = splat2(rsqrtf(fmaf(sq[p], inv_channels, kLayerNormEps)));
-    }
+    const float2 rstd = splat2(rsqrtf(fmaf(group_sum<32>(q2.x + q2.y), inv_channels, kLayerNormEps)));
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
         const int idx = lane + 32 * k;
-        float2 g[PAIRS], b[PAIRS];
+        float2 g[PAIRS], b[PAIRS], o[PAIRS];
         load_param<T>(s_gamma, NVEC, idx, g);
         load_param<T>(s_beta, NVEC, idx, b);
 #pragma unroll
-        for (int p = 0; p < RPP; ++p) {
-            float2 o[PAIRS];
-#pragma unroll
-            for (int e = 0; e < PAIRS; ++e) {
-                o[e] = fma2(mul2(g[e], rstd[p]), v[p][k][e], b[e]);  // beta + (gamma * rstd) * (t - mean)
-            }
-            if (live[p]) {
-                dst[p][idx] = Vec2<T>::pack(o);
-            }
+        for (int e = 0; e < PAIRS; ++e) {
+            o[e] = fma2(mul2(g[e], rstd), v[k][e], b[e]);  // beta + (gamma * rstd) * (t - mean)
         }
+        dst[idx] = Vec2<T>::pack(o);
     }
 }
 
-// K2. PREFETCH: the next pass's rows are requested before the current ones are reduced.
-template <typename T, int VPT, int RPP, bool PREFETCH, bool MIXED>
+// K2: a warp per row, persistent blocks; the next row is requested before the current one is reduced.
+template <typename T, int VPT>
 __global__ void __launch_bounds__(kRowsBlock)
 bias_residual_ln_rows_kernel(const T *x, const T *bias, const T *residual, const T *gamma, const T *beta, T *out,
                              int64_t rows, float inv_channels) {
@@ -590,6 +557,7 @@ bias_residual_ln_rows_kernel(const T *x, const T *bias, const T *residual, const
     constexpr int PAIRS = Vec2<T>::PAIRS;
     constexpr int NVEC = 32 * VPT;
     constexpr int WARPS = kRowsBlock / 32;
+    constexpr bool MIXED = sizeof(T) == 2;
     extern __shared__ float4 s_params[];
     const float4 *s_gamma = s_params;
     const float4 *s_beta = s_params + (EPV / 4) * NVEC;
@@ -600,23 +568,19 @@ bias_residual_ln_rows_kernel(const T *x, const T *bias, const T *residual, const
     const uint4 *xv = reinterpret_cast<const uint4 *>(x) + lane;
     const uint4 *rv = reinterpret_cast<const uint4 *>(residual) + lane;
     uint4 *ov = reinterpret_cast<uint4 *>(out);
-    const int64_t stride = (int64_t) gridDim.x * (WARPS * RPP);
-    int64_t row = ((int64_t) blockIdx.x * WARPS + warp) * RPP;
+    const int64_t stride = (int64_t) gridDim.x * WARPS;
+    int64_t row = (int64_t) blockIdx.x * WARPS + warp;
 
-    uint4 rx[RPP][VPT], rr[RPP][VPT];
-    auto issue_loads = [&](int64_t r0) {
+    uint4 rx[VPT], rr[VPT];
+    auto issue_loads = [&](int64_t r) {
 #pragma unroll
-        for (int p = 0; p < RPP; ++p) {
-            const int64_t r = r0 + p < rows ? r0 + p : rows - 1;  // a row past the end repeats the last one
-#pragma unroll
-            for (int k = 0; k < VPT; ++k) {
-                rx[p][k] = __ldcs(xv + r * NVEC + 32 * k);
-                rr[p][k] = __ldcs(rv + r * NVEC + 32 * k);
-            }
+        for (int k = 0; k < VPT; ++k) {
+            rx[k] = __ldcs(xv + r * NVEC + 32 * k);
+            rr[k] = __ldcs(rv + r * NVEC + 32 * k);
         }
     };
-    // The first rows' loads go out before the parameters are staged, so that the two latencies overlap.
-    if (PREFETCH && row < rows) {
+    // The first row's loads go out before the parameters are staged, so that the two latencies overlap.
+    if (row < rows) {
         issue_loads(row);
     }
     stage_param<T>(gamma, s_params, NVEC, threadIdx.x, kRowsBlock);
@@ -625,36 +589,18 @@ bias_residual_ln_rows_kernel(const T *x, const T *bias, const T *residual, const
     __syncthreads();
 
     for (; row < rows; row += stride) {
-        if (!PREFETCH) {
-            issue_loads(row);
-        }
-        float2 v[RPP][VPT][PAIRS];
+        float2 v[VPT][PAIRS];
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
-            float2 b[PAIRS];
-            load_param<T>(s_bias, NVEC, lane + 32 * k, b);
-#pragma unroll
-            for (int p = 0; p < RPP; ++p) {
-#pragma unroll
-                for (int e = 0; e < PAIRS; ++e) {
-                    v[p][k][e] = b[e];
-                }
-                accumulate_vec<T, MIXED>(rx[p][k], v[p][k]);  // (x + bias)
-                accumulate_vec<T, MIXED>(rr[p][k], v[p][k]);  //          + residual
-            }
+            load_param<T>(s_bias, NVEC, lane + 32 * k, v[k]);
+            accumulate_vec<T, MIXED>(rx[k], v[k]);  // (x + bias)
+            accumulate_vec<T, MIXED>(rr[k], v[k]);  //          + residual
         }
-        uint4 *dst[RPP];
-        bool live[RPP];
-#pragma unroll
-        for (int p = 0; p < RPP; ++p) {
-            live[p] = row + p < rows;
-            dst[p] = ov + (row + p) * NVEC;
-        }
-        // The raw registers are free again: fetch the next rows while these are reduced.
-        if (PREFETCH && row + stride < rows) {
+        // The raw registers are free again: fetch the next row while this one is reduced.
+        if (row + stride < rows) {
             issue_loads(row + stride);
         }
-        normalise_store_rows<T, VPT, RPP>(v, lane, inv_channels, s_gamma, s_beta, dst, live);
+        normalise_store_row<T, VPT>(v, lane, inv_channels, s_gamma, s_beta, ov + row * NVEC);
     }
 }
 
@@ -664,7 +610,7 @@ bias_residual_ln_rows_kernel(const T *x, const T *bias, const T *residual, const
 // two steps ahead and the gathered word row one step ahead of the row being normalised.
 constexpr int kMaxTypeRowsSmem = 4;
 
-template <typename T, int VPT, bool MIXED, int MIN_BLOCKS>
+template <typename T, int VPT, int MIN_BLOCKS>
 __global__ void __launch_bounds__(kRowsBlock, MIN_BLOCKS)
 embed_ln_rows_kernel(const int32_t *ids, const int8_t *segment_ids, const T *word, const T *pos, const T *type,
                      const T *gamma, const T *beta, T *out, uint32_t tokens, uint32_t batch, uint32_t seq, int vocab,
@@ -674,6 +620,7 @@ embed_ln_rows_kernel(const int32_t *ids, const int8_t *segment_ids, const T *wor
     constexpr int NVEC = 32 * VPT;
     constexpr int WARPS = kRowsBlock / 32;
     constexpr int PV = (EPV / 4) * NVEC;  // float4 per staged row
+    constexpr bool MIXED = sizeof(T) == 2;
     extern __shared__ float4 s_params[];
     const float4 *s_gamma = s_params;
     const float4 *s_beta = s_params + PV;
@@ -758,23 +705,22 @@ embed_ln_rows_kernel(const int32_t *ids, const int8_t *segment_ids, const T *wor
             }
         }
         const float4 *s_trow = s_type + seg_in_flight * PV;
-        float2 v[1][VPT][PAIRS];
+        float2 v[VPT][PAIRS];
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
             float2 t[PAIRS];
             load_param<T>(s_trow, NVEC, lane + 32 * k, t);
 #pragma unroll
             for (int e = 0; e < PAIRS; ++e) {
-                v[0][k][e] = pos_row[k][e];
+                v[k][e] = pos_row[k][e];
             }
-            accumulate_vec<T, MIXED>(rw[k], v[0][k]);  // (word + pos)
+            accumulate_vec<T, MIXED>(rw[k], v[k]);  // (word + pos)
 #pragma unroll
             for (int e = 0; e < PAIRS; ++e) {
-                v[0][k][e] = add2(v[0][k][e], t[e]);   //             + type, the reference's order
+                v[k][e] = add2(v[k][e], t[e]);      //             + type, the reference's order
             }
         }
-        uint4 *dst[1] = {ov + ((size_t) b * seq + s) * NVEC};
-        const bool live[1] = {true};
+        uint4 *dst = ov + ((size_t) b * seq + s) * NVEC;
         // the raw registers are free again: request the next word row, then the indices after it
         if (step + 1 < j_count) {
             issue_word_row();
@@ -786,7 +732,7 @@ embed_ln_rows_kernel(const int32_t *ids, const int8_t *segment_ids, const T *wor
             ++s;
             new_pos = true;
         }
-        normalise_store_rows<T, VPT, 1>(v, lane, inv_hidden, s_gamma, s_beta, dst, live);
+        normalise_store_row<T, VPT>(v, lane, inv_hidden, s_gamma, s_beta, dst);
     }
 }
 
@@ -914,40 +860,20 @@ static bool use_bulk_rows(size_t row_bytes, int64_t tokens) {
     return row_bytes >= 2048 && tokens >= 16384;
 }
 
-static int k2_variant() {
-    return option(CUBK_OPT_EXACT_WIDTH_ROWS);
-}
-
-static int k1_variant() {
-    return option(CUBK_OPT_EXACT_WIDTH_EMBED);
-}
-
-// Launch of the exact-width K2 for one VPT; false = this variant / width is not built.
+// Launch of the exact-width K2 for one VPT.
 template <typename T, int VPT>
-bool launch_ln_rows(int variant, const T *x, const T *bias, const T *residual, const T *gamma, const T *beta, T *out,
+void launch_ln_rows(const T *x, const T *bias, const T *residual, const T *gamma, const T *beta, T *out,
                     int64_t rows, int channels, cudaStream_t stream) {
+    static OccupancyCache cache;
     const size_t smem = sizeof(float) * 3 * (size_t) channels;
-    const float inv = 1.f / (float) channels;
-#define ROWS_LAUNCH(RPP, PREFETCH, MIXED)                                                                  \
-    {                                                                                                      \
-        static OccupancyCache cache;                                                                       \
-        auto kernel = bias_residual_ln_rows_kernel<T, VPT, RPP, PREFETCH, MIXED>;                          \
-        int64_t grid = (rows + (kRowsBlock / 32) * RPP - 1) / ((kRowsBlock / 32) * RPP);                   \
-        const int resident = resident_blocks(kernel, kRowsBlock, smem, &cache);                            \
-        if (grid > resident) grid = resident;                                                              \
-        kernel<<<(unsigned) grid, kRowsBlock, smem, stream>>>(x, bias, residual, gamma, beta, out, rows, inv); \
-        return true;                                                                                       \
+    auto kernel = bias_residual_ln_rows_kernel<T, VPT>;
+    int64_t grid = (rows + (kRowsBlock / 32) - 1) / (kRowsBlock / 32);
+    const int resident = resident_blocks(kernel, kRowsBlock, smem, &cache);
+    if (grid > resident) {
+        grid = resident;
     }
-    constexpr bool HALF = sizeof(T) == 2;
-    switch (variant) {
-        case 1: ROWS_LAUNCH(1, true, false)
-        case 2: ROWS_LAUNCH(1, true, HALF)
-        case 3: ROWS_LAUNCH(2, false, false)
-        case 4: ROWS_LAUNCH(2, false, HALF)
-        case 5: ROWS_LAUNCH(2, true, false)
-        default: return false;
-    }
-#undef ROWS_LAUNCH
+    kernel<<<(unsigned) grid, kRowsBlock, smem, stream>>>(x, bias, residual, gamma, beta, out, rows,
+                                                          1.f / (float) channels);
 }
 
 template <typename T>
@@ -967,17 +893,19 @@ int bias_residual_ln(const T *x, const T *bias, const T *residual, const T *gamm
                         (bias == nullptr || aligned16(bias)) && (residual == nullptr || aligned16(residual));
     if (vec_ok) {
         const int nvec = channels / EPV;
-        if (bias != nullptr && residual != nullptr && nvec % 32 == 0 && k2_variant() > 0) {
-            bool launched = false;
+        if (bias != nullptr && residual != nullptr && nvec % 32 == 0 && option(CUBK_OPT_EXACT_WIDTH_ROWS) != 0) {
+            bool launched = true;
+#define ROWS(VPT) launch_ln_rows<T, VPT>(x, bias, residual, gamma, beta, out, rows, channels, stream)
             switch (nvec / 32) {
-                case 1: launched = launch_ln_rows<T, 1>(k2_variant(), x, bias, residual, gamma, beta, out, rows, channels, stream); break;
-                case 2: launched = launch_ln_rows<T, 2>(k2_variant(), x, bias, residual, gamma, beta, out, rows, channels, stream); break;
-                case 3: launched = launch_ln_rows<T, 3>(k2_variant(), x, bias, residual, gamma, beta, out, rows, channels, stream); break;
-                case 4: launched = launch_ln_rows<T, 4>(k2_variant(), x, bias, residual, gamma, beta, out, rows, channels, stream); break;
-                case 6: launched = launch_ln_rows<T, 6>(k2_variant(), x, bias, residual, gamma, beta, out, rows, channels, stream); break;
-                case 8: launched = launch_ln_rows<T, 8>(k2_variant(), x, bias, residual, gamma, beta, out, rows, channels, stream); break;
-                default: break;
+                case 1: ROWS(1); break;
+                case 2: ROWS(2); break;
+                case 3: ROWS(3); break;
+                case 4: ROWS(4); break;
+                case 6: ROWS(6); break;
+                case 8: ROWS(8); break;
+                default: launched = false; break;
             }
+#undef ROWS
             if (launched) {
                 return check_launch();
             }
@@ -1043,38 +971,28 @@ bool launch_embed_bulk_depth(const int32_t *ids, const int8_t *segment_ids, cons
                                         hidden, nvec, vocab, type_vocab, status, stream);
 }
 
-// Launch of the exact-width K1 for one VPT; false = this variant is not built.
+// Launch of the exact-width K1 for one VPT; false = the staged rows do not fit shared memory.
+// Rows of three vectors per lane (hidden 768 in binary16) are compiled for three resident blocks per
+// SM (80 registers, a few spilled words): 20.1 us against 25.2 us without the cap on 32768 tokens.
 template <typename T, int VPT>
-bool launch_embed_rows(int variant, const int32_t *ids, const int8_t *segment_ids, const T *word, const T *pos,
-                       const T *type, const T *gamma, const T *beta, T *out, int64_t tokens, int batch, int seq,
-                       int hidden, int vocab, int type_vocab, uint32_t *status, cudaStream_t stream) {
+bool launch_embed_rows(const int32_t *ids, const int8_t *segment_ids, const T *word, const T *pos, const T *type,
+                       const T *gamma, const T *beta, T *out, int64_t tokens, int batch, int seq, int hidden,
+                       int vocab, int type_vocab, uint32_t *status, cudaStream_t stream) {
+    static OccupancyCache cache;
     const size_t smem = sizeof(float) * (2 + (size_t) type_vocab) * (size_t) hidden;
     if (smem > kMaxParamSmem) {
         return false;
     }
-    const float inv = 1.f / (float) hidden;
-#define ROWS_LAUNCH(MIXED, MIN_BLOCKS)                                                                     \
-    {                                                                                                      \
-        static OccupancyCache cache;                                                                       \
-        auto kernel = embed_ln_rows_kernel<T, VPT, MIXED, MIN_BLOCKS>;                                     \
-        int64_t grid = (tokens + (kRowsBlock / 32) - 1) / (kRowsBlock / 32);                               \
-        const int resident = resident_blocks(kernel, kRowsBlock, smem, &cache);                            \
-        if (grid > resident) grid = resident;                                                              \
-        kernel<<<(unsigned) grid, kRowsBlock, smem, stream>>>(ids, segment_ids, word, pos, type, gamma,    \
-                                                              beta, out, (uint32_t) tokens,                \
-                                                              (uint32_t) batch, (uint32_t) seq, vocab,     \
-                                                              type_vocab, status, inv);                    \
-        return true;                                                                                       \
+    auto kernel = embed_ln_rows_kernel<T, VPT, (VPT == 3 ? 3 : 1)>;
+    int64_t grid = (tokens + (kRowsBlock / 32) - 1) / (kRowsBlock / 32);
+    const int resident = resident_blocks(kernel, kRowsBlock, smem, &cache);
+    if (grid > resident) {
+        grid = resident;
     }
-    constexpr bool HALF = sizeof(T) == 2;
-    switch (variant) {
-        case 1: ROWS_LAUNCH(false, 1)
-        case 2: ROWS_LAUNCH(HALF, 1)
-        case 3: ROWS_LAUNCH(false, (HALF && VPT == 3 ? 3 : 1))
-        case 4: ROWS_LAUNCH(HALF, (HALF && VPT == 3 ? 3 : 1))
-        default: return false;
-    }
-#undef ROWS_LAUNCH
+    kernel<<<(unsigned) grid, kRowsBlock, smem, stream>>>(ids, segment_ids, word, pos, type, gamma, beta, out,
+                                                          (uint32_t) tokens, (uint32_t) batch, (uint32_t) seq, vocab,
+                                                          type_vocab, status, 1.f / (float) hidden);
+    return true;
 }
 
 template <typename T>
@@ -1117,20 +1035,28 @@ int embed_ln(const int32_t *ids, const int8_t *segment_ids, const T *word, const
                 return check_launch();
             }
         }
-        if (nvec % 32 == 0 && type_vocab <= kMaxTypeRowsSmem && k1_variant() > 0) {
+        // binary16 rows that fill a warp exactly (float32 rows are faster on the kernels above and below:
+        // 33 us general / 30 us staged against 40 us on 32768 tokens of hidden 768)
+        if constexpr (sizeof(T) == 2) {
+          if (nvec % 32 == 0 && type_vocab <= kMaxTypeRowsSmem && option(CUBK_OPT_EXACT_WIDTH_EMBED) != 0) {
             bool launched = false;
+#define ROWS(VPT)                                                                                              \
+    launched = launch_embed_rows<T, VPT>(ids, segment_ids, word, pos, type, gamma, beta, out, tokens, batch, seq, \
+                                         hidden, vocab, type_vocab, status, stream)
             switch (nvec / 32) {
-                case 1: launched = launch_embed_rows<T, 1>(k1_variant(), ids, segment_ids, word, pos, type, gamma, beta, out, tokens, batch, seq, hidden, vocab, type_vocab, status, stream); break;
-                case 2: launched = launch_embed_rows<T, 2>(k1_variant(), ids, segment_ids, word, pos, type, gamma, beta, out, tokens, batch, seq, hidden, vocab, type_vocab, status, stream); break;
-                case 3: launched = launch_embed_rows<T, 3>(k1_variant(), ids, segment_ids, word, pos, type, gamma, beta, out, tokens, batch, seq, hidden, vocab, type_vocab, status, stream); break;
-                case 4: launched = launch_embed_rows<T, 4>(k1_variant(), ids, segment_ids, word, pos, type, gamma, beta, out, tokens, batch, seq, hidden, vocab, type_vocab, status, stream); break;
-                case 6: launched = launch_embed_rows<T, 6>(k1_variant(), ids, segment_ids, word, pos, type, gamma, beta, out, tokens, batch, seq, hidden, vocab, type_vocab, status, stream); break;
-                case 8: launched = launch_embed_rows<T, 8>(k1_variant(), ids, segment_ids, word, pos, type, gamma, beta, out, tokens, batch, seq, hidden, vocab, type_vocab, status, stream); break;
+                case 1: ROWS(1); break;
+                case 2: ROWS(2); break;
+                case 3: ROWS(3); break;
+                case 4: ROWS(4); break;
+                case 6: ROWS(6); break;
+                case 8: ROWS(8); break;
                 default: break;
             }
+#undef ROWS
             if (launched) {
                 return check_launch();
             }
+          }
         }
 #define LAUNCH(TPR, VPT, BLOCK, PERSISTENT)                                                           \
     {                                                                                                 \

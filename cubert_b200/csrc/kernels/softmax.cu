@@ -46,10 +46,16 @@ __device__ __forceinline__ void load_mask_add<__half>(const int8_t *mask_row, in
 // MASK_SMEM: the additive terms live in shared memory (float32, [EPV/4][nvec] so that 128-bit reads
 // are conflict-free) instead of in registers; long rows then need half the registers, and twice as
 // many warps stay resident.
-template <typename T, int LPR, int VPT, int ROWS, int BLOCK, bool MASK_SMEM>
+// EXTENTS: key_extents[b] = n says that every key of batch entry b from column n on is masked out (and
+// at least one below n is kept). Vectors that lie entirely at or beyond n are then not read at all:
+// their probabilities are exactly 0, which is what the full computation gives them. They are written
+// as zeros up to column max(n, zero_to) and left untouched beyond it (a consumer that reads only the
+// first n columns of this entry needs no zeros after them).
+template <typename T, int LPR, int VPT, int ROWS, int BLOCK, bool MASK_SMEM, bool EXTENTS>
 __global__ void __launch_bounds__(BLOCK)
 masked_softmax_kernel(const T *scores, const int8_t *mask, T *out, uint32_t rows_per_batch, int seq, int nvec,
-                      float scale, uint32_t total_items, FastDiv items_per_batch) {
+                      float scale, uint32_t total_items, FastDiv items_per_batch, const int32_t *key_extents,
+                      int zero_to) {
     constexpr int EPV = Vec<T>::EPV;
     constexpr int PAIRS = Vec2<T>::PAIRS;
     extern __shared__ float4 s_madd[];
@@ -77,9 +83,25 @@ masked_softmax_kernel(const T *scores, const int8_t *mask, T *out, uint32_t rows
     uint32_t cur_b = 0xffffffffu;
     const float2 scale2 = splat2(scale);
     const float2 log2e2 = splat2(kLog2e);
+    // per vector of this lane: read and reduced (in_use), written (stored); all true without extents
+    bool in_use[VPT], stored[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        in_use[k] = stored[k] = l + k * LPR < nvec;
+    }
 
     for (uint32_t item = item_begin; item < item_end; ++item) {
         const uint32_t b = fast_div(item, items_per_batch);
+        if (EXTENTS && b != cur_b) {
+            const int n = min(max(__ldg(key_extents + b), 1), seq);
+            const int write_to = max(n, zero_to);
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                const int first_col = (l + k * LPR) * EPV;
+                in_use[k] = first_col < n;
+                stored[k] = first_col < min(write_to, seq);
+            }
+        }
         if (b != cur_b && MASK_SMEM) {  // uniform over the block: all its threads walk the same items
             cur_b = b;
             __syncthreads();  // the previous entry's terms are no longer read
@@ -132,7 +154,7 @@ masked_softmax_kernel(const T *scores, const int8_t *mask, T *out, uint32_t rows
 #pragma unroll
             for (int k = 0; k < VPT; ++k) {
                 const int idx = l + k * LPR;
-                raw[r][k] = (live[r] && idx < nvec) ? ld_stream(src + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
+                raw[r][k] = (live[r] && in_use[k]) ? ld_stream(src + (size_t) idx * EPV) : make_uint4(0, 0, 0, 0);
             }
         }
 
@@ -143,7 +165,7 @@ masked_softmax_kernel(const T *scores, const int8_t *mask, T *out, uint32_t rows
 #pragma unroll
             for (int k = 0; k < VPT; ++k) {
                 Vec2<T>::unpack(raw[r][k], v[k]);
-                if (l + k * LPR < nvec) {
+                if (in_use[k]) {
                     float2 m[PAIRS];
                     if (MASK_SMEM) {
 #pragma unroll
@@ -168,7 +190,7 @@ masked_softmax_kernel(const T *scores, const int8_t *mask, T *out, uint32_t rows
             float2 sum2 = make_float2(0.f, 0.f);
 #pragma unroll
             for (int k = 0; k < VPT; ++k) {
-                if (l + k * LPR < nvec) {
+                if (in_use[k]) {
 #pragma unroll
                     for (int e = 0; e < PAIRS; ++e) {
                         const float2 t = fma2(v[k][e], log2e2, neg_mx);
@@ -185,12 +207,14 @@ masked_softmax_kernel(const T *scores, const int8_t *mask, T *out, uint32_t rows
 #pragma unroll
                 for (int k = 0; k < VPT; ++k) {
                     const int idx = l + k * LPR;
-                    if (idx < nvec) {
+                    if (in_use[k]) {
 #pragma unroll
                         for (int e = 0; e < PAIRS; ++e) {
                             v[k][e] = mul2(v[k][e], inv);
                         }
                         st_vec(dst + (size_t) idx * EPV, Vec2<T>::pack(v[k]));
+                    } else if (EXTENTS && stored[k]) {
+                        st_vec(dst + (size_t) idx * EPV, make_uint4(0, 0, 0, 0));
                     }
                 }
             }
@@ -198,11 +222,11 @@ masked_softmax_kernel(const T *scores, const int8_t *mask, T *out, uint32_t rows
     }
 }
 
-// Any row length, any alignment: one warp per row, three scalar passes.
+// Any row length, any alignment: one warp per row, three scalar passes. Key extents as above, by column.
 template <typename T>
 __global__ void __launch_bounds__(128)
 masked_softmax_generic_kernel(const T *scores, const int8_t *mask, T *out, int64_t rows, int64_t rows_per_batch,
-                              int seq, float scale) {
+                              int seq, float scale, const int32_t *key_extents, int zero_to) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t) blockIdx.x * 4 + (threadIdx.x >> 5);
     if (row >= rows) {
@@ -210,23 +234,30 @@ masked_softmax_generic_kernel(const T *scores, const int8_t *mask, T *out, int64
     }
     const T *src = scores + row * seq;
     T *dst = out + row * seq;
-    const int8_t *mask_row = mask != nullptr ? mask + (row / rows_per_batch) * seq : nullptr;
+    const int64_t b = row / rows_per_batch;
+    const int8_t *mask_row = mask != nullptr ? mask + b * seq : nullptr;
+    const int n = key_extents != nullptr ? min(max(key_extents[b], 1), seq) : seq;
+    const int write_to = key_extents != nullptr ? min(max(n, zero_to), seq) : seq;
     float mx = -3.0e38f;
-    for (int j = lane; j < seq; j += 32) {
+    for (int j = lane; j < n; j += 32) {
         const float add = (mask_row != nullptr && mask_row[j] == 0) ? kMaskedScore : 0.f;
         mx = fmaxf(mx, fmaf(scale, to_float<T>(src[j]), add));
     }
     mx = group_max<32>(mx);
     float sum = 0.f;
-    for (int j = lane; j < seq; j += 32) {
+    for (int j = lane; j < n; j += 32) {
         const float add = (mask_row != nullptr && mask_row[j] == 0) ? kMaskedScore : 0.f;
         sum += fast_exp2((fmaf(scale, to_float<T>(src[j]), add) - mx) * kLog2e);
     }
     sum = group_sum<32>(sum);
     const float inv = 1.f / sum;
-    for (int j = lane; j < seq; j += 32) {
-        const float add = (mask_row != nullptr && mask_row[j] == 0) ? kMaskedScore : 0.f;
-        dst[j] = from_float<T>(fast_exp2((fmaf(scale, to_float<T>(src[j]), add) - mx) * kLog2e) * inv);
+    for (int j = lane; j < write_to; j += 32) {
+        float p = 0.f;
+        if (j < n) {
+            const float add = (mask_row != nullptr && mask_row[j] == 0) ? kMaskedScore : 0.f;
+            p = fast_exp2((fmaf(scale, to_float<T>(src[j]), add) - mx) * kLog2e) * inv;
+        }
+        dst[j] = from_float<T>(p);
     }
 }
 
@@ -241,8 +272,10 @@ static bool mask_in_smem() {
 
 template <typename T>
 int masked_softmax(const T *scores, const int8_t *mask, int64_t rows, int64_t rows_per_batch, int seq,
-                   float scale, T *out, cudaStream_t stream) {
-    if (scores == nullptr || out == nullptr || rows < 0 || seq <= 0 || (mask != nullptr && rows_per_batch <= 0)) {
+                   float scale, T *out, cudaStream_t stream, const int32_t *key_extents = nullptr,
+                   int zero_to = 0) {
+    if (scores == nullptr || out == nullptr || rows < 0 || seq <= 0 || (mask != nullptr && rows_per_batch <= 0) ||
+        (key_extents != nullptr && (mask == nullptr || zero_to < 0))) {
         return CUBK_ERR_INVALID_ARG;
     }
     if (rows == 0) {
@@ -263,9 +296,11 @@ int masked_softmax(const T *scores, const int8_t *mask, int64_t rows, int64_t ro
                         rows % rows_per_batch == 0;
     if (vec_ok) {
 #define LAUNCH_AS(LPR, VPT, ROWS, MASK_SMEM)                                                            \
+    if (key_extents != nullptr) LAUNCH_WITH(LPR, VPT, ROWS, MASK_SMEM, true) else LAUNCH_WITH(LPR, VPT, ROWS, MASK_SMEM, false)
+#define LAUNCH_WITH(LPR, VPT, ROWS, MASK_SMEM, EXTENTS)                                                 \
     {                                                                                                   \
         static OccupancyCache cache;                                                                    \
-        auto kernel = masked_softmax_kernel<T, LPR, VPT, ROWS, BLOCK, MASK_SMEM>;                       \
+        auto kernel = masked_softmax_kernel<T, LPR, VPT, ROWS, BLOCK, MASK_SMEM, EXTENTS>;              \
         const size_t smem = MASK_SMEM ? sizeof(float) * (size_t) seq : 0;                               \
         const int64_t rows_per_block = (int64_t) (BLOCK / 32) * (32 / LPR) * ROWS;                      \
         const int64_t per_batch = (rows_per_batch + rows_per_block - 1) / rows_per_block;               \
@@ -274,7 +309,8 @@ int masked_softmax(const T *scores, const int8_t *mask, int64_t rows, int64_t ro
         if (grid > items) grid = items;                                                                 \
         kernel<<<(unsigned) grid, BLOCK, smem, stream>>>(scores, mask, out, (uint32_t) rows_per_batch,  \
                                                          seq, nvec, scale, (uint32_t) items,            \
-                                                         make_fastdiv((uint32_t) per_batch));           \
+                                                         make_fastdiv((uint32_t) per_batch), key_extents,\
+                                                         zero_to);                                      \
     }
 #define LAUNCH(LPR, VPT, ROWS) LAUNCH_AS(LPR, VPT, ROWS, false)
 #define LAUNCH_LONG(LPR, VPT, ROWS)                                  \
@@ -302,10 +338,12 @@ int masked_softmax(const T *scores, const int8_t *mask, int64_t rows, int64_t ro
 #undef LAUNCH_LONG
 #undef LAUNCH
 #undef LAUNCH_AS
+#undef LAUNCH_WITH
     } else {
         const int64_t grid = (rows + 3) / 4;
         masked_softmax_generic_kernel<T><<<(unsigned) grid, 128, 0, stream>>>(scores, mask, out, rows,
-                                                                             rows_per_batch, seq, scale);
+                                                                             rows_per_batch, seq, scale,
+                                                                             key_extents, zero_to);
     }
     return check_launch();
 }
@@ -324,6 +362,26 @@ int cubk_masked_softmax_f16(const void *scores, const int8_t *mask, int64_t rows
                             int seq, float scale, void *out, void *stream) {
     return cubk::masked_softmax<__half>((const __half *) scores, mask, rows, rows_per_batch, seq, scale,
                                         (__half *) out, (cudaStream_t) stream);
+}
+
+int cubk_masked_softmax_extents_f32(const float *scores, const int8_t *mask, const int32_t *key_extents, int zero_to,
+                                    int64_t rows, int64_t rows_per_batch, int seq, float scale, float *out,
+                                    void *stream) {
+    if (key_extents == nullptr) {
+        return CUBK_ERR_INVALID_ARG;
+    }
+    return cubk::masked_softmax<float>(scores, mask, rows, rows_per_batch, seq, scale, out, (cudaStream_t) stream,
+                                       key_extents, zero_to);
+}
+
+int cubk_masked_softmax_extents_f16(const void *scores, const int8_t *mask, const int32_t *key_extents, int zero_to,
+                                    int64_t rows, int64_t rows_per_batch, int seq, float scale, void *out,
+                                    void *stream) {
+    if (key_extents == nullptr) {
+        return CUBK_ERR_INVALID_ARG;
+    }
+    return cubk::masked_softmax<__half>((const __half *) scores, mask, rows, rows_per_batch, seq, scale,
+                                        (__half *) out, (cudaStream_t) stream, key_extents, zero_to);
 }
 
 }

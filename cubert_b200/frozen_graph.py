@@ -40,7 +40,7 @@ def _len_delimited(field, payload):
     return _key(field, 2) + _varint(len(payload)) + payload
 
 
-def _tensor_proto(arr):
+def _tensor_proto(arr, declared_shape=None):
     arr = np.ascontiguousarray(arr)
     if arr.dtype == np.float32:
         dtype = DT_FLOAT
@@ -48,29 +48,33 @@ def _tensor_proto(arr):
         dtype = DT_HALF
     else:
         raise TypeError("only float32 and float16 tensors are written, got %s" % arr.dtype)
-    shape = b"".join(_len_delimited(2, _key(1, 0) + _varint(int(d))) for d in arr.shape)
+    dims = arr.shape if declared_shape is None else declared_shape
+    shape = b"".join(_len_delimited(2, _key(1, 0) + _varint(int(d))) for d in dims)
     return dtype, (_key(1, 0) + _varint(dtype) + _len_delimited(2, shape) +
                    _len_delimited(4, arr.tobytes()))
 
 
-def _const_node(name, arr):
-    dtype, tensor = _tensor_proto(arr)
+def _const_node(name, arr, declared_shape=None):
+    dtype, tensor = _tensor_proto(arr, declared_shape)
     attr_dtype = _len_delimited(1, b"dtype") + _len_delimited(2, _key(6, 0) + _varint(dtype))
     attr_value = _len_delimited(1, b"value") + _len_delimited(2, _len_delimited(8, tensor))
     return (_len_delimited(1, name.encode()) + _len_delimited(2, b"Const") +
             _len_delimited(5, attr_dtype) + _len_delimited(5, attr_value))
 
 
-def write_frozen_graph(path, var, extra_nodes=()):
+def write_frozen_graph(path, var, extra_nodes=(), declared_shapes=None):
     """var: {TensorFlow variable name: float32/float16 array}. extra_nodes: names of
-    weight-less nodes to interleave (a real graph has many; the loader must skip them)."""
+    weight-less nodes to interleave (a real graph has many; the loader must skip them).
+    declared_shapes: {name: dims} written as the tensor's shape in place of the array's own
+    (for tests of files whose shape and content disagree)."""
+    declared_shapes = declared_shapes or {}
     with open(path, "wb") as f:
         for name in extra_nodes:
             node = _len_delimited(1, name.encode()) + _len_delimited(2, b"Identity") + \
                 _len_delimited(3, b"some/input")
             f.write(_len_delimited(1, node))
         for name, arr in var.items():
-            f.write(_len_delimited(1, _const_node(name, arr)))
+            f.write(_len_delimited(1, _const_node(name, arr, declared_shapes.get(name))))
         # GraphDef.versions = 4 { producer = 1 }: an unknown-to-the-loader field at the end
         f.write(_len_delimited(4, _key(1, 0) + _varint(27)))
 

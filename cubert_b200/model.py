@@ -62,7 +62,8 @@ _EXTENSION_API = ["cubert_b200_last_error", "cubert_b200_open", "cubert_b200_com
                   "cubert_b200_open_tokenizer", "cubert_b200_close_tokenizer", "cubert_b200_encode",
                   "cubert_b200_tokenize", "cubert_b200_tokenize_compute_m",
                   "cubert_b200_replica_device",
-                  "cubert_b200_replica_stream", "cubert_b200_forward_device", "cubert_b200_device_outputs",
+                  "cubert_b200_replica_stream", "cubert_b200_forward_device", "cubert_b200_forward_device_masked",
+                  "cubert_b200_device_outputs",
                   "cubert_b200_synchronize", "cubert_b200_profile_enable", "cubert_b200_profile_read"]
 
 
@@ -111,6 +112,8 @@ def load():
     lib.cubert_b200_replica_stream.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]
     lib.cubert_b200_forward_device.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                                C.c_void_p]
+    lib.cubert_b200_forward_device_masked.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                                      C.c_void_p, C.c_void_p]
     lib.cubert_b200_device_outputs.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(_COutput)]
     lib.cubert_b200_synchronize.argtypes = [C.c_void_p, C.c_int, C.c_int]
     lib.cubert_b200_profile_enable.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
@@ -292,10 +295,17 @@ class Model:
                                                         self._compute_type, 1 if output_to_float else 0))
 
     # ---- additions of include/cubert_b200.h -------------------------------------------------
-    def forward_device(self, replica, batch, d_ids, d_mask, d_segments):
-        """Forward pass on device-resident inputs (raw device addresses); asynchronous."""
-        _check(self._lib.cubert_b200_forward_device(self._handle, self._compute_type, replica, batch, d_ids,
-                                                    d_mask, d_segments))
+    def forward_device(self, replica, batch, d_ids, d_mask, d_segments, host_mask=None):
+        """Forward pass on device-resident inputs (raw device addresses); asynchronous. host_mask: the
+        caller's host copy of the mask (int8 numpy array), which lets the replica leave masked key columns
+        out of the attention."""
+        if host_mask is None:
+            _check(self._lib.cubert_b200_forward_device(self._handle, self._compute_type, replica, batch, d_ids,
+                                                        d_mask, d_segments))
+        else:
+            assert host_mask.dtype == np.int8 and host_mask.flags["C_CONTIGUOUS"]
+            _check(self._lib.cubert_b200_forward_device_masked(self._handle, self._compute_type, replica, batch, d_ids,
+                                                               d_mask, d_segments, host_mask.ctypes.data))
 
     def device_outputs(self, replica=0):
         c = _COutput()

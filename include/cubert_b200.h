@@ -92,6 +92,14 @@ int cubert_b200_replica_stream(void *model, int compute_type, int replica, void 
  * same replica: the caller owns the replica while it uses these two calls. */
 int cubert_b200_forward_device(void *model, int compute_type, int replica, int batch_size,
                                const int32_t *input_ids, const int8_t *input_mask, const int8_t *segment_ids);
+/* The same for a caller that also holds a HOST copy of the mask (batch_size * seq_length int8, equal to what
+ * input_mask holds on the device). The host copy tells the replica where each sequence's kept keys end, which it
+ * cannot learn from device memory without a round trip: the attention products and the softmax then leave the
+ * masked key columns past that point out (their probabilities are exactly 0), as cuBERT_compute does for host
+ * inputs. host_input_mask may be NULL (= cubert_b200_forward_device). */
+int cubert_b200_forward_device_masked(void *model, int compute_type, int replica, int batch_size,
+                                      const int32_t *input_ids, const int8_t *input_mask, const int8_t *segment_ids,
+                                      const int8_t *host_input_mask);
 int cubert_b200_device_outputs(void *model, int compute_type, int replica, struct cuBERT_Output *outputs);
 int cubert_b200_synchronize(void *model, int compute_type, int replica);
 

@@ -156,6 +156,25 @@ int cubk_masked_softmax_f32(const float *scores, const int8_t *mask, int64_t row
 int cubk_masked_softmax_f16(const void *scores, const int8_t *mask, int64_t rows, int64_t rows_per_batch,
                             int seq, float scale, void *out, void *stream);
 
+/* K4 for callers that know, per batch entry, where the kept keys end. key_extents is a device array of
+ * int32, one per batch entry: n = key_extents[b] (clamped to 1..seq) promises that mask[b*seq + j] == 0 for
+ * every j >= n and that some key below n is kept. Columns at or beyond n (rounded up to a whole 16-byte
+ * vector) are then not read; their probabilities are exactly 0, as in the full computation. Of those columns,
+ * the ones below zero_to are written as zeros, the rest are left untouched, so a consumer that multiplies
+ * only the first n columns of entry b (a batched product with k = n) can pass zero_to = 0, and one that reads
+ * a common extent E >= n passes zero_to = E; zero_to = seq gives the output of cubk_masked_softmax_*.
+ * mask must not be NULL. Moves n / seq of the bytes of the plain call. The reference has no counterpart: it
+ * computes, masks, exponentiates and multiplies every padded key (src/cuBERT/op_att/AttentionSelf.cpp:96-111,
+ * op_att/BatchMatMul.cpp:57-68,124-135).
+ * Where the two calls differ: a masked key whose scaled score exceeds the largest kept score of its row by
+ * about 9900 or more would get a non-zero probability from the plain call and gets 0 here. */
+int cubk_masked_softmax_extents_f32(const float *scores, const int8_t *mask, const int32_t *key_extents,
+                                    int zero_to, int64_t rows, int64_t rows_per_batch, int seq, float scale,
+                                    float *out, void *stream);
+int cubk_masked_softmax_extents_f16(const void *scores, const int8_t *mask, const int32_t *key_extents,
+                                    int zero_to, int64_t rows, int64_t rows_per_batch, int seq, float scale,
+                                    void *out, void *stream);
+
 /* ---- K5a: bias + tanh (BERT pooler activation) ---------------------------------------------------
  * out = tanh(x (+ bias)). Replaces tanh_<T> (src/cuBERT/op_bert/BertPooler.h:9,
  * op_bert/BertPooler.cu:14-26) plus the bias prefill of BertPooler<T>::compute

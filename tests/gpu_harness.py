@@ -64,6 +64,17 @@ def masked_softmax(scores, mask, rows_per_batch, scale=1.0, t="f32", inplace=Fal
     return out
 
 
+def masked_softmax_extents(scores, mask, extents, zero_to, rows_per_batch, scale=1.0, t="f32", out=None):
+    """As masked_softmax, with per-batch-entry key extents (torch int32 [B]); `out` defaults to a new tensor
+    filled with NaN so that untouched columns can be told apart."""
+    rows, seq = scores.shape
+    if out is None:
+        out = torch.full_like(scores, float("nan"))
+    kernels.check(fn("masked_softmax_extents", t)(ptr(scores), ptr(mask), ptr(extents), int(zero_to), rows,
+                                                  rows_per_batch, seq, float(scale), ptr(out), stream()))
+    return out
+
+
 def embed_ln(ids, seg, word, pos, typ, gamma, beta, t="f32", status=None):
     b, s = ids.shape
     vocab, hidden = word.shape

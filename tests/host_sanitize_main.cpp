@@ -1,6 +1,8 @@
 // Host-only harness for the model-file reader and the tokenizer, built by tests/test_host_sanitizers.py
 // with -fsanitize=address,undefined. It reads a list of commands from stdin, one per line:
 //   graph <float|half> <path>      open a frozen graph; prints "ok <tensors> <checksum>" or "rejected: <why>"
+//   model <float|half> <path> <seq_length> <layers> <heads>   open it and check every tensor's size against the
+//                                  geometry, as cuBERT_open does before building replicas; "ok" or "rejected: <why>"
 //   tok <lower 0|1> <vocab path> <max_seq_length> <hex of UTF-8 text>    prints "ok <ids...>" or "rejected: <why>"
 // A malformed input must end in "rejected" (a C++ exception), never in a sanitizer report or a crash.
 #include <cstdint>
@@ -40,6 +42,13 @@ void open_graph(const std::string &path) {
                 g.intermediate_size, g.num_labels);
 }
 
+template <typename T>
+void open_model(const std::string &path, size_t seq_length, size_t layers, size_t heads) {
+    cubert::FrozenGraph<T> g(path.c_str());
+    g.validate(seq_length, layers, heads);
+    std::printf("ok\n");
+}
+
 std::string unhex(const std::string &h) {
     std::string out;
     for (size_t i = 0; i + 1 < h.size(); i += 2) {
@@ -66,6 +75,15 @@ int main() {
                     open_graph<__half>(path);
                 } else {
                     open_graph<float>(path);
+                }
+            } else if (cmd == "model") {
+                std::string type, path;
+                size_t seq_length = 0, layers = 0, heads = 0;
+                in >> type >> path >> seq_length >> layers >> heads;
+                if (type == "half") {
+                    open_model<__half>(path, seq_length, layers, heads);
+                } else {
+                    open_model<float>(path, seq_length, layers, heads);
                 }
             } else if (cmd == "tok") {
                 int lower = 1;

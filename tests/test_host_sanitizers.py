@@ -79,6 +79,46 @@ def test_model_files_valid_truncated_and_corrupted(harness, tmp_path):
     assert sum(l.startswith("rejected") for l in lines) > 20     # truncated files cannot all parse
 
 
+def test_model_whose_tensor_sizes_disagree_with_its_geometry_is_rejected(harness, tmp_path):
+    """A file can parse and still be unusable: shapes that promise more elements than the content holds, a
+    sequence length beyond the position table, a head count that does not divide the hidden size, a layer
+    count beyond the file's. Each must be refused before a replica copies from the arrays."""
+    cfg = synthetic.config("tiny")
+    var = synthetic.random_weights(cfg, 3)
+    H, L, heads = cfg["hidden"], cfg["layers"], cfg["heads"]
+    good = str(tmp_path / "good.pb")
+    frozen_graph.write_frozen_graph(good, var)
+    commands = ["model float %s 16 %d %d" % (good, L, heads), "model half %s 16 %d %d" % (good, L, heads),
+                "model float %s %d %d %d" % (good, cfg["max_position"], L, heads)]
+    expect_ok = len(commands)
+    # geometry the caller gets wrong
+    commands += ["model float %s %d %d %d" % (good, cfg["max_position"] + 1, L, heads),
+                 "model float %s 16 %d %d" % (good, L + 1, heads),
+                 "model float %s 16 %d %d" % (good, L, heads + 1 if H % (heads + 1) else 7),
+                 "model float %s 0 %d %d" % (good, L, heads)]
+    # files whose declared shapes and contents disagree
+    lies = {
+        "vocab": {"bert/embeddings/word_embeddings": (cfg["vocab"] * 4, H)},
+        "hidden": {"bert/embeddings/word_embeddings": (cfg["vocab"], H * 2),
+                   "bert/embeddings/token_type_embeddings": (cfg["type_vocab"], H * 2)},
+        "inter": {"bert/encoder/layer_0/intermediate/dense/bias": (cfg["intermediate"] * 2,)},
+        "labels": {"output_weights": (cfg["num_labels"] + 3, H)},
+    }
+    for name, declared in lies.items():
+        p = str(tmp_path / ("lie_%s.pb" % name))
+        frozen_graph.write_frozen_graph(p, var, declared_shapes=declared)
+        commands.append("model float %s 16 %d %d" % (p, L, heads))
+    short = dict(var)
+    short["bert/encoder/layer_0/output/dense/kernel"] = var["bert/encoder/layer_0/output/dense/kernel"][:-1]
+    p = str(tmp_path / "short.pb")
+    frozen_graph.write_frozen_graph(p, short)
+    commands.append("model half %s 16 %d %d" % (p, L, heads))
+    lines = run(harness, commands)
+    assert len(lines) == len(commands)
+    assert all(l == "ok" for l in lines[:expect_ok]), lines[:expect_ok]
+    assert all(l.startswith("rejected: ") and "invalid" in l for l in lines[expect_ok:]), lines[expect_ok:]
+
+
 def test_tokenizer_on_valid_and_malformed_text(harness, tmp_path):
     vocab = ["[PAD]", "[UNK]", "[CLS]", "[SEP]", "hello", "world", "##s", "un", "##aff", "##able", "!", ",", "中", "文",
              "e", "cafe", "é"]

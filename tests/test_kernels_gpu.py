@@ -290,6 +290,48 @@ def test_masked_softmax(oracle, t, kind, batch, heads, seq, mask_terms, kernel_o
     assert torch.equal(got, got2)
 
 
+@pytest.mark.parametrize("zero_to", ["own", "common", "full"])
+@pytest.mark.parametrize("t", DTYPES)
+@pytest.mark.parametrize("batch,heads,seq", [(6, 3, 128), (3, 2, 512), (5, 2, 32), (4, 2, 64), (3, 1, 37), (2, 1, 1024),
+                                             (3, 2, 2056), (70, 2, 128)])
+def test_masked_softmax_with_key_extents(t, batch, heads, seq, zero_to):
+    """The call that is told where each sequence's kept keys end: below the extent it must equal the plain call
+    bit for bit (the columns it skips contribute exact zeros there), from the extent up to zero_to it writes
+    zeros, and beyond that it touches nothing."""
+    rng = np.random.default_rng(batch * 131 + seq)
+    vector_path = seq % 8 == 0 and seq // (4 if t == "f32" else 8) <= 256
+    step = 32 if vector_path and seq >= 32 else 1
+    x, _ = _prep(rng.standard_normal((batch, seq, heads, seq)) * 3, t)
+    lengths = rng.integers(1, seq + 1, batch)
+    lengths[0] = seq                      # a full sequence
+    lengths[-1] = 1                       # and one with a single kept key
+    mask = np.zeros((batch, seq), np.int8)
+    for b, n in enumerate(lengths):
+        mask[b, :n] = rng.integers(0, 2, n) * 5     # any non-zero value keeps
+        mask[b, n - 1] = 1                          # the last kept key sits at n - 1
+    extents = np.minimum((lengths + step - 1) // step * step, seq).astype(np.int32)
+    common = int(extents.max())
+    z = {"own": 0, "common": common, "full": seq}[zero_to]
+    plain = G.masked_softmax(x.view(-1, seq), G.dev(mask), seq * heads, 0.125, t).view(batch, seq, heads, seq)
+    got = G.masked_softmax_extents(x.view(-1, seq), G.dev(mask), G.dev(extents), z, seq * heads, 0.125, t)
+    got = got.view(batch, seq, heads, seq)
+    for b in range(batch):
+        n, w = int(extents[b]), max(int(extents[b]), z)
+        assert torch.equal(got[b, :, :, :n], plain[b, :, :, :n]), (b, n)
+        assert bool((got[b, :, :, n:w] == 0).all()) and bool((plain[b, :, :, n:w] == 0).all())
+        assert bool(torch.isnan(got[b, :, :, w:]).all()), (b, w)
+    # in place
+    again = x.clone().view(-1, seq)
+    G.masked_softmax_extents(again, G.dev(mask), G.dev(extents), seq, seq * heads, 0.125, t, out=again)
+    assert torch.equal(again.view(batch, seq, heads, seq), plain)
+    lib = kernels.load()
+    f = getattr(lib, "cubk_masked_softmax_extents_" + t)
+    assert f(x.data_ptr(), G.dev(mask).data_ptr(), None, 0, batch * seq * heads, seq * heads, seq, 1.0, x.data_ptr(),
+             G.stream()) == kernels.CUBK_ERR_INVALID_ARG
+    assert f(x.data_ptr(), None, G.dev(extents).data_ptr(), 0, batch * seq * heads, seq * heads, seq, 1.0,
+             x.data_ptr(), G.stream()) == kernels.CUBK_ERR_INVALID_ARG
+
+
 # ============================================================================ K1 embedding + add + LayerNorm
 
 def _choose_embed_kernel(kernel_options, which):

@@ -367,7 +367,8 @@ def test_padding_is_skipped_without_changing_the_results(model_files, oracle, ct
     prof = m.profile_read()
     m.profile_enable(False)
     kept = int(np.count_nonzero(mask[:, 1:])) + B
-    rows = (kept + 63) // 64 * 64
+    step = max(64, (B * S // 16 + 63) // 64 * 64)      # packed lengths come in sixteenths of the request
+    rows = (kept + step - 1) // step * step
     assert rows < B * S
     e = 4 if ct == model.ComputeType.FLOAT else 2
     # packed rows in every layer but the last, which runs on the B first tokens only
@@ -385,6 +386,115 @@ def test_padding_is_skipped_without_changing_the_results(model_files, oracle, ct
         ref = oracle.bert_forward(var, synthetic.model_geometry(cfg, S), ids, mask, seg)
         for k in ("pooled_output", "logits", "probs"):
             assert rel_err(getattr(packed, k), ref[k]) < 1e-5, k
+    m.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ct", [model.ComputeType.FLOAT, model.ComputeType.HALF])
+def test_a_sequence_without_any_kept_key_is_not_packed(model_files, oracle, ct):
+    """A mask row of zeros (the empty rows that fill a fixed batch): the reference gives every key of that
+    sequence the same -10000, i.e. uniform attention over ALL its positions, so none may be dropped. The
+    request must give what the full pass gives, also right after a different request has left its rows in
+    the replica's buffers."""
+    path, cfg, var = model_files["small"]
+    B, S = 64, 32
+    rng = np.random.default_rng(29)
+    ids, full_mask, seg, _ = synthetic.random_inputs(cfg, B, S, 29, lengths="full", segments="random")
+    ids2, _, seg2, _ = synthetic.random_inputs(cfg, B, S, 31, segments="random")
+    mask = np.zeros((B, S), np.int8)
+    for b in range(B):
+        mask[b, :rng.integers(2, 9)] = 1
+    mask[7, :] = 0
+    mask[40, :] = 0
+    dt = np.float32 if ct == model.ComputeType.FLOAT else np.float16
+    m = model.Model(path, B, S, cfg["layers"], cfg["heads"], ct)
+    full = _run(m, ids2, mask, seg2, cfg)          # every position computed: the answer to match
+    _run(m, ids, full_mask, seg, cfg)              # a different request: its rows stay behind in the buffers
+    out = model.Output()
+    out.pooled_output = np.zeros((B, cfg["hidden"]), dt)
+    out.probs = np.zeros((B, 2), dt)
+    m.compute_m(ids2, mask, seg2, out)             # pooled outputs only: the request that may skip padding
+    tol = 1e-5 if ct == model.ComputeType.FLOAT else 4e-3
+    assert rel_err(out.pooled_output, full["pooled_output"]) < tol
+    assert rel_err(out.probs, full["probs"]) < tol
+    if ct == model.ComputeType.FLOAT:
+        ref = oracle.bert_forward(var, synthetic.model_geometry(cfg, S), ids2, mask, seg2)
+        assert rel_err(out.pooled_output, ref["pooled_output"]) < 1e-5
+    m.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ct", [model.ComputeType.FLOAT, model.ComputeType.HALF])
+@pytest.mark.parametrize("batch", [24, 130])     # 130 x 128 positions: per-position outputs leave in sub-batches
+def test_masked_key_columns_are_left_out_of_the_attention(model_files, oracle, ct, batch, monkeypatch):
+    """With the mask visible on the host, the attention products and the softmax work only on the key columns
+    below each sequence's last kept key (rounded up to 32). Those columns carry probability exactly 0 in the
+    full computation, so every output must be what the library gives with the feature off -- for ragged
+    prefixes, masks with holes, a full sequence, a sequence without any kept key -- eagerly, captured and
+    replayed, for per-position requests, pooled-only requests and device-resident inputs."""
+    import torch
+    path, cfg, var = model_files["small"]
+    S = 128
+    rng = np.random.default_rng(41 + batch)
+    ids, mask, seg, _ = synthetic.random_inputs(cfg, batch, S, 41, lengths=(1, S), segments="random")
+    mask[0, :] = 1                                   # a full sequence
+    mask[1, :] = 0                                   # no kept key at all: uniform attention over every position
+    mask[2, :] = 0
+    mask[2, [3, 40, 77]] = [1, 9, -3]                # holes; any non-zero value keeps
+    mask[3, :] = 0
+    mask[3, 0] = 1                                   # a single kept key
+    dt = np.float32 if ct == model.ComputeType.FLOAT else np.float16
+    tol = 1e-5 if ct == model.ComputeType.FLOAT else 4e-3
+
+    monkeypatch.setenv("CUBERT_SKIP_MASKED_KEYS", "0")
+    plain = model.Model(path, batch, S, cfg["layers"], cfg["heads"], ct)
+    want = _run(plain, ids, mask, seg, cfg)
+    mask_b = mask.copy()
+    mask_b[1, 5] = 1                                 # every sequence keeps a key: pooled-only requests get packed
+    want_b = _run(plain, ids, mask_b, seg, cfg)
+    plain.close()
+    monkeypatch.delenv("CUBERT_SKIP_MASKED_KEYS")
+
+    m = model.Model(path, batch, S, cfg["layers"], cfg["heads"], ct)
+    for _ in range(3):                               # eager, captured, replayed
+        got = _run(m, ids, mask, seg, cfg)
+        for k, ref in want.items():
+            assert rel_err(got[k], ref) < tol, (k, rel_err(got[k], ref))
+    # K4 moved only the kept key columns
+    m.profile_read()
+    m.profile_enable(True)
+    _run(m, ids, mask, seg, cfg)
+    prof = m.profile_read()
+    m.profile_enable(False)
+    last = np.where(mask.any(axis=1), S - np.argmax(mask[:, ::-1] != 0, axis=1), S)
+    extents = np.minimum((last + 31) // 32 * 32, S)
+    e = 4 if ct == model.ComputeType.FLOAT else 2
+    assert prof["masked_softmax"]["bytes"] == cfg["layers"] * (2 * int(extents.sum()) * S * cfg["heads"] * e + batch * S)
+    assert int(extents.sum()) < 0.9 * batch * S
+    # pooled outputs only (padding rows skipped as well)
+    for _ in range(3):
+        out = model.Output()
+        out.pooled_output = np.zeros((batch, cfg["hidden"]), dt)
+        out.probs = np.zeros((batch, 2), dt)
+        m.compute_m(ids, mask_b, seg, out)
+        assert rel_err(out.pooled_output, want_b["pooled_output"]) < tol
+        assert rel_err(out.probs, want_b["probs"]) < tol
+    # a different request in between, then inputs resident on the device with the host's copy of the mask
+    ids2, mask2, seg2, _ = synthetic.random_inputs(cfg, batch, S, 43, lengths=(90, S))
+    _run(m, ids2, mask2, seg2, cfg)
+    d_ids, d_mask, d_seg = (torch.from_numpy(a).cuda() for a in (ids, mask, seg))
+    torch.cuda.synchronize()
+    import gpu_harness as G
+    for host_mask in (mask, None, mask):
+        m.forward_device(0, batch, d_ids.data_ptr(), d_mask.data_ptr(), d_seg.data_ptr(), host_mask=host_mask)
+        m.synchronize(0)
+        ptrs = m.device_outputs(0)
+        seq_out = G.copy_from_device(ptrs["sequence_output"], (batch, S, cfg["hidden"]), dt)
+        assert rel_err(seq_out, want["sequence_output"]) < tol
+    if ct == model.ComputeType.FLOAT:
+        truth = oracle.bert_forward(var, synthetic.model_geometry(cfg, S), ids, mask, seg)
+        for k in ("sequence_output", "pooled_output", "probs"):
+            assert rel_err(got[k], truth[k]) < 1e-5, (k, rel_err(got[k], truth[k]))
     m.close()
 
 

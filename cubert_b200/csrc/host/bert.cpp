@@ -27,6 +27,7 @@ struct K<float> {
     static constexpr auto bias_tanh = cubk_bias_tanh_f32;
     static constexpr auto mean_pool = cubk_mean_pool_f32;
     static constexpr auto logits_probs = cubk_logits_probs_f32;
+    static constexpr auto pooler_head = cubk_pooler_head_f32;
 };
 
 template <>
@@ -39,6 +40,7 @@ struct K<__half> {
     static constexpr auto bias_tanh = cubk_bias_tanh_f16;
     static constexpr auto mean_pool = cubk_mean_pool_f16;
     static constexpr auto logits_probs = cubk_logits_probs_f16;
+    static constexpr auto pooler_head = cubk_pooler_head_f16;
 };
 
 template <typename T>
@@ -176,6 +178,13 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
         probs_.allocate(sizeof(T) * B * num_labels);
     }
 
+    // first-token pooler + a small classifier: K5a and K5c run as one launch (cubk_pooler_head_*)
+    {
+        const size_t epv = 16 / sizeof(T);
+        fuse_heads_ = has_pooler_dense_ && has_classifier_ && num_labels <= 8 && H % epv == 0 && H / epv <= 512 &&
+                      env_int("CUBERT_FUSE_HEADS", 1) != 0;
+    }
+
     // ---- inputs, activations
     {
         const size_t mask_at = (sizeof(int32_t) * R + 15) / 16 * 16, seg_at = mask_at + (R + 15) / 16 * 16;
@@ -251,6 +260,20 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
         // extents in steps of 32 keys, or of an eighth of the sequence when that is more (at most 8 groups)
         key_granule_ = (int) ((S / 8 + 31) / 32 * 32);
         key_granule_ = key_granule_ < 32 ? 32 : key_granule_;
+        const int forced_granule = env_int("CUBERT_KEY_GRANULE", 0);
+        if (forced_granule >= 8 && forced_granule % 8 == 0) {
+            key_granule_ = forced_granule;
+        }
+        key_group_gemms_ = env_int("CUBERT_KEY_GEMM", 1) != 0;
+        key_group_mode_ = env_int("CUBERT_KEY_GROUP_MODE", 0);
+        if (key_group_mode_ == 1) {
+            CUDA_CHECK(cudaEventCreateWithFlags(&fork_, cudaEventDisableTiming));
+            for (int i = 0; i < kSideStreams; ++i) {
+                CUDA_CHECK(cudaStreamCreateWithFlags(&side_stream_[i], cudaStreamNonBlocking));
+                CUDA_CHECK(cudaEventCreateWithFlags(&join_[i], cudaEventDisableTiming));
+                side_blas_[i].reset(new Blas(side_stream_[i], 0, (size_t) 8 << 20));
+            }
+        }
         seq_extent_.assign(B, (int32_t) S);
         CUDA_CHECK(cudaMallocHost(reinterpret_cast<void **>(&h_plan_), sizeof(int32_t) * 2 * B));
         plan_dev_.allocate(sizeof(int32_t) * 2 * B);
@@ -317,6 +340,19 @@ Bert<T>::~Bert() {
     }
     if (staging_read_ != nullptr) {
         cudaEventDestroy(staging_read_);
+    }
+    for (int i = 0; i < kSideStreams; ++i) {
+        side_blas_[i].reset();
+        if (side_stream_[i] != nullptr) {
+            cudaStreamSynchronize(side_stream_[i]);
+            cudaStreamDestroy(side_stream_[i]);
+        }
+        if (join_[i] != nullptr) {
+            cudaEventDestroy(join_[i]);
+        }
+    }
+    if (fork_ != nullptr) {
+        cudaEventDestroy(fork_);
     }
     if (h_plan_ != nullptr) {
         cudaFreeHost(h_plan_);
@@ -542,6 +578,57 @@ void Bert<T>::sort_attention_pointers(size_t batch_size) {
     for (int i = 0; i < 5; ++i) {
         KERNEL_CHECK(cubk_embed_gather_i32(order, (int64_t) batch_size, from[i]->get(), (int) max_batch_size, 2 * heads, 4,
                                            to[i]->get(), nullptr, stream_));
+    }
+}
+
+// The two attention products of a whole batch, one per group of equal key extent, over the sorted pointer
+// arrays: scores (keys x queries, k = d) or context (d x queries, k = keys).
+template <typename T>
+void Bert<T>::grouped_products(bool scores_product, int S, int d, int heads, int H, float alpha, int algo) {
+    const T *const *a = scores_product ? k_sorted_.template as<const T *>() : v_sorted_.template as<const T *>();
+    const T *const *b = scores_product ? q_sorted_.template as<const T *>() : score_sorted_.template as<const T *>();
+    T *const *c = scores_product ? score_sorted_.template as<T *>() : ctx_sorted_.template as<T *>();
+    const int lda = 3 * H, ldb = scores_product ? 3 * H : S * heads, ldc = scores_product ? S * heads : H;
+    auto one = [&](Blas &blas, int g) {
+        const size_t at = (size_t) plan_.start[g] * heads;
+        const int count = (plan_.start[g + 1] - plan_.start[g]) * heads;
+        if (scores_product) {
+            blas.gemm_batched<T>(true, false, plan_.extent[g], S, d, alpha, a + at, lda, b + at, ldb, 0.f, c + at, ldc, count, algo);
+        } else {
+            blas.gemm_batched<T>(false, false, d, S, plan_.extent[g], alpha, a + at, lda, b + at, ldb, 0.f, c + at, ldc, count,
+                                 algo);
+        }
+    };
+    if (key_group_mode_ == 2) {
+        int m[kMaxKeyGroups], n[kMaxKeyGroups], k[kMaxKeyGroups], count[kMaxKeyGroups];
+        for (int g = 0; g < plan_.groups; ++g) {
+            m[g] = scores_product ? plan_.extent[g] : d;
+            n[g] = S;
+            k[g] = scores_product ? d : plan_.extent[g];
+            count[g] = (plan_.start[g + 1] - plan_.start[g]) * heads;
+        }
+        blas_->gemm_grouped<T>(scores_product, false, plan_.groups, m, n, k, alpha, a, lda, b, ldb, 0.f, c, ldc, count);
+        return;
+    }
+    if (key_group_mode_ == 1 && plan_.groups > 1) {
+        CUDA_CHECK(cudaEventRecord(fork_, stream_));
+        const int used = plan_.groups - 1 < kSideStreams ? plan_.groups - 1 : kSideStreams;
+        for (int i = 0; i < used; ++i) {
+            CUDA_CHECK(cudaStreamWaitEvent(side_stream_[i], fork_, 0));
+        }
+        // the largest group (the last) on the replica's own stream, the others dealt round the side streams
+        for (int g = 0; g + 1 < plan_.groups; ++g) {
+            one(*side_blas_[g % kSideStreams], g);
+        }
+        one(*blas_, plan_.groups - 1);
+        for (int i = 0; i < used; ++i) {
+            CUDA_CHECK(cudaEventRecord(join_[i], side_stream_[i]));
+            CUDA_CHECK(cudaStreamWaitEvent(stream_, join_[i], 0));
+        }
+        return;
+    }
+    for (int g = 0; g < plan_.groups; ++g) {
+        one(*blas_, g);
     }
 }
 
@@ -783,8 +870,8 @@ void Bert<T>::forward_layers(size_t l_begin, size_t l_end, size_t b0, size_t nb,
     const size_t p0 = b0 * (size_t) heads;  // first entry of the range in the pointer arrays
 
     // key columns the attention works on (see KeyPlan)
-    const bool grouped = plan_.active && b0 == 0 && nb == batch_size;
-    const int keys = plan_.active && !grouped ? range_extent(b0, nb) : S;
+    const bool grouped = plan_.active && key_group_gemms_ && b0 == 0 && nb == batch_size;
+    const int keys = plan_.active && key_group_gemms_ && !grouped ? range_extent(b0, nb) : S;
     const int32_t *extents = plan_.active ? plan_dev_.template as<int32_t>() + max_batch_size + b0 : nullptr;
     int64_t key_columns = R;   // sum over the range's sequences of the key columns K4 moves
     if (plan_.active) {
@@ -816,13 +903,7 @@ void Bert<T>::forward_layers(size_t l_begin, size_t l_end, size_t b0, size_t nb,
         // of equal extent over the sorted pointer arrays, or (a range of sequences) the range's largest extent.
         begin(CUBERT_B200_K_GEMM);
         if (grouped) {
-            for (int g = 0; g < plan_.groups; ++g) {
-                const size_t at = (size_t) plan_.start[g] * heads;
-                const int count = (plan_.start[g + 1] - plan_.start[g]) * heads;
-                blas_->gemm_batched<T>(true, false, plan_.extent[g], S, d, att_scale, k_sorted_.template as<const T *>() + at,
-                                       3 * H, q_sorted_.template as<const T *>() + at, 3 * H, 0.f,
-                                       score_sorted_.template as<T *>() + at, S * heads, count, algo_qk_);
-            }
+            grouped_products(true, S, d, heads, H, att_scale, algo_qk_);
         } else {
             blas_->gemm_batched<T>(true, false, keys, S, d, att_scale, k_ptrs_.template as<const T *>() + p0, 3 * H,
                                    q_ptrs_.template as<const T *>() + p0, 3 * H, 0.f, score_ptrs_.template as<T *>() + p0,
@@ -843,13 +924,7 @@ void Bert<T>::forward_layers(size_t l_begin, size_t l_end, size_t b0, size_t nb,
         // context[b, i, h, c] = sum_j V[b,j,h,c] * P[b,i,h,j]   (op_att/BatchMatMul.cpp:124-135)
         begin(CUBERT_B200_K_GEMM);
         if (grouped) {
-            for (int g = 0; g < plan_.groups; ++g) {
-                const size_t at = (size_t) plan_.start[g] * heads;
-                const int count = (plan_.start[g + 1] - plan_.start[g]) * heads;
-                blas_->gemm_batched<T>(false, false, d, S, plan_.extent[g], 1.f, v_sorted_.template as<const T *>() + at, 3 * H,
-                                       score_sorted_.template as<const T *>() + at, S * heads, 0.f,
-                                       ctx_sorted_.template as<T *>() + at, H, count, algo_qkv_);
-            }
+            grouped_products(false, S, d, heads, H, 1.f, algo_qkv_);
         } else {
             blas_->gemm_batched<T>(false, false, d, S, keys, 1.f, v_ptrs_.template as<const T *>() + p0, 3 * H,
                                    score_ptrs_.template as<const T *>() + p0, S * heads, 0.f, ctx_ptrs_.template as<T *>() + p0,
@@ -999,8 +1074,17 @@ void Bert<T>::forward_heads(size_t batch_size, const int8_t *d_mask, size_t pack
                        algo_pooler_);
         end(CUBERT_B200_K_GEMM, 0);
         begin(CUBERT_B200_K_BIAS_TANH);
-        KERNEL_CHECK(K<T>::bias_tanh(pooled_.template as<T>(), pooler_bias_.template as<T>(), B, H, pooled_.template as<T>(), st));
-        end(CUBERT_B200_K_BIAS_TANH, 2 * (int64_t) B * H * e + H * e);
+        if (fuse_heads_) {
+            // pooler activation and classifier in one launch (counted with the pooler activation)
+            KERNEL_CHECK(K<T>::pooler_head(pooled_.template as<T>(), pooler_bias_.template as<T>(), output_weights_.template as<T>(),
+                                           has_classifier_bias_ ? output_bias_.template as<T>() : nullptr, B, H, (int) num_labels,
+                                           pooled_.template as<T>(), logits_.template as<T>(), probs_.template as<T>(), st));
+            end(CUBERT_B200_K_BIAS_TANH, 2 * (int64_t) B * H * e + H * e + (int64_t) num_labels * H * e +
+                                             2 * (int64_t) B * num_labels * e);
+        } else {
+            KERNEL_CHECK(K<T>::bias_tanh(pooled_.template as<T>(), pooler_bias_.template as<T>(), B, H, pooled_.template as<T>(), st));
+            end(CUBERT_B200_K_BIAS_TANH, 2 * (int64_t) B * H * e + H * e);
+        }
     } else {
         begin(CUBERT_B200_K_MEAN_POOL);
         KERNEL_CHECK(K<T>::mean_pool(x, B, S, H, pooled_.template as<T>(), pool_scratch_.get(), pool_scratch_.bytes(), st));
@@ -1014,7 +1098,7 @@ void Bert<T>::forward_heads(size_t batch_size, const int8_t *d_mask, size_t pack
         end(CUBERT_B200_K_EVENT_OVERHEAD, 0);
     }
 
-    if (has_classifier_) {
+    if (has_classifier_ && !(fuse_heads_ && has_pooler_dense_)) {
         begin(CUBERT_B200_K_LOGITS_PROBS);
         KERNEL_CHECK(K<T>::logits_probs(pooled_.template as<T>(), output_weights_.template as<T>(),
                                         has_classifier_bias_ ? output_bias_.template as<T>() : nullptr, B, H,

@@ -149,6 +149,7 @@ private:
     bool has_pooler_dense_ = false;
     bool has_classifier_ = false;
     bool has_classifier_bias_ = false;
+    bool fuse_heads_ = false;
 
     // weights
     DeviceBuffer word_emb_, type_emb_, pos_emb_, emb_ln_gamma_, emb_ln_beta_;
@@ -205,6 +206,17 @@ private:
     void build_key_plan(size_t batch_size, const int8_t *input_mask);
     void sort_attention_pointers(size_t batch_size);   // device side of the plan; part of the forward pass
     int range_extent(size_t b0, size_t nb) const;
+    // how the per-group products are issued: 0 = one after the other on the replica's stream, 1 = the groups
+    // side by side on side streams (forked and joined with events, branches of the graph when captured),
+    // 2 = one grouped library call (cublasGemmGroupedBatchedEx)
+    int key_group_mode_ = 0;
+    bool key_group_gemms_ = true;            // false: the products keep every key column, only K4 uses the extents
+    static constexpr int kSideStreams = 3;
+    cudaStream_t side_stream_[kSideStreams] = {};
+    std::unique_ptr<Blas> side_blas_[kSideStreams];
+    cudaEvent_t fork_ = nullptr, join_[kSideStreams] = {};
+    // op(A) * op(B) per group: `fixed` is the dimension that does not depend on the group (queries)
+    void grouped_products(bool scores_product, int S, int d, int heads, int H, float alpha, int algo);
     cudaEvent_t staging_read_ = nullptr;     // after the last copy out of the pinned staging buffers
     bool staging_in_flight_ = false;
     void wait_for_staging();

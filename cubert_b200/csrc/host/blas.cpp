@@ -16,13 +16,13 @@ int gemm_algo_from_env(const char *env, bool half) {
     return std::atoi(val);
 }
 
-Blas::Blas(cudaStream_t stream, size_t fp32_emulation_workspace) : stream_(stream) {
+Blas::Blas(cudaStream_t stream, size_t fp32_emulation_workspace, size_t workspace_bytes) : stream_(stream) {
     CUBLAS_CHECK(cublasCreate(&handle_));
     CUBLAS_CHECK(cublasSetStream(handle_, stream_));
     CUBLAS_CHECK(cublasLtCreate(&lt_));
     // float32 storage must not be demoted to TF32
     CUBLAS_CHECK(cublasSetMathMode(handle_, CUBLAS_DEFAULT_MATH));
-    size_t bytes = kWorkspaceBytes;
+    size_t bytes = workspace_bytes > 0 ? workspace_bytes : kWorkspaceBytes;
     if (fp32_emulation_workspace > 0 && env_int("CUBERT_FP32_EMULATION", 1) != 0) {
         // A cuBLAS older than 12.9 refuses the mode and the products stay on the float32 pipes.
         fp32_emulation_ = cublasSetMathMode(handle_, CUBLAS_FP32_EMULATED_BF16X9_MATH) == CUBLAS_STATUS_SUCCESS;
@@ -75,6 +75,33 @@ void Blas::gemm_batched(bool trans_a, bool trans_b, int m, int n, int k, float a
                                      reinterpret_cast<const void *const *>(B), dt, ldb, &beta,
                                      reinterpret_cast<void *const *>(C), dt, ldc, batch, CUBLAS_COMPUTE_32F,
                                      (cublasGemmAlgo_t) algo));
+}
+
+template <typename T>
+void Blas::gemm_grouped(bool trans_a, bool trans_b, int groups, const int *m, const int *n, const int *k, float alpha,
+                        const T *const *A, int lda, const T *const *B, int ldb, float beta, T *const *C, int ldc,
+                        const int *count) {
+    constexpr int kMax = 32;
+    if (groups <= 0 || groups > kMax) {
+        throw std::invalid_argument("gemm_grouped: group count");
+    }
+    constexpr cudaDataType_t dt = Storage<T>::cuda_type;
+    cublasOperation_t ta[kMax], tb[kMax];
+    int lda_v[kMax], ldb_v[kMax], ldc_v[kMax];
+    float alpha_v[kMax], beta_v[kMax];
+    for (int g = 0; g < groups; ++g) {
+        ta[g] = trans_a ? CUBLAS_OP_T : CUBLAS_OP_N;
+        tb[g] = trans_b ? CUBLAS_OP_T : CUBLAS_OP_N;
+        lda_v[g] = lda;
+        ldb_v[g] = ldb;
+        ldc_v[g] = ldc;
+        alpha_v[g] = alpha;
+        beta_v[g] = beta;
+    }
+    CUBLAS_CHECK(cublasGemmGroupedBatchedEx(handle_, ta, tb, m, n, k, alpha_v, reinterpret_cast<const void *const *>(A), dt,
+                                            lda_v, reinterpret_cast<const void *const *>(B), dt, ldb_v, beta_v,
+                                            reinterpret_cast<void *const *>(C), dt, ldc_v, groups, count,
+                                            CUBLAS_COMPUTE_32F));
 }
 
 template <typename T>
@@ -145,6 +172,9 @@ void Blas::gemm_bias(int m, int n, int k, const T *A, int lda, const T *B, int l
                                 int);                                                                               \
     template void Blas::gemm_batched<T>(bool, bool, int, int, int, float, const T *const *, int, const T *const *,  \
                                         int, float, T *const *, int, int, int);                                     \
+    template void Blas::gemm_grouped<T>(bool, bool, int, const int *, const int *, const int *, float,              \
+                                        const T *const *, int, const T *const *, int, float, T *const *, int,       \
+                                        const int *);                                                               \
     template void Blas::gemm_bias<T>(int, int, int, const T *, int, const T *, int, const T *, T *, int);
 
 INSTANTIATE(float)

@@ -26,7 +26,7 @@ public:
     // tensor-core products of operands split three ways (cuBLAS 12.9 "BF16x9", results as accurate as
     // float32 arithmetic), which needs that much workspace for the split operands. Off with
     // CUBERT_FP32_EMULATION=0 or an older cuBLAS. CUBERT_BLAS_WORKSPACE_MB overrides the size.
-    explicit Blas(cudaStream_t stream, size_t fp32_emulation_workspace = 0);
+    explicit Blas(cudaStream_t stream, size_t fp32_emulation_workspace = 0, size_t workspace_bytes = 0);
     bool fp32_emulation() const { return fp32_emulation_; }
     ~Blas();
     Blas(const Blas &) = delete;
@@ -41,6 +41,14 @@ public:
     template <typename T>
     void gemm_batched(bool trans_a, bool trans_b, int m, int n, int k, float alpha, const T *const *A, int lda,
                       const T *const *B, int ldb, float beta, T *const *C, int ldc, int batch, int algo);
+
+    // `groups` pointer-array batched products of different shapes in one library call
+    // (cublasGemmGroupedBatchedEx): group g multiplies count[g] consecutive entries of the pointer arrays
+    // with (m[g], n[g], k[g]); transposition, leading dimensions, alpha and beta are common to all.
+    template <typename T>
+    void gemm_grouped(bool trans_a, bool trans_b, int groups, const int *m, const int *n, const int *k, float alpha,
+                      const T *const *A, int lda, const T *const *B, int ldb, float beta, T *const *C, int ldc,
+                      const int *count);
 
     // C = A * B + bias (bias of length m broadcast over the n columns), through the cuBLASLt
     // bias epilogue. Used where no fused kernel follows the product (the Q/K/V projection).

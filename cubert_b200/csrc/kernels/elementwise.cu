@@ -42,6 +42,15 @@ struct GeluCoef<10> {
     }
 };
 
+// max(x, 0) that hands a NaN on (fmaxf would return 0 for it): a NaN that reaches the activation, say
+// from a binary16 overflow in the product before it, stays visible in the output as it does in the
+// reference's x * 0.5 * (1 + erf(..)).
+__device__ __forceinline__ float relu_keep_nan(float x) {
+    float y;
+    asm("max.NaN.f32 %0, %1, 0f00000000;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <int DEG>
 struct GeluTailFit {
     __device__ __forceinline__ float2 operator()(float2 x) const {
@@ -52,7 +61,7 @@ struct GeluTailFit {
             p = fma2(p, w, splat2(GeluCoef<DEG>::c(k)));
         }
         const float2 q = make_float2(fast_exp2(p.x), fast_exp2(p.y));
-        return fma2(w, q, make_float2(fmaxf(x.x, 0.f), fmaxf(x.y, 0.f)));
+        return fma2(w, q, make_float2(relu_keep_nan(x.x), relu_keep_nan(x.y)));
     }
 };
 

@@ -3,6 +3,8 @@
 //
 // These touch at most a few MB per call and are latency-bound, except the mean pooler on
 // long sequences ([batch, 512, 1024] is 1 MB per sequence), which is a streaming read.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace cubk {
@@ -11,18 +13,23 @@ namespace cubk {
 // Block = (32 column vectors) x (BY sequence lanes). Each thread sums every BY-th position
 // of its 16-byte column vector inside the block's slice of the sequence; the BY partial sums
 // are combined through shared memory. With `splits` > 1 the slices of one sequence go to
-// different blocks, which leave float32 partial sums in scratch [batch, splits, hidden] for
-// mean_pool_finish_kernel; that keeps every SM busy when batch * hidden alone is too small
-// a grid.
+// different blocks, which keeps every SM busy when batch * hidden alone is too small a grid:
+// each block leaves its float32 partial sums in scratch [batch, splits, hidden] and takes a
+// ticket from a counter per (sequence, column block); the block that draws the last ticket adds
+// the slices up, always in slice order (so the result does not depend on which block came last),
+// and writes the means. Nobody waits for anybody. The counters sit behind the partial sums in
+// scratch and are cleared by a memset node in front of the kernel.
 constexpr int kPoolBX = 32;
 constexpr int kPoolBY = 8;
 constexpr int kPoolUnroll = 4;
 
 template <typename T>
 __global__ void __launch_bounds__(kPoolBX *kPoolBY)
-mean_pool_kernel(const T *x, T *out, float *partial, int seq, int hidden, int nvec, int splits, int chunk) {
+mean_pool_kernel(const T *x, T *out, float *partial, unsigned int *tickets, int seq, int hidden, int nvec, int splits,
+                 int chunk) {
     constexpr int EPV = Vec<T>::EPV;
     __shared__ float smem[kPoolBY][kPoolBX][EPV + 1];
+    __shared__ unsigned int s_ticket;
 
     const int cv = blockIdx.x * kPoolBX + threadIdx.x;
     const int split = blockIdx.y;
@@ -60,7 +67,8 @@ mean_pool_kernel(const T *x, T *out, float *partial, int seq, int hidden, int nv
         smem[threadIdx.y][threadIdx.x][e] = acc[e];
     }
     __syncthreads();
-    if (threadIdx.y == 0 && cv < nvec) {
+    const bool writer = threadIdx.y == 0 && cv < nvec;
+    if (writer) {
 #pragma unroll
         for (int e = 0; e < EPV; ++e) {
             float t = 0.f;
@@ -70,36 +78,52 @@ mean_pool_kernel(const T *x, T *out, float *partial, int seq, int hidden, int nv
             }
             acc[e] = t;
         }
-        if (splits == 1) {
-            T *dst = out + (size_t) b * hidden + (size_t) cv * EPV;
+    }
+    if (splits > 1) {
+        if (writer) {
+            float4 *dst = reinterpret_cast<float4 *>(partial + ((size_t) b * splits + split) * hidden + (size_t) cv * EPV);
 #pragma unroll
-            for (int e = 0; e < EPV; ++e) {
-                dst[e] = from_float<T>(acc[e] / (float) seq);
+            for (int q = 0; q < EPV / 4; ++q) {
+                dst[q] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
             }
-        } else {
-            float *dst = partial + ((size_t) b * splits + split) * hidden + (size_t) cv * EPV;
+            __threadfence();  // this thread's partial sums are visible before the block's ticket is drawn
+        }
+        __syncthreads();
+        if (threadIdx.x == 0 && threadIdx.y == 0) {
+            s_ticket = atomicAdd(&tickets[(size_t) b * gridDim.x + blockIdx.x], 1u);
+        }
+        __syncthreads();
+        if (s_ticket != (unsigned int) splits - 1) {
+            return;  // other slices of this sequence are still on their way; the last one finishes
+        }
+        __threadfence();
+        if (writer) {
 #pragma unroll
             for (int e = 0; e < EPV; ++e) {
-                dst[e] = acc[e];
+                acc[e] = 0.f;
+            }
+            for (int k = 0; k < splits; ++k) {
+                const float4 *src =
+                    reinterpret_cast<const float4 *>(partial + ((size_t) b * splits + k) * hidden + (size_t) cv * EPV);
+#pragma unroll
+                for (int q = 0; q < EPV / 4; ++q) {
+                    const float4 f = __ldcg(src + q);  // from L2: written by other SMs
+                    acc[4 * q] += f.x;
+                    acc[4 * q + 1] += f.y;
+                    acc[4 * q + 2] += f.z;
+                    acc[4 * q + 3] += f.w;
+                }
             }
         }
     }
-}
-
-template <typename T>
-__global__ void __launch_bounds__(256)
-mean_pool_finish_kernel(const float *partial, T *out, int batch, int seq, int hidden, int splits) {
-    const int64_t i = (int64_t) blockIdx.x * 256 + threadIdx.x;
-    if (i >= (int64_t) batch * hidden) {
-        return;
+    if (writer) {
+        float m[EPV];
+#pragma unroll
+        for (int e = 0; e < EPV; ++e) {
+            m[e] = acc[e] / (float) seq;
+        }
+        st_vec(out + (size_t) b * hidden + (size_t) cv * EPV, Vec<T>::pack(m));
     }
-    const int b = (int) (i / hidden);
-    const int c = (int) (i % hidden);
-    float t = 0.f;
-    for (int k = 0; k < splits; ++k) {
-        t += partial[((size_t) b * splits + k) * hidden + c];
-    }
-    out[i] = from_float<T>(t / (float) seq);
 }
 
 // Scalar version for widths or alignments the vector kernel cannot take: thread per (b, c).
@@ -119,15 +143,16 @@ mean_pool_generic_kernel(const T *x, T *out, int batch, int seq, int hidden) {
     out[i] = from_float<T>(t / (float) seq);
 }
 
-// Number of sequence slices: 1 when batch * column blocks already gives two waves of blocks
-// on 148 SMs, otherwise enough slices to get there, each at least 32 positions long.
+// Number of sequence slices: 1 when batch * column blocks already gives four blocks per SM on 148 SMs
+// (half of what fits; measured at [64, 512, 1024] binary16, two waves of 148 left the GPU half empty),
+// otherwise enough slices to get there, each at least 32 positions long.
 static int mean_pool_splits(int batch, int seq, int hidden, int epv) {
     if (hidden % epv != 0) {
         return 1;
     }
     const int nvec = hidden / epv;
     const int64_t blocks = (int64_t) batch * ((nvec + kPoolBX - 1) / kPoolBX);
-    const int64_t want = 2 * 148;
+    const int64_t want = 4 * 148;
     if (blocks >= want || seq < 64) {
         return 1;
     }
@@ -139,13 +164,29 @@ static int mean_pool_splits(int batch, int seq, int hidden, int epv) {
     return splits < 1 ? 1 : (int) splits;
 }
 
+// Bytes of the partial sums (a multiple of 16) and of the ticket counters behind them.
+static size_t pool_partial_bytes(int batch, int splits, int hidden) {
+    return sizeof(float) * (size_t) batch * splits * hidden;
+}
+
+static size_t pool_ticket_bytes(int batch, int nvec) {
+    return (sizeof(unsigned int) * (size_t) batch * ((nvec + kPoolBX - 1) / kPoolBX) + 15) / 16 * 16;
+}
+
+// Whether the vector kernel (the only one that splits, hence the only one that needs scratch) takes the call.
+template <typename T>
+static bool mean_pool_vectorised(const void *x, const void *out, int batch, int hidden) {
+    return hidden % Vec<T>::EPV == 0 && (x == nullptr || aligned16(x)) && (out == nullptr || aligned16(out)) &&
+           batch <= 65535;
+}
+
 template <typename T>
 size_t mean_pool_scratch_bytes(int batch, int seq, int hidden) {
-    if (batch <= 0 || seq <= 0 || hidden <= 0) {
+    if (batch <= 0 || seq <= 0 || hidden <= 0 || !mean_pool_vectorised<T>(nullptr, nullptr, batch, hidden)) {
         return 0;
     }
     const int splits = mean_pool_splits(batch, seq, hidden, Vec<T>::EPV);
-    return splits == 1 ? 0 : sizeof(float) * (size_t) batch * splits * hidden;
+    return splits == 1 ? 0 : pool_partial_bytes(batch, splits, hidden) + pool_ticket_bytes(batch, hidden / Vec<T>::EPV);
 }
 
 template <typename T>
@@ -158,31 +199,31 @@ int mean_pool(const T *x, int batch, int seq, int hidden, T *out, void *scratch,
         return CUBK_OK;
     }
     constexpr int EPV = Vec<T>::EPV;
-    const bool vec_ok = hidden % EPV == 0 && aligned16(x) && batch <= 65535;
-    if (!vec_ok) {
+    if (!mean_pool_vectorised<T>(x, out, batch, hidden)) {
         const int64_t n = (int64_t) batch * hidden;
         mean_pool_generic_kernel<T><<<(unsigned) ((n + 255) / 256), 256, 0, stream>>>(x, out, batch, seq, hidden);
         return check_launch();
     }
     const int nvec = hidden / EPV;
     const int splits = mean_pool_splits(batch, seq, hidden, EPV);
+    unsigned int *tickets = nullptr;
     if (splits > 1) {
-        const size_t need = sizeof(float) * (size_t) batch * splits * hidden;
-        if (scratch == nullptr || scratch_bytes < need || !aligned16(scratch)) {
+        const size_t partial_bytes = pool_partial_bytes(batch, splits, hidden);
+        const size_t ticket_bytes = pool_ticket_bytes(batch, nvec);
+        if (scratch == nullptr || scratch_bytes < partial_bytes + ticket_bytes || !aligned16(scratch)) {
             return CUBK_ERR_SCRATCH;
+        }
+        tickets = reinterpret_cast<unsigned int *>(static_cast<char *>(scratch) + partial_bytes);
+        const cudaError_t err = cudaMemsetAsync(tickets, 0, ticket_bytes, stream);
+        if (err != cudaSuccess) {
+            set_last_error(err);
+            return CUBK_ERR_LAUNCH;
         }
     }
     const int chunk = (seq + splits - 1) / splits;
     const dim3 grid((nvec + kPoolBX - 1) / kPoolBX, splits, batch);
-    mean_pool_kernel<T><<<grid, dim3(kPoolBX, kPoolBY), 0, stream>>>(x, out, (float *) scratch, seq, hidden, nvec,
-                                                                     splits, chunk);
-    int rc = check_launch();
-    if (rc != CUBK_OK || splits == 1) {
-        return rc;
-    }
-    const int64_t n = (int64_t) batch * hidden;
-    mean_pool_finish_kernel<T><<<(unsigned) ((n + 255) / 256), 256, 0, stream>>>((const float *) scratch, out,
-                                                                                batch, seq, hidden, splits);
+    mean_pool_kernel<T><<<grid, dim3(kPoolBX, kPoolBY), 0, stream>>>(x, out, (float *) scratch, tickets, seq, hidden,
+                                                                     nvec, splits, chunk);
     return check_launch();
 }
 
@@ -198,8 +239,8 @@ static __device__ __align__(256) float g_static_pool_scratch[kStaticPoolScratchB
 
 // In host code `g_static_pool_scratch` is only a handle for the runtime, not a device address;
 // the address a kernel can use comes from cudaGetSymbolAddress, asked once per device with that
-// device current. Entries are written once (racing threads store the same value).
-static void *g_static_pool_scratch_addr[kMaxDevices] = {nullptr};
+// device current. A slot is written once; threads that race to fill it store the same value.
+static std::atomic<void *> g_static_pool_scratch_addr[kMaxDevices];
 
 static int static_pool_scratch(void **addr) {
     int device = 0;
@@ -211,16 +252,16 @@ static int static_pool_scratch(void **addr) {
     if (device < 0 || device >= kMaxDevices) {
         return CUBK_ERR_UNSUPPORTED;
     }
-    if (g_static_pool_scratch_addr[device] == nullptr) {
-        void *p = nullptr;
+    void *p = g_static_pool_scratch_addr[device].load(std::memory_order_relaxed);
+    if (p == nullptr) {
         err = cudaGetSymbolAddress(&p, g_static_pool_scratch);
         if (err != cudaSuccess || p == nullptr) {
             set_last_error(err);
             return CUBK_ERR_LAUNCH;
         }
-        g_static_pool_scratch_addr[device] = p;
+        g_static_pool_scratch_addr[device].store(p, std::memory_order_relaxed);
     }
-    *addr = g_static_pool_scratch_addr[device];
+    *addr = p;
     return CUBK_OK;
 }
 
@@ -295,6 +336,117 @@ int logits_probs(const T *pooled, const T *weights, const T *bias, int batch, in
     }
     logits_probs_kernel<T><<<batch, 128, sizeof(float) * labels, stream>>>(pooled, weights, bias, hidden, labels,
                                                                           logits, probs);
+    return check_launch();
+}
+
+// ------------------------------------------------------------------ K5a + K5c in one launch
+// pooled = tanh(x + pooler_bias) written out, then the classifier on it: what bias_act_kernel<Tanh>
+// followed by logits_probs_kernel computes, for the small label counts of a classification head.
+// One 128-thread block per sequence; a thread owns whole 16-byte vectors of the row (all its reads
+// of x, the pooler bias and the classifier rows are 128-bit), keeps its slice of the pooled row in
+// registers -- in storage precision, since the reference's classifier reads the stored pooled
+// output -- and accumulates the dot products of up to kHeadLabels labels at once, which one block
+// reduction then finishes. Saves a launch (and a round trip of the pooled row) on the path that
+// bounds small-batch serving.
+constexpr int kHeadLabels = 8;        // label rows handled per launch
+constexpr int kHeadMaxVectors = 4;    // vectors per thread: rows up to 128 * 4 vectors
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+pooler_head_kernel(const T *x, const T *pooler_bias, const T *weights, const T *bias, int hidden, int nvec, int labels,
+                   T *pooled, T *logits, T *probs) {
+    constexpr int EPV = Vec<T>::EPV;
+    __shared__ float red[4][kHeadLabels];
+    __shared__ float s_logits[kHeadLabels];
+    const int b = blockIdx.x;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    float acc[kHeadLabels];
+#pragma unroll
+    for (int l = 0; l < kHeadLabels; ++l) {
+        acc[l] = 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < kHeadMaxVectors; ++k) {
+        const int idx = threadIdx.x + k * 128;
+        if (idx < nvec) {
+            float v[EPV], pb[EPV];
+            Vec<T>::unpack(ld_stream(x + (size_t) b * hidden + (size_t) idx * EPV), v);
+            Vec<T>::unpack(ld_param(pooler_bias + (size_t) idx * EPV), pb);
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) {
+                v[e] = tanhf(v[e] + pb[e]);
+            }
+            const uint4 stored = Vec<T>::pack(v);
+            st_vec(pooled + (size_t) b * hidden + (size_t) idx * EPV, stored);
+            Vec<T>::unpack(stored, v);  // what the classifier sees is the stored pooled output
+#pragma unroll
+            for (int l = 0; l < kHeadLabels; ++l) {
+                if (l < labels) {
+                    float w[EPV];
+                    Vec<T>::unpack(ld_param(weights + (size_t) l * hidden + (size_t) idx * EPV), w);
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) {
+                        acc[l] = fmaf(w[e], v[e], acc[l]);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int l = 0; l < kHeadLabels; ++l) {
+        acc[l] = group_sum<32>(acc[l]);
+        if (lane == 0) {
+            red[warp][l] = acc[l];
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < labels) {
+        const int l = threadIdx.x;
+        float t = (red[0][l] + red[1][l]) + (red[2][l] + red[3][l]);
+        if (bias != nullptr) {
+            t = to_float<T>(bias[l]) + t;
+        }
+        const T stored = from_float<T>(t);  // the softmax reads the stored logit (op_out/AdditionalOutputLayer.cpp:61-64)
+        logits[(size_t) b * labels + l] = stored;
+        s_logits[l] = to_float<T>(stored);
+    }
+    if (probs == nullptr) {
+        return;
+    }
+    __syncthreads();
+    if (threadIdx.x < labels) {
+        float mx = s_logits[0];
+        for (int l = 1; l < labels; ++l) {
+            mx = fmaxf(mx, s_logits[l]);
+        }
+        float sum = 0.f;
+        for (int l = 0; l < labels; ++l) {
+            sum += expf(s_logits[l] - mx);
+        }
+        probs[(size_t) b * labels + threadIdx.x] = from_float<T>(expf(s_logits[threadIdx.x] - mx) / sum);
+    }
+}
+
+// CUBK_ERR_UNSUPPORTED tells the caller to use cubk_bias_tanh_* and cubk_logits_probs_* instead.
+template <typename T>
+int pooler_head(const T *x, const T *pooler_bias, const T *weights, const T *bias, int batch, int hidden, int labels,
+                T *pooled, T *logits, T *probs, cudaStream_t stream) {
+    if (x == nullptr || pooler_bias == nullptr || weights == nullptr || pooled == nullptr || logits == nullptr ||
+        batch < 0 || hidden <= 0 || labels <= 0) {
+        return CUBK_ERR_INVALID_ARG;
+    }
+    constexpr int EPV = Vec<T>::EPV;
+    if (labels > kHeadLabels || hidden % EPV != 0 || hidden / EPV > 128 * kHeadMaxVectors || !aligned16(x) ||
+        !aligned16(pooler_bias) || !aligned16(weights) || !aligned16(pooled)) {
+        return CUBK_ERR_UNSUPPORTED;
+    }
+    if (batch == 0) {
+        return CUBK_OK;
+    }
+    pooler_head_kernel<T><<<batch, 128, 0, stream>>>(x, pooler_bias, weights, bias, hidden, hidden / EPV, labels, pooled,
+                                                     logits, probs);
     return check_launch();
 }
 
@@ -424,11 +576,16 @@ int cubk_mean_pool_f16(const void *x, int batch, int seq, int hidden, void *out,
 
 int cubk_mean_pool_static_scratch(const void *x, int elem_bytes, int batch, int seq, int hidden, void *out,
                                   void *stream) {
-    if (elem_bytes != 2 && elem_bytes != 4) {
+    if ((elem_bytes != 2 && elem_bytes != 4) || x == nullptr || out == nullptr || batch < 0 || seq <= 0 || hidden <= 0) {
         return CUBK_ERR_INVALID_ARG;
     }
-    const size_t need = elem_bytes == 4 ? cubk::mean_pool_scratch_bytes<float>(batch, seq, hidden)
-                                        : cubk::mean_pool_scratch_bytes<__half>(batch, seq, hidden);
+    // scratch is needed exactly when the ordinary entry point would take its split path for these operands
+    size_t need = 0;
+    if (elem_bytes == 4 ? cubk::mean_pool_vectorised<float>(x, out, batch, hidden)
+                        : cubk::mean_pool_vectorised<__half>(x, out, batch, hidden)) {
+        need = elem_bytes == 4 ? cubk::mean_pool_scratch_bytes<float>(batch, seq, hidden)
+                               : cubk::mean_pool_scratch_bytes<__half>(batch, seq, hidden);
+    }
     if (need > cubk::kStaticPoolScratchBytes) {
         return CUBK_ERR_SCRATCH;  // the shape needs more partial sums than the built-in array holds
     }
@@ -445,6 +602,19 @@ int cubk_mean_pool_static_scratch(const void *x, int elem_bytes, int batch, int 
     }
     return cubk::mean_pool<__half>((const __half *) x, batch, seq, hidden, (__half *) out, scratch,
                                    cubk::kStaticPoolScratchBytes, (cudaStream_t) stream);
+}
+
+int cubk_pooler_head_f32(const float *x, const float *pooler_bias, const float *weights, const float *bias, int batch,
+                         int hidden, int labels, float *pooled, float *logits, float *probs, void *stream) {
+    return cubk::pooler_head<float>(x, pooler_bias, weights, bias, batch, hidden, labels, pooled, logits, probs,
+                                    (cudaStream_t) stream);
+}
+
+int cubk_pooler_head_f16(const void *x, const void *pooler_bias, const void *weights, const void *bias, int batch,
+                         int hidden, int labels, void *pooled, void *logits, void *probs, void *stream) {
+    return cubk::pooler_head<__half>((const __half *) x, (const __half *) pooler_bias, (const __half *) weights,
+                                     (const __half *) bias, batch, hidden, labels, (__half *) pooled,
+                                     (__half *) logits, (__half *) probs, (cudaStream_t) stream);
 }
 
 int cubk_logits_probs_f32(const float *pooled, const float *weights, const float *bias, int batch, int hidden,

@@ -54,6 +54,7 @@ _SIGNATURES = {
     "cubk_mean_pool_{t}": (_I, [_P, _I, _I, _I, _P, _P, _Z, _P]),
     "cubk_mean_pool_static_scratch": (_I, [_P, _I, _I, _I, _I, _P, _P]),
     "cubk_logits_probs_{t}": (_I, [_P, _P, _P, _I, _I, _I, _P, _P, _P]),
+    "cubk_pooler_head_{t}": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P]),
     "cubk_not_{t}": (_I, [_P, _P, _L, _P]),
     "cubk_half_to_float": (_I, [_P, _P, _L, _P]),
 }

@@ -187,9 +187,12 @@ int cubk_bias_tanh_f16(const void *x, const void *bias, int64_t rows, int channe
 /* ---- K5b: mean pooling over the sequence axis ---------------------------------------------------
  * out[b,c] = (sum_s x[b,s,c]) / seq   (every position counts; the mask is ignored)
  * Replaces reduce_mean_1<T> (src/cuBERT/op_bert/BertPooler.h:14-16, op_bert/BertPooler.cu:35-66).
- * When batch is small the sequence axis is split over several thread blocks and the float32
- * partial sums go through `scratch` (device memory, 16-byte aligned, at least
- * cubk_mean_pool_scratch_bytes(batch, seq, hidden) bytes; may be NULL when that is 0). */
+ * When batch is small the sequence axis is split over several thread blocks: their float32 partial sums and
+ * one arrival counter per (sequence, block of 256 columns) go through `scratch` (device memory, 16-byte
+ * aligned, at least cubk_mean_pool_scratch_bytes(batch, seq, hidden) bytes; may be NULL when that is 0).
+ * The call clears the counters itself (an asynchronous memset on `stream`); the contents of scratch before
+ * and after a call mean nothing. The block that arrives last adds the slices in slice order, so the result
+ * is the same from run to run. */
 size_t cubk_mean_pool_scratch_bytes(int batch, int seq, int hidden);
 int cubk_mean_pool_f32(const float *x, int batch, int seq, int hidden, float *out,
                        void *scratch, size_t scratch_bytes, void *stream);
@@ -207,8 +210,9 @@ int cubk_mean_pool_f16(const void *x, int batch, int seq, int hidden, void *out,
  *     binary16 [70, 512, 1024] needs 560 KiB) are refused with CUBK_ERR_SCRATCH before anything runs.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
  *     that device current); make that first call outside any stream capture.
- *   - All calls on a device share the one array. It keeps whatever the previous call left; that is
- *     harmless because every partial sum is written before it is read, so nothing needs clearing.
+ *   - All calls on a device share the one array. It keeps whatever the previous call left: every partial
+ *     sum is written before it is read, and the arrival counters, the one part that must start at zero,
+ *     are cleared by each call before its kernel runs (an asynchronous memset on `stream`).
  *     Two calls whose kernels can overlap on the GPU (different streams, no ordering between them)
  *     race on it: order them on one stream or with events. */
 #define CUBK_STATIC_POOL_SCRATCH_BYTES (512u * 1024u)
@@ -225,6 +229,22 @@ int cubk_logits_probs_f32(const float *pooled, const float *weights, const float
                           int batch, int hidden, int labels, float *logits, float *probs, void *stream);
 int cubk_logits_probs_f16(const void *pooled, const void *weights, const void *bias,
                           int batch, int hidden, int labels, void *logits, void *probs, void *stream);
+
+/* ---- K5a + K5c in one launch ----------------------------------------------------------------------
+ * pooled = tanh(x + pooler_bias);  logits = pooled * weights^T (+ bias);  probs = softmax(logits)
+ * The same results as cubk_bias_tanh_* followed by cubk_logits_probs_* on its output (the classifier reads
+ * the pooled row in storage precision, the softmax the stored logits), for classification heads of up to
+ * 8 labels: replaces tanh_<T> and the pooler bias (src/cuBERT/op_bert/BertPooler.cpp:62-77) together with
+ * ClassifierOutputLayer (src/cuBERT/op_out/AdditionalOutputLayer.cpp:44-66). x [batch, hidden] is the pooler's
+ * dense product; pooled may alias x; bias and probs may be NULL. Returns CUBK_ERR_UNSUPPORTED, having done
+ * nothing, for more than 8 labels, rows that are not whole aligned 16-byte vectors or hidden above 4096
+ * (binary16) / 2048 (float32): callers then use the two separate calls. */
+int cubk_pooler_head_f32(const float *x, const float *pooler_bias, const float *weights, const float *bias,
+                         int batch, int hidden, int labels, float *pooled, float *logits, float *probs,
+                         void *stream);
+int cubk_pooler_head_f16(const void *x, const void *pooler_bias, const void *weights, const void *bias,
+                         int batch, int hidden, int labels, void *pooled, void *logits, void *probs,
+                         void *stream);
 
 /* ---- helpers ------------------------------------------------------------------------------------
  * out[i] = !in[i] as 0/1 in the storage type. Replaces _not<T> (src/cuBERT/op_att/AttentionMask.h:9). */

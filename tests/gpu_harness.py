@@ -75,6 +75,18 @@ def masked_softmax_extents(scores, mask, extents, zero_to, rows_per_batch, scale
     return out
 
 
+def pooler_head(x, pooler_bias, weights, bias, t="f32", want_probs=True):
+    """(status, pooled, logits, probs) of the one-launch pooler activation + classifier."""
+    batch, hidden = x.shape
+    labels = weights.shape[0]
+    pooled = torch.full_like(x, float("nan"))
+    logits = torch.full((batch, labels), float("nan"), dtype=x.dtype, device="cuda")
+    probs = torch.full((batch, labels), float("nan"), dtype=x.dtype, device="cuda") if want_probs else None
+    rc = fn("pooler_head", t)(ptr(x), ptr(pooler_bias), ptr(weights), ptr(bias), batch, hidden, labels, ptr(pooled),
+                              ptr(logits), ptr(probs), stream())
+    return rc, pooled, logits, probs
+
+
 def embed_ln(ids, seg, word, pos, typ, gamma, beta, t="f32", status=None):
     b, s = ids.shape
     vocab, hidden = word.shape

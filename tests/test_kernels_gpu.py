@@ -332,6 +332,20 @@ def test_masked_softmax_with_key_extents(t, batch, heads, seq, zero_to):
              x.data_ptr(), G.stream()) == kernels.CUBK_ERR_INVALID_ARG
 
 
+@pytest.mark.parametrize("t", DTYPES)
+def test_gelu_hands_on_nan_and_infinity(t):
+    """A NaN or +inf that reaches the activation (a binary16 overflow upstream) must stay visible, as in the
+    reference's x * 0.5 * (1 + erf(x / sqrt 2)). For -inf the reference yields NaN (-inf * 0); this kernel
+    gives the limit of GELU there, a zero: the one non-finite input on which the two differ."""
+    x = torch.tensor([[float("nan"), float("inf"), -float("inf"), 1.0, -1.0, 0.0, float("nan"), 2.0]],
+                     dtype=G.TORCH_DTYPE[t], device="cuda")
+    got = G.host(G.bias_gelu(x, None, t))[0]
+    assert np.isnan(got[0]) and np.isnan(got[6])
+    assert got[1] == np.inf
+    assert abs(got[2]) <= 1e-6
+    assert np.all(np.isfinite(got[3:6])) and abs(got[3] - 0.8413447) < 2e-3 and abs(got[4] + 0.1586553) < 2e-3
+
+
 # ============================================================================ K1 embedding + add + LayerNorm
 
 def _choose_embed_kernel(kernel_options, which):
@@ -460,6 +474,54 @@ def test_mean_pool_scratch_contract():
     small = torch.empty(need - 4, dtype=torch.uint8, device="cuda")
     rc = lib.cubk_mean_pool_f32(x.data_ptr(), 2, 512, 1024, out.data_ptr(), small.data_ptr(), need - 4, G.stream())
     assert rc == kernels.CUBK_ERR_SCRATCH
+
+
+@pytest.mark.parametrize("t", DTYPES)
+@pytest.mark.parametrize("batch,hidden,labels,bias", [(1, 768, 2, True), (256, 768, 2, True), (7, 1024, 8, False),
+                                                      (33, 64, 1, True), (5, 2048, 3, True), (3, 8, 5, True)])
+def test_pooler_activation_and_classifier_in_one_launch(oracle, t, batch, hidden, labels, bias):
+    """cubk_pooler_head_* against the two calls it stands for: the pooled row bit for bit, logits and probs as
+    the classifier gives them on the STORED pooled row (only the order of the dot product's additions differs)."""
+    rng = np.random.default_rng(batch * 7 + hidden + labels)
+    x, _ = _prep(rng.standard_normal((batch, hidden)) * 2, t)
+    pb, _ = _prep(rng.standard_normal(hidden), t)
+    w, wh = _prep(rng.standard_normal((labels, hidden)) * 0.1, t)
+    b, bh = _prep(rng.standard_normal(labels), t) if bias else (None, None)
+    rc, pooled, logits, probs = G.pooler_head(x, pb, w, b, t)
+    assert rc == kernels.CUBK_OK
+    assert torch.equal(pooled, G.bias_tanh(x, pb, t))
+    two_l, two_p = G.logits_probs(pooled, w, b, t)
+    ref_logits, ref_probs = oracle.classifier(G.host(pooled), wh, bh)
+    _check(logits, ref_logits, t, 1.0, "logits")
+    _check(logits, G.host(two_l), t, 1.0, "logits against the separate call")
+    if t == "f32":
+        _check(probs, ref_probs, t, 1e-3, "probs")
+    else:
+        _check(probs, oracle.softmax_(G.host(logits)), t, 1e-1, "probs of stored logits")
+        assert np.max(np.abs(G.host(probs) - ref_probs)) <= G.F16_ATOL
+    # in place, and without probs
+    x2 = x.clone()
+    lib = kernels.load()
+    f = getattr(lib, "cubk_pooler_head_" + t)
+    logits2 = torch.empty_like(logits)
+    assert f(x2.data_ptr(), pb.data_ptr(), w.data_ptr(), G.ptr(b), batch, hidden, labels, x2.data_ptr(),
+             logits2.data_ptr(), None, G.stream()) == kernels.CUBK_OK
+    assert torch.equal(x2, pooled) and torch.equal(logits2, logits)
+
+
+def test_pooler_head_declines_what_it_does_not_cover():
+    lib = kernels.load()
+    x = torch.zeros((2, 4096), device="cuda")
+    s = G.stream()
+    p = x.data_ptr()
+    assert lib.cubk_pooler_head_f32(p, p, p, None, 2, 768, 9, p, p, None, s) == kernels.CUBK_ERR_UNSUPPORTED      # labels
+    assert lib.cubk_pooler_head_f32(p, p, p, None, 2, 770, 2, p, p, None, s) == kernels.CUBK_ERR_UNSUPPORTED      # width
+    assert lib.cubk_pooler_head_f32(p, p, p, None, 2, 4096, 2, p, p, None, s) == kernels.CUBK_ERR_UNSUPPORTED     # too wide
+    assert lib.cubk_pooler_head_f32(p + 4, p, p, None, 2, 768, 2, p, p, None, s) == kernels.CUBK_ERR_UNSUPPORTED  # alignment
+    assert lib.cubk_pooler_head_f32(None, p, p, None, 2, 768, 2, p, p, None, s) == kernels.CUBK_ERR_INVALID_ARG
+    assert lib.cubk_pooler_head_f32(p, p, p, None, 2, 768, 0, p, p, None, s) == kernels.CUBK_ERR_INVALID_ARG
+    torch.cuda.synchronize()
+    assert bool((x == 0).all())
 
 
 @pytest.mark.parametrize("t", DTYPES)

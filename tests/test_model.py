@@ -289,7 +289,8 @@ def test_device_resident_forward_and_profile(model_files):
     L = cfg["layers"]
     assert prof["embed_ln"]["launches"] == 1 and prof["bias_residual_ln"]["launches"] == 2 * L
     assert prof["bias_gelu"]["launches"] == L and prof["masked_softmax"]["launches"] == L
-    assert prof["bias_tanh"]["launches"] == 1 and prof["logits_probs"]["launches"] == 1
+    # pooler activation and the two-label classifier run as one launch, counted with the former
+    assert prof["bias_tanh"]["launches"] == 1 and prof["logits_probs"]["launches"] == 0
     assert prof["gemm"]["launches"] == 6 * L + 1 and prof["event_overhead"]["launches"] == 1
     assert prof["bias_gelu"]["ms"] > 0
     assert prof["bias_gelu"]["bytes"] == L * (2 * b * s * cfg["intermediate"] * 4 + cfg["intermediate"] * 4)

@@ -7,6 +7,8 @@ Produces, next to this file:
     lib/libcubert_kernels.so  -- the fused kernels and their C ABI (include/cubert_kernels.h)
     lib/libcuBERT.so          -- the host library with the cuBERT C API (include/cuBERT.h),
                                  linked against libcubert_kernels.so, cuBLAS and cuBLASLt
+    lib/serve_mix             -- closed-loop serving client in native code (csrc/bench/serve_mix.cpp),
+                                 a C++ program that uses nothing but the C API
 
 nvcc cross-compiles without a GPU, so this also runs on a CPU-only machine.
 """
@@ -32,6 +34,7 @@ NVCC_FLAGS = ARCH_FLAGS + ["-lineinfo", "-O3", "-std=c++17", "-ccbin", HOST_CXX,
 
 KERNEL_LIB = os.path.join(LIBDIR, "libcubert_kernels.so")
 HOST_LIB = os.path.join(LIBDIR, "libcuBERT.so")
+SERVE_MIX = os.path.join(LIBDIR, "serve_mix")
 
 
 def _sources(sub):
@@ -114,11 +117,28 @@ def build_host(force=False, verbose=True):
     return HOST_LIB
 
 
+def build_serve_mix(force=False, verbose=True):
+    src = os.path.join(CSRC, "bench", "serve_mix.cpp")
+    if not os.path.exists(src):
+        return None
+    host_lib = build_host(force=False, verbose=verbose)
+    if not force and os.path.exists(SERVE_MIX) and _mtime(SERVE_MIX) >= max(_mtime(src), _mtime(host_lib)):
+        return SERVE_MIX
+    if verbose:
+        print("[build] compiling csrc/bench/serve_mix.cpp", file=sys.stderr)
+    _run([HOST_CXX, "-O2", "-std=c++17", "-pthread", "-I" + INCLUDE, src, "-o", SERVE_MIX, "-L" + LIBDIR, "-lcuBERT",
+          "-lcubert_kernels", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(CUDA_HOME, "lib64")])
+    return SERVE_MIX
+
+
 def build_all(force=False, verbose=True):
     out = [build_kernels(force, verbose)]
     host = build_host(force, verbose)
     if host:
         out.append(host)
+        client = build_serve_mix(force, verbose)
+        if client:
+            out.append(client)
     return out
 
 

@@ -14,6 +14,7 @@ latency and aggregate sequences/s.
 import argparse
 import json
 import os
+import subprocess
 import tempfile
 import threading
 import time
@@ -44,6 +45,9 @@ def main():
     ap.add_argument("--dtype", default="f16", choices=["f16", "f32"])
     ap.add_argument("--seed", type=int, default=5)
     ap.add_argument("--distinct", type=int, default=2048, help="distinct requests generated; the stream cycles over them")
+    ap.add_argument("--native", action="store_true",
+                    help="drive the C API from the native client (lib/serve_mix: C++ threads, its own seeded stream of "
+                         "the same mix) instead of Python threads")
     a = ap.parse_args()
 
     cfg = synthetic.config("base")
@@ -53,6 +57,21 @@ def main():
         var = {k: v.astype(np.float16) for k, v in var.items()}
     path = os.path.join(tempfile.mkdtemp(prefix="cubert_serve_"), "model.pb")
     frozen_graph.write_frozen_graph(path, var)
+    if a.native:
+        from . import build as native
+        if not os.path.exists(native.SERVE_MIX):
+            raise SystemExit("%s is missing: run `python -m cubert_b200.build`" % native.SERVE_MIX)
+        proc = subprocess.run([native.SERVE_MIX, path, str(a.requests), str(a.clients), str(a.seed),
+                               "1" if a.dtype == "f16" else "0", str(cfg["layers"]), str(cfg["heads"]), str(cfg["vocab"]),
+                               str(seq)], stdout=subprocess.PIPE, universal_newlines=True)
+        os.unlink(path)
+        lines = [l for l in proc.stdout.splitlines() if l.startswith("{")]
+        if proc.returncode != 0 or not lines:
+            raise SystemExit("serve_mix failed (exit %d)" % proc.returncode)
+        line = json.loads(lines[-1])
+        line["models_per_gpu"] = int(os.environ.get("CUBERT_NUM_MODELS_PER_GPU", "1"))
+        print(json.dumps(line), flush=True)
+        return
     ct = model.ComputeType.HALF if a.dtype == "f16" else model.ComputeType.FLOAT
     m = model.Model(path, 32, seq, cfg["layers"], cfg["heads"], ct)
     os.unlink(path)

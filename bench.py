@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Workload (BASELINE config 3): BERT-base, binary16 weight/activation storage with float32
+Workload: BERT-base, binary16 weight/activation storage with float32
 arithmetic, seq_length 128, batch 256 per GPU, per-sequence valid length uniform in [8, 128]
 (prefix mask), seeded random-init weights N(0, 0.02) and uniform token ids; outputs
 cuBERT_SEQUENCE_OUTPUT and cuBERT_POOLED_OUTPUT. One step = one forward pass over one batch.
@@ -26,7 +26,7 @@ Printed by rank 0 as ONE JSON line:
 
 --impl reference times only that CPU implementation, on the same workload definition.
 
---workload large_seq512 runs the second full-model case instead (BASELINE config 4): BERT-large,
+--workload large_seq512 runs the second full-model case instead: BERT-large,
 binary16 storage, seq_length 512, ONE batch of 512 sequences split evenly over the GPUs ("strong"
 scaling), full masks, mean pooler, output cuBERT_POOLED_OUTPUT, seed 3.
 """
@@ -50,7 +50,7 @@ WORLD = int(os.environ.get("WORLD_SIZE", "1"))
 # large_seq512 is the second full-model case: one 512-sequence batch split evenly over the GPUs
 # (strong scaling), mean pooler, pooled_output only.
 WORKLOADS = {
-    # the reference's own published case (README: batch 128, seq 32, float32), BASELINE config 1
+    # the reference's own published case (its README: batch 128, seq 32, float32)
     "base_seq32_f32": dict(model="base", seq=32, batch=128, lengths=None, seed=0, scaling="weak", dtype="f32",
                            segments="half", outputs=("logits", "probs"), cpu_sample=128,
                            metric="BERT-base seq32 float32 seqs/s",

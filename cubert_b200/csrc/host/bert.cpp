@@ -264,16 +264,7 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
         if (forced_granule >= 8 && forced_granule % 8 == 0) {
             key_granule_ = forced_granule;
         }
-        key_group_gemms_ = env_int("CUBERT_KEY_GEMM", 1) != 0;
-        key_group_mode_ = env_int("CUBERT_KEY_GROUP_MODE", 0);
-        if (key_group_mode_ == 1) {
-            CUDA_CHECK(cudaEventCreateWithFlags(&fork_, cudaEventDisableTiming));
-            for (int i = 0; i < kSideStreams; ++i) {
-                CUDA_CHECK(cudaStreamCreateWithFlags(&side_stream_[i], cudaStreamNonBlocking));
-                CUDA_CHECK(cudaEventCreateWithFlags(&join_[i], cudaEventDisableTiming));
-                side_blas_[i].reset(new Blas(side_stream_[i], 0, (size_t) 8 << 20));
-            }
-        }
+        key_group_gemms_ = env_int("CUBERT_KEY_GEMM", 0) != 0;
         seq_extent_.assign(B, (int32_t) S);
         CUDA_CHECK(cudaMallocHost(reinterpret_cast<void **>(&h_plan_), sizeof(int32_t) * 2 * B));
         plan_dev_.allocate(sizeof(int32_t) * 2 * B);
@@ -340,19 +331,6 @@ Bert<T>::~Bert() {
     }
     if (staging_read_ != nullptr) {
         cudaEventDestroy(staging_read_);
-    }
-    for (int i = 0; i < kSideStreams; ++i) {
-        side_blas_[i].reset();
-        if (side_stream_[i] != nullptr) {
-            cudaStreamSynchronize(side_stream_[i]);
-            cudaStreamDestroy(side_stream_[i]);
-        }
-        if (join_[i] != nullptr) {
-            cudaEventDestroy(join_[i]);
-        }
-    }
-    if (fork_ != nullptr) {
-        cudaEventDestroy(fork_);
     }
     if (h_plan_ != nullptr) {
         cudaFreeHost(h_plan_);
@@ -508,10 +486,11 @@ void Bert<T>::build_key_plan(size_t batch_size, const int8_t *input_mask) {
     if (!skip_masked_keys_ || input_mask == nullptr || batch_size * S < kMinPositionsForKeyPlan) {
         return;
     }
-    const int granule = key_granule_;
+    // per-group products want few distinct extents; K4 alone can use them vector by vector
+    const int granule = key_group_gemms_ ? key_granule_ : 8;
     int count[kMaxKeyGroups + 2] = {};
     const int buckets = (int) ((S + granule - 1) / granule);   // extent = bucket * granule, capped at S
-    if (buckets > kMaxKeyGroups) {
+    if (key_group_gemms_ && buckets > kMaxKeyGroups) {
         return;
     }
     int64_t columns = 0;
@@ -525,7 +504,9 @@ void Bert<T>::build_key_plan(size_t batch_size, const int8_t *input_mask) {
         int extent = last < 0 ? (int) S : (last / granule + 1) * granule;
         extent = extent > (int) S ? (int) S : extent;
         seq_extent_[b] = extent;
-        count[(extent + granule - 1) / granule] += 1;
+        if (key_group_gemms_) {
+            count[(extent + granule - 1) / granule] += 1;
+        }
         columns += extent;
         hash = (hash ^ (uint64_t) extent) * 1099511628211ull;
     }
@@ -533,31 +514,37 @@ void Bert<T>::build_key_plan(size_t batch_size, const int8_t *input_mask) {
         return;  // under a tenth of the key columns is padding: the extra launches would cost more
     }
     wait_for_staging();
-    // counting sort: groups in order of growing extent
-    int first[kMaxKeyGroups + 2] = {};
-    int groups = 0, at = 0;
-    for (int k = 1; k <= buckets; ++k) {
-        first[k] = at;
-        if (count[k] > 0) {
-            plan_.start[groups] = at;
-            plan_.extent[groups] = k * granule > (int) S ? (int) S : k * granule;
-            ++groups;
-        }
-        at += count[k];
-    }
-    plan_.start[groups] = at;
     int32_t *order = h_plan_;
     int32_t *extents = h_plan_ + max_batch_size;
+    int groups = 0;
+    if (key_group_gemms_) {
+        // counting sort: groups in order of growing extent
+        int first[kMaxKeyGroups + 2] = {};
+        int at = 0;
+        for (int k = 1; k <= buckets; ++k) {
+            first[k] = at;
+            if (count[k] > 0) {
+                plan_.start[groups] = at;
+                plan_.extent[groups] = k * granule > (int) S ? (int) S : k * granule;
+                ++groups;
+            }
+            at += count[k];
+        }
+        plan_.start[groups] = at;
+        for (size_t b = 0; b < batch_size; ++b) {
+            order[first[(seq_extent_[b] + granule - 1) / granule]++] = (int32_t) b;
+        }
+    }
     for (size_t b = 0; b < batch_size; ++b) {
-        const int k = (seq_extent_[b] + granule - 1) / granule;
-        order[first[k]++] = (int32_t) b;
         extents[b] = seq_extent_[b];
     }
     plan_.groups = groups;
     plan_.key_columns = columns;
-    plan_.signature = hash == 0 ? 1 : hash;
+    plan_.signature = hash < 2 ? 2 : hash;
     plan_.active = true;
-    CUDA_CHECK(cudaMemcpyAsync(plan_dev_.get(), h_plan_, sizeof(int32_t) * batch_size, cudaMemcpyHostToDevice, stream_));
+    if (key_group_gemms_) {
+        CUDA_CHECK(cudaMemcpyAsync(plan_dev_.get(), order, sizeof(int32_t) * batch_size, cudaMemcpyHostToDevice, stream_));
+    }
     CUDA_CHECK(cudaMemcpyAsync(plan_dev_.template as<int32_t>() + max_batch_size, extents, sizeof(int32_t) * batch_size,
                                cudaMemcpyHostToDevice, stream_));
     CUDA_CHECK(cudaEventRecord(staging_read_, stream_));
@@ -568,7 +555,7 @@ void Bert<T>::build_key_plan(size_t batch_size, const int8_t *input_mask) {
 // (a row = the `heads` pointers of one sequence, gathered as 2 * heads 32-bit words).
 template <typename T>
 void Bert<T>::sort_attention_pointers(size_t batch_size) {
-    if (!plan_.active) {
+    if (!plan_.active || !key_group_gemms_) {
         return;
     }
     const int heads = (int) num_attention_heads;
@@ -589,46 +576,16 @@ void Bert<T>::grouped_products(bool scores_product, int S, int d, int heads, int
     const T *const *b = scores_product ? q_sorted_.template as<const T *>() : score_sorted_.template as<const T *>();
     T *const *c = scores_product ? score_sorted_.template as<T *>() : ctx_sorted_.template as<T *>();
     const int lda = 3 * H, ldb = scores_product ? 3 * H : S * heads, ldc = scores_product ? S * heads : H;
-    auto one = [&](Blas &blas, int g) {
+    for (int g = 0; g < plan_.groups; ++g) {   // group g: the sequences start[g] .. start[g + 1] of the sorted order
         const size_t at = (size_t) plan_.start[g] * heads;
         const int count = (plan_.start[g + 1] - plan_.start[g]) * heads;
         if (scores_product) {
-            blas.gemm_batched<T>(true, false, plan_.extent[g], S, d, alpha, a + at, lda, b + at, ldb, 0.f, c + at, ldc, count, algo);
+            blas_->gemm_batched<T>(true, false, plan_.extent[g], S, d, alpha, a + at, lda, b + at, ldb, 0.f, c + at, ldc, count,
+                                   algo);
         } else {
-            blas.gemm_batched<T>(false, false, d, S, plan_.extent[g], alpha, a + at, lda, b + at, ldb, 0.f, c + at, ldc, count,
-                                 algo);
+            blas_->gemm_batched<T>(false, false, d, S, plan_.extent[g], alpha, a + at, lda, b + at, ldb, 0.f, c + at, ldc, count,
+                                   algo);
         }
-    };
-    if (key_group_mode_ == 2) {
-        int m[kMaxKeyGroups], n[kMaxKeyGroups], k[kMaxKeyGroups], count[kMaxKeyGroups];
-        for (int g = 0; g < plan_.groups; ++g) {
-            m[g] = scores_product ? plan_.extent[g] : d;
-            n[g] = S;
-            k[g] = scores_product ? d : plan_.extent[g];
-            count[g] = (plan_.start[g + 1] - plan_.start[g]) * heads;
-        }
-        blas_->gemm_grouped<T>(scores_product, false, plan_.groups, m, n, k, alpha, a, lda, b, ldb, 0.f, c, ldc, count);
-        return;
-    }
-    if (key_group_mode_ == 1 && plan_.groups > 1) {
-        CUDA_CHECK(cudaEventRecord(fork_, stream_));
-        const int used = plan_.groups - 1 < kSideStreams ? plan_.groups - 1 : kSideStreams;
-        for (int i = 0; i < used; ++i) {
-            CUDA_CHECK(cudaStreamWaitEvent(side_stream_[i], fork_, 0));
-        }
-        // the largest group (the last) on the replica's own stream, the others dealt round the side streams
-        for (int g = 0; g + 1 < plan_.groups; ++g) {
-            one(*side_blas_[g % kSideStreams], g);
-        }
-        one(*blas_, plan_.groups - 1);
-        for (int i = 0; i < used; ++i) {
-            CUDA_CHECK(cudaEventRecord(join_[i], side_stream_[i]));
-            CUDA_CHECK(cudaStreamWaitEvent(stream_, join_[i], 0));
-        }
-        return;
-    }
-    for (int g = 0; g < plan_.groups; ++g) {
-        one(*blas_, g);
     }
 }
 
@@ -718,7 +675,7 @@ template <typename T>
 void Bert<T>::run(size_t batch_size, const int32_t *d_ids, const int8_t *d_mask, const int8_t *d_segments,
                   size_t packed, bool heads_only) {
     const GraphKey key{batch_size, packed, d_ids, d_mask, d_segments, heads_only ? kWholePassHeadsOnly : kWholePass, 0, 0,
-                       plan_.signature};
+                       plan_key()};
     run_graph(key, [&] { forward(batch_size, d_ids, d_mask, d_segments, packed, heads_only); });
 }
 
@@ -732,7 +689,7 @@ void Bert<T>::run_graph(const GraphKey &key, const std::function<void()> &body) 
         return;
     }
     auto it = graphs_.find(key);
-    if (it != graphs_.end() && key.keys != 0 &&
+    if (it != graphs_.end() && key.keys > 1 &&
         (it->second.extents.size() != key.batch ||
          !std::equal(it->second.extents.begin(), it->second.extents.end(), seq_extent_.begin()))) {
         body();  // another set of key extents with the same hash: never replay a graph of other shapes
@@ -753,7 +710,7 @@ void Bert<T>::run_graph(const GraphKey &key, const std::function<void()> &body) 
             graphs_.erase(oldest);
         }
         it = graphs_.emplace(key, GraphEntry()).first;
-        if (key.keys != 0) {
+        if (key.keys > 1) {
             it->second.extents.assign(seq_extent_.begin(), seq_extent_.begin() + (long) key.batch);
         }
     }
@@ -1202,7 +1159,7 @@ void Bert<T>::compute_output(size_t batch_size, const int *input_ids, const int8
     const size_t tail = chunks > 1 ? ((size_t) tail_layers_ < L ? (size_t) tail_layers_ : L) : 0;
     const size_t per_chunk = (batch_size + chunks - 1) / chunks;
     if (L - tail > 0) {
-        const GraphKey key{batch_size, 0, d_ids, d_mask, d_seg, kHeadLayers, 0, L - tail, plan_.signature};
+        const GraphKey key{batch_size, 0, d_ids, d_mask, d_seg, kHeadLayers, 0, L - tail, plan_key()};
         run_graph(key, [&] { forward_layers(0, L - tail, 0, batch_size, batch_size, d_mask, 0); });
     }
     size_t used = 0;
@@ -1213,7 +1170,7 @@ void Bert<T>::compute_output(size_t batch_size, const int *input_ids, const int8
         }
         const size_t nb = batch_size - b0 < per_chunk ? batch_size - b0 : per_chunk;
         if (tail > 0) {
-            const GraphKey key{batch_size, 0, d_ids, d_mask, d_seg, kTailLayers, b0, nb, plan_.signature};
+            const GraphKey key{batch_size, 0, d_ids, d_mask, d_seg, kTailLayers, b0, nb, plan_key()};
             run_graph(key, [&] { forward_layers(L - tail, L, b0, nb, batch_size, d_mask, 0); });
         }
         if (out->sequence_output != nullptr) {

@@ -120,7 +120,7 @@ private:
         const void *ids, *mask, *segments;
         int phase;        // which part of the pass the graph holds
         size_t b0, nb;    // kTailLayers: the sequences it covers
-        uint64_t keys;    // KeyPlan::signature (0 = every key column), which fixes the attention products' shapes
+        uint64_t keys;    // plan_key(): what the attention launches of the graph depend on
         bool operator<(const GraphKey &o) const {
             return std::tie(batch, packed, ids, mask, segments, phase, b0, nb, keys) <
                    std::tie(o.batch, o.packed, o.ids, o.mask, o.segments, o.phase, o.b0, o.nb, o.keys);
@@ -179,21 +179,22 @@ private:
     T *sequence_output_ = nullptr;
 
     // Attention over kept keys only. When the host sees the mask, every sequence gets a key extent: the
-    // position after its last kept key, rounded up to a multiple of key_granule_ (the whole sequence when no
-    // key is kept, the reference's uniform attention). Key columns from the extent on are masked, so their
-    // probabilities are exactly 0: the Q.K^T product need not compute them, K4 need not read or write them
-    // and the P.V product need not multiply them. Sequences are grouped by extent (a counting sort); each
-    // group runs the two batched products with its own extent over pointer arrays in sorted order, and K4
-    // reads the per-sequence extents. A range of sequences (the sub-batches of compute_output) uses the
-    // largest extent of the range. Off with CUBERT_SKIP_MASKED_KEYS=0, for requests under 2048 positions,
-    // and when less than a tenth of the key columns would be dropped.
+    // position after its last kept key, rounded up (the whole sequence when no key is kept, the reference's
+    // uniform attention). Key columns from the extent on are masked, so their probabilities are exactly 0:
+    // K4 reads the per-sequence extents from device memory, does not load those scores and writes zeros.
+    // Optionally (CUBERT_KEY_GEMM=1, see key_group_gemms_) the Q.K^T product does not compute them and the
+    // P.V product does not multiply them either: sequences are grouped by extent (a counting sort, extents
+    // in steps of key_granule_), each group runs the two batched products with its own extent over pointer
+    // arrays in sorted order, and a range of sequences (the sub-batches of compute_output) uses the largest
+    // extent of the range. Off with CUBERT_SKIP_MASKED_KEYS=0, for sequences under 64 positions, requests
+    // under 2048 positions, and when less than a tenth of the key columns would be dropped.
     static constexpr int kMaxKeyGroups = 16;
     struct KeyPlan {
         bool active = false;
         int groups = 0;
         int start[kMaxKeyGroups + 1] = {};   // first sorted sequence of each group, and the end
         int extent[kMaxKeyGroups] = {};      // key columns of each group
-        uint64_t signature = 0;              // hash of the per-sequence extents (never 0 when active)
+        uint64_t signature = 0;              // hash of the per-sequence extents (2 or more when active)
         int64_t key_columns = 0;             // sum of the extents
     };
     KeyPlan plan_;
@@ -206,16 +207,17 @@ private:
     void build_key_plan(size_t batch_size, const int8_t *input_mask);
     void sort_attention_pointers(size_t batch_size);   // device side of the plan; part of the forward pass
     int range_extent(size_t b0, size_t nb) const;
-    // how the per-group products are issued: 0 = one after the other on the replica's stream, 1 = the groups
-    // side by side on side streams (forked and joined with events, branches of the graph when captured),
-    // 2 = one grouped library call (cublasGemmGroupedBatchedEx)
-    int key_group_mode_ = 0;
-    bool key_group_gemms_ = true;            // false: the products keep every key column, only K4 uses the extents
-    static constexpr int kSideStreams = 3;
-    cudaStream_t side_stream_[kSideStreams] = {};
-    std::unique_ptr<Blas> side_blas_[kSideStreams];
-    cudaEvent_t fork_ = nullptr, join_[kSideStreams] = {};
-    // op(A) * op(B) per group: `fixed` is the dimension that does not depend on the group (queries)
+    // false (default): the two products keep every key column and only K4 uses the extents (it then reads
+    // no score beyond them). true (CUBERT_KEY_GEMM=1): the products run per group of equal extent as well.
+    // Measured on B200, BERT-base, 256 x 128 with lengths U[8,128] (four groups): the per-group products take
+    // 47 us more per layer than the two whole ones (small pointer-array products have a floor of about
+    // 15 us each), 7.43 against 7.07 ms per step; side by side on four streams 7.36 ms, as one
+    // cublasGemmGroupedBatchedEx call 7.98 ms, with two groups of 64 and 128 keys 7.49 ms.
+    bool key_group_gemms_ = false;
+    // what the attention part of a captured graph depends on: 0 = no plan, 1 = extents read from device
+    // memory by K4 only (the same graph serves every mask), otherwise the plan's signature
+    uint64_t plan_key() const { return !plan_.active ? 0 : (key_group_gemms_ ? plan_.signature : 1); }
+    // Q.K^T (scores_product) or P.V for every group of the plan
     void grouped_products(bool scores_product, int S, int d, int heads, int H, float alpha, int algo);
     cudaEvent_t staging_read_ = nullptr;     // after the last copy out of the pinned staging buffers
     bool staging_in_flight_ = false;

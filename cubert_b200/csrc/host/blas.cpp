@@ -78,33 +78,6 @@ void Blas::gemm_batched(bool trans_a, bool trans_b, int m, int n, int k, float a
 }
 
 template <typename T>
-void Blas::gemm_grouped(bool trans_a, bool trans_b, int groups, const int *m, const int *n, const int *k, float alpha,
-                        const T *const *A, int lda, const T *const *B, int ldb, float beta, T *const *C, int ldc,
-                        const int *count) {
-    constexpr int kMax = 32;
-    if (groups <= 0 || groups > kMax) {
-        throw std::invalid_argument("gemm_grouped: group count");
-    }
-    constexpr cudaDataType_t dt = Storage<T>::cuda_type;
-    cublasOperation_t ta[kMax], tb[kMax];
-    int lda_v[kMax], ldb_v[kMax], ldc_v[kMax];
-    float alpha_v[kMax], beta_v[kMax];
-    for (int g = 0; g < groups; ++g) {
-        ta[g] = trans_a ? CUBLAS_OP_T : CUBLAS_OP_N;
-        tb[g] = trans_b ? CUBLAS_OP_T : CUBLAS_OP_N;
-        lda_v[g] = lda;
-        ldb_v[g] = ldb;
-        ldc_v[g] = ldc;
-        alpha_v[g] = alpha;
-        beta_v[g] = beta;
-    }
-    CUBLAS_CHECK(cublasGemmGroupedBatchedEx(handle_, ta, tb, m, n, k, alpha_v, reinterpret_cast<const void *const *>(A), dt,
-                                            lda_v, reinterpret_cast<const void *const *>(B), dt, ldb_v, beta_v,
-                                            reinterpret_cast<void *const *>(C), dt, ldc_v, groups, count,
-                                            CUBLAS_COMPUTE_32F));
-}
-
-template <typename T>
 void Blas::gemm_bias(int m, int n, int k, const T *A, int lda, const T *B, int ldb, const T *bias, T *C,
                      int ldc) {
     if (m == 0 || n == 0) {
@@ -172,9 +145,6 @@ void Blas::gemm_bias(int m, int n, int k, const T *A, int lda, const T *B, int l
                                 int);                                                                               \
     template void Blas::gemm_batched<T>(bool, bool, int, int, int, float, const T *const *, int, const T *const *,  \
                                         int, float, T *const *, int, int, int);                                     \
-    template void Blas::gemm_grouped<T>(bool, bool, int, const int *, const int *, const int *, float,              \
-                                        const T *const *, int, const T *const *, int, float, T *const *, int,       \
-                                        const int *);                                                               \
     template void Blas::gemm_bias<T>(int, int, int, const T *, int, const T *, int, const T *, T *, int);
 
 INSTANTIATE(float)

@@ -42,14 +42,6 @@ public:
     void gemm_batched(bool trans_a, bool trans_b, int m, int n, int k, float alpha, const T *const *A, int lda,
                       const T *const *B, int ldb, float beta, T *const *C, int ldc, int batch, int algo);
 
-    // `groups` pointer-array batched products of different shapes in one library call
-    // (cublasGemmGroupedBatchedEx): group g multiplies count[g] consecutive entries of the pointer arrays
-    // with (m[g], n[g], k[g]); transposition, leading dimensions, alpha and beta are common to all.
-    template <typename T>
-    void gemm_grouped(bool trans_a, bool trans_b, int groups, const int *m, const int *n, const int *k, float alpha,
-                      const T *const *A, int lda, const T *const *B, int ldb, float beta, T *const *C, int ldc,
-                      const int *count);
-
     // C = A * B + bias (bias of length m broadcast over the n columns), through the cuBLASLt
     // bias epilogue. Used where no fused kernel follows the product (the Q/K/V projection).
     template <typename T>

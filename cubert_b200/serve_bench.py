@@ -1,4 +1,4 @@
-"""Online-serving mix through the replica manager (BASELINE config 5).
+"""Online-serving mix through the replica manager.
 
     CUBERT_NUM_MODELS_PER_GPU=2 python -m cubert_b200.serve_bench [--requests N] [--clients C]
                                                                    [--dtype f16|f32] [--seed S]

@@ -1,4 +1,4 @@
-"""Isolated sweep of the fused kernels (BASELINE config 2): achieved HBM GB/s per kernel and shape.
+"""Isolated sweep of the fused kernels: achieved HBM GB/s per kernel and shape.
 
     python -m cubert_b200.sweep [--quick] [--large] [--only ln,gelu,softmax,embed,pool] [--dtype f16,f32]
                                 [--iters N] [--json out.json]

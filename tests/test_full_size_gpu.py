@@ -4,7 +4,7 @@ Kernels at the largest shapes of the isolated sweep (more than 2^31 elements per
 reference's `int` indices cannot address): the CPU oracle checks a random sample of rows, and
 size-independent properties cover every row (LayerNorm rows have mean beta-weighted 0 and unit
 variance, softmax rows sum to 1 with zeros exactly where the mask is 0, GELU is bounded by its input).
-Whole model at the sizes of BASELINE configs 1, 3 and 4 against the reference's CPU code.
+Whole model at the sizes of the three full-model benchmark workloads against the reference's CPU code.
 """
 import numpy as np
 import pytest
@@ -106,7 +106,7 @@ def _rel(a, b):
 
 
 def test_config1_bert_base_f32_seq32_batch128(base_model_file, reference_cpu):
-    """BASELINE config 1: BERT-base float32, seq 32, batch 128, logits and probs, against the
+    """The reference's published case: BERT-base float32, seq 32, batch 128, logits and probs, against the
     reference's CPU build on the same weights and inputs (seed 0, ids in [1, 21128), full mask,
     segment 0 for the first 16 positions)."""
     path, cfg, var = base_model_file
@@ -129,7 +129,7 @@ def test_config1_bert_base_f32_seq32_batch128(base_model_file, reference_cpu):
 
 
 def test_config3_bert_base_f16_seq128_variable_length(base_model_file, reference_cpu):
-    """BASELINE config 3 (the benchmark workload) on a 32-sequence slice: binary16 storage against the
+    """The headline benchmark workload (BERT-base, seq 128, ragged masks) on a 32-sequence slice: binary16 storage against the
     float32 reference on binary16-rounded weights."""
     path, cfg, var = base_model_file
     var16 = {k: v.astype(np.float16).astype(np.float32) for k, v in var.items()}
@@ -150,7 +150,7 @@ def test_config3_bert_base_f16_seq128_variable_length(base_model_file, reference
 
 
 def test_config4_bert_large_f16_seq512_mean_pooler(tmp_path, reference_cpu):
-    """BASELINE config 4 on a 4-sequence slice: BERT-large geometry, seq 512, no pooler weights
+    """The BERT-large workload on a 4-sequence slice: BERT-large geometry, seq 512, no pooler weights
     (mean pooler) and no classifier, cuBERT_POOLED_OUTPUT."""
     cfg = synthetic.config("large", layers=4)   # 4 of the 24 layers keep the CPU reference to seconds
     var = synthetic.random_weights(cfg, 3)

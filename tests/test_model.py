@@ -427,12 +427,16 @@ def test_a_sequence_without_any_kept_key_is_not_packed(model_files, oracle, ct):
 @pytest.mark.gpu
 @pytest.mark.parametrize("ct", [model.ComputeType.FLOAT, model.ComputeType.HALF])
 @pytest.mark.parametrize("batch", [24, 130])     # 130 x 128 positions: per-position outputs leave in sub-batches
-def test_masked_key_columns_are_left_out_of_the_attention(model_files, oracle, ct, batch, monkeypatch):
-    """With the mask visible on the host, the attention products and the softmax work only on the key columns
-    below each sequence's last kept key (rounded up to 32). Those columns carry probability exactly 0 in the
-    full computation, so every output must be what the library gives with the feature off -- for ragged
-    prefixes, masks with holes, a full sequence, a sequence without any kept key -- eagerly, captured and
-    replayed, for per-position requests, pooled-only requests and device-resident inputs."""
+@pytest.mark.parametrize("products_too", ["0", "1"])
+def test_masked_key_columns_are_left_out_of_the_attention(model_files, oracle, ct, batch, products_too, monkeypatch):
+    """With the mask visible on the host, the softmax (and with CUBERT_KEY_GEMM=1 the two attention products as
+    well, per group of sequences) works only on the key columns below each sequence's last kept key, rounded
+    up to 8 (32 with the products). Those columns carry probability exactly 0 in the full computation, so every
+    output must be what the library gives with the feature off -- for ragged prefixes, masks with holes, a full
+    sequence, a sequence without any kept key -- eagerly, captured and replayed, for per-position requests,
+    pooled-only requests and device-resident inputs."""
+    monkeypatch.setenv("CUBERT_KEY_GEMM", products_too)
+    step = 32 if products_too == "1" else 8
     import torch
     path, cfg, var = model_files["small"]
     S = 128
@@ -468,7 +472,7 @@ def test_masked_key_columns_are_left_out_of_the_attention(model_files, oracle, c
     prof = m.profile_read()
     m.profile_enable(False)
     last = np.where(mask.any(axis=1), S - np.argmax(mask[:, ::-1] != 0, axis=1), S)
-    extents = np.minimum((last + 31) // 32 * 32, S)
+    extents = np.minimum((last + step - 1) // step * step, S)
     e = 4 if ct == model.ComputeType.FLOAT else 2
     assert prof["masked_softmax"]["bytes"] == cfg["layers"] * (2 * int(extents.sum()) * S * cfg["heads"] * e + batch * S)
     assert int(extents.sum()) < 0.9 * batch * S

@@ -158,20 +158,25 @@ def test_one_layer_of_non_gemm_work_against_the_reference_kernels(refgpu, t):
 
 # ============================================================================ whole model: the reference's GPU build
 
-@pytest.mark.parametrize("name,half", [("base_seq32", False), ("base_seq128", True)])
+@pytest.mark.parametrize("name,half", [("base_seq32", False), ("base_seq128", True), ("large_seq512", True)])
 def test_whole_model_against_the_references_gpu_build(name, half, tmp_path):
     """The reference's complete GPU build (its host code and its own kernels, compiled for sm_100a by
     `make -C oracle ref_gpu_full`) and this library on the same B200, same weights, same inputs, both
     through their host-buffer API: parity of every output, and the time per call side by side, once
     with pooled_output alone copied back (where this library skips padding) and once with sequence_output too. base_seq32: BERT-base float32, batch 128, seq 32 (the reference's
-    published case); base_seq128: binary16 storage, batch 256, seq 128, valid length U[8,128]."""
+    published case); base_seq128: binary16 storage, batch 256, seq 128, valid length U[8,128] (the whole
+    benchmark batch, per-position outputs leaving in sub-batches); large_seq512: BERT-large at its full depth of
+    24 layers, binary16 storage, seq 512, 8 sequences, mean pooler -- the check that binary16 rounding does not
+    grow over 24 layers beyond what the reference's own binary16 build shows."""
     import time
     from cubert_b200 import frozen_graph, model, synthetic
     from oracle import bindings
     if bindings.build_gpu_full() is None:
         pytest.skip("reference GPU build not available (reference tree absent at build time)")
-    cfg = synthetic.config("base")
-    if half:
+    cfg = synthetic.config("large" if name == "large_seq512" else "base")
+    if name == "large_seq512":
+        B, Sq, seed, lengths = 8, 512, 3, "full"
+    elif half:
         B, Sq, seed, lengths = 256, 128, 2, (8, 128)
     else:
         B, Sq, seed, lengths = 128, 32, 0, "full"
@@ -198,7 +203,10 @@ def test_whole_model_against_the_references_gpu_build(name, half, tmp_path):
         scale = float(np.sqrt(np.mean(v.astype(np.float64) ** 2))) + 1e-30
         if half:
             # both sides round to binary16 at different places (the reference after every operator)
-            assert err < (2e-2 if k in ("probs", "pooled_output", "logits") else 1e-1), (k, err)
+            # pooled_output of the mean pooler averages 512 positions: held to 1e-2
+            bar = 1e-2 if (k == "pooled_output" and name == "large_seq512") else \
+                (2e-2 if k in ("probs", "pooled_output", "logits") else 1e-1)
+            assert err < bar, (k, err)
         else:
             # the reference's GPU kernels use fast-math intrinsics (__expf, erff approximations)
             assert err / scale < 2e-4, (k, err / scale)

@@ -39,7 +39,7 @@ def _worker(rank, world, port, out):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         assert replicas.rank_info() == (rank, rank, world)
-        begin, end = replicas.shard_range(513, rank, world)      # config 4 style: one batch split over ranks
+        begin, end = replicas.shard_range(513, rank, world)      # one batch split over the ranks (strong scaling)
         seconds = 0.25 * (rank + 1)                              # rank 1 is the slow one
         covered = replicas.sum_over_ranks(end - begin)
         slowest = replicas.max_over_ranks(seconds)

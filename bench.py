@@ -167,14 +167,41 @@ def measured_peak():
     return 6650.0, "fallback"
 
 
-# Per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the fused kernels on
-# this workload's shapes, from the ncu captures summarised under profiles/. None = not captured.
-NCU_TRAFFIC_BYTES = {
-    "bias_gelu": 347537280,         # 201.4 MB read + 146.2 MB written (rest of the output still in L2)
-    "bias_residual_ln": 108957440,  # 100.7 MB read + 8.3 MB written
-    "masked_softmax": 147773000,    # 100.7 MB read + 47.1 MB written
-    "embed_ln": 29354880,           # 26.0 MB read + 3.3 MB written: word rows are served by L2
+# Per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the fused kernels on the headline
+# workload's shapes, from the ncu captures summarised under profiles/. Each figure belongs to ONE kernel of ONE
+# library version on ONE workload; ncu_traffic() hands it out only when all three still hold, else None.
+NCU_TRAFFIC = {
+    "bias_gelu": dict(bytes=346974336, kernel="bias_act_kernel<__half, 128, 2, 4, GeluTailFit<6>>",
+                      note="201.3 MB read + 145.6 MB written (rest of the output still in L2)"),
+    "bias_residual_ln": dict(bytes=108217344, kernel="bias_residual_ln_rows_kernel<__half, 3>",
+                             note="100.7 MB read + 7.5 MB written"),
+    "masked_softmax": dict(bytes=123932032, kernel="masked_softmax_kernel<__half, 4, 4, 1, 256, true, true>",
+                           note="77.1 MB read (scores past each sequence's last kept key are not read) + 46.8 MB written"),
+    "embed_ln": dict(bytes=33222528, kernel="embed_ln_rows_kernel<__half, 3, 3>",
+                     note="28.8 MB read + 4.4 MB written: word rows are served by L2"),
 }
+NCU_TRAFFIC_SOURCE = dict(workload="base_seq128", cubk_version=110,
+                          profile="profiles/fused_kernels_in_bench_f16_ncu_full.md")
+NCU_TRAFFIC_BYTES = {k: v["bytes"] for k, v in NCU_TRAFFIC.items()}
+
+
+def ncu_traffic(family, workload_name, cubk_version, default_switches):
+    """DRAM bytes per launch that ncu measured for `family`, or None when the capture does not describe what
+    runs now: another workload, another build of the kernel library, or kernel-selection switches
+    (cubk_set_option / their environment variables, the CUBERT_* toggles that change what K4 reads) off their
+    defaults."""
+    entry = NCU_TRAFFIC.get(family)
+    if (entry is None or workload_name != NCU_TRAFFIC_SOURCE["workload"] or
+            cubk_version != NCU_TRAFFIC_SOURCE["cubk_version"] or not default_switches):
+        return None
+    return dict(bytes=entry["bytes"], kernel=entry["kernel"], profile=NCU_TRAFFIC_SOURCE["profile"], note=entry["note"])
+
+
+def switches_at_defaults(env):
+    """True when no variable that changes which kernel variant runs, or what it reads, is set."""
+    names = ("CUBK_BULK_COPY", "CUBK_SOFTMAX_MASK_SMEM", "CUBK_EXACT_WIDTH_ROWS", "CUBK_EXACT_WIDTH_EMBED",
+             "CUBERT_SKIP_MASKED_KEYS", "CUBERT_KEY_GEMM", "CUBERT_KEY_GRANULE")
+    return not any(n in env for n in names)
 
 
 def make_model_file(cfg, seed, half):
@@ -395,10 +422,13 @@ def run_ours(args):
     top = max(ours, key=lambda k: ours[k]["ms_total"])
     # What the event pair itself costs: the same bracket around a one-thread kernel, once per pass.
     overhead_us = kernels.get("event_overhead", {}).get("us_per_launch")
+    from cubert_b200 import kernels as kernel_lib
+    workload_name = [k for k, v in WORKLOADS.items() if v is WORKLOAD][0]
+    traffic = ncu_traffic(top, workload_name, kernel_lib.load().cubk_version(), switches_at_defaults(os.environ))
     roofline = {"bound": "hbm", "kernel": top, "achieved": ours[top]["gbs"], "peak": peak, "peak_kind": peak_kind,
                 "unit": "GB/s", "frac": ours[top]["gbs"] / peak,
                 "bytes_per_launch": ours[top]["bytes_per_launch"], "us_per_launch": ours[top]["us_per_launch"],
-                "traffic": NCU_TRAFFIC_BYTES.get(top) if WORKLOAD is WORKLOADS["base_seq128"] else None,
+                "traffic": traffic["bytes"] if traffic else None, "traffic_source": traffic,
                 "event_bracket_overhead_us": overhead_us}
     if overhead_us:
         for k, v in ours.items():

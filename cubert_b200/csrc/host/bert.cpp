@@ -830,11 +830,14 @@ void Bert<T>::forward_layers(size_t l_begin, size_t l_end, size_t b0, size_t nb,
     const bool grouped = plan_.active && key_group_gemms_ && b0 == 0 && nb == batch_size;
     const int keys = plan_.active && key_group_gemms_ && !grouped ? range_extent(b0, nb) : S;
     const int32_t *extents = plan_.active ? plan_dev_.template as<int32_t>() + max_batch_size + b0 : nullptr;
-    int64_t key_columns = R;   // sum over the range's sequences of the key columns K4 moves
+    // key columns K4 reads and writes, summed over the range's sequences (it writes zeros from a sequence's
+    // extent up to what the P.V product will read)
+    int64_t read_columns = R, written_columns = R;
     if (plan_.active) {
-        key_columns = 0;
+        read_columns = written_columns = 0;
         for (size_t b = b0; b < b0 + nb; ++b) {
-            key_columns += seq_extent_[b];
+            read_columns += seq_extent_[b];
+            written_columns += grouped ? seq_extent_[b] : (seq_extent_[b] > keys ? seq_extent_[b] : keys);
         }
     }
 
@@ -876,7 +879,7 @@ void Bert<T>::forward_layers(size_t l_begin, size_t l_end, size_t b0, size_t nb,
         } else {
             KERNEL_CHECK(K<T>::masked_softmax(scores, mask, R * heads, (int64_t) S * heads, S, 1.0f, scores, st));
         }
-        end(CUBERT_B200_K_MASKED_SOFTMAX, 2 * key_columns * S * heads * e + R);
+        end(CUBERT_B200_K_MASKED_SOFTMAX, (read_columns + written_columns) * S * heads * e + R);
 
         // context[b, i, h, c] = sum_j V[b,j,h,c] * P[b,i,h,j]   (op_att/BatchMatMul.cpp:124-135)
         begin(CUBERT_B200_K_GEMM);

@@ -21,7 +21,7 @@ namespace cubk {
 // scratch and are cleared by a memset node in front of the kernel.
 constexpr int kPoolBX = 32;
 constexpr int kPoolBY = 8;
-constexpr int kPoolUnroll = 4;
+constexpr int kPoolUnroll = 8;
 
 template <typename T>
 __global__ void __launch_bounds__(kPoolBX *kPoolBY)

@@ -95,3 +95,20 @@ def test_a_bench_process_sees_one_gpu_whatever_the_launcher_left_visible():
     assert bench.device_for_rank("", 3) == "3" and bench.device_for_rank(None, 0) == "0"
     assert bench.device_for_rank("GPU-aaaa,GPU-bbbb", 1) == "GPU-bbbb"
     assert bench.device_for_rank("2", 5) == "5"
+
+
+def test_ncu_traffic_is_only_reported_for_what_was_captured():
+    """roofline.traffic is a figure from one ncu capture: it must vanish when the workload, the kernel library's
+    version or a kernel-selection switch differs from what was captured."""
+    bench = _bench_module()
+    v = bench.NCU_TRAFFIC_SOURCE["cubk_version"]
+    got = bench.ncu_traffic("bias_gelu", "base_seq128", v, True)
+    assert got["bytes"] == bench.NCU_TRAFFIC["bias_gelu"]["bytes"] and got["profile"].startswith("profiles/")
+    assert os.path.exists(os.path.join(ROOT, got["profile"]))
+    assert bench.ncu_traffic("bias_gelu", "large_seq512", v, True) is None
+    assert bench.ncu_traffic("bias_gelu", "base_seq128", v + 1, True) is None
+    assert bench.ncu_traffic("bias_gelu", "base_seq128", v, False) is None
+    assert bench.ncu_traffic("mean_pool", "base_seq128", v, True) is None
+    assert bench.switches_at_defaults({"PATH": "/bin"}) and not bench.switches_at_defaults({"CUBERT_KEY_GEMM": "1"})
+    from cubert_b200 import kernels
+    assert kernels.load().cubk_version() == v, "kernel library version changed: re-capture or clear bench.NCU_TRAFFIC"

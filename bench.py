@@ -420,7 +420,8 @@ def run_ours(args):
         kernels[k] = entry
     ours = {k: v for k, v in kernels.items() if k != "gemm" and "gbs" in v}
     top = max(ours, key=lambda k: ours[k]["ms_total"])
-    # What the event pair itself costs: the same bracket around a one-thread kernel, once per pass.
+    # What the event pair itself costs at least: the same bracket around nothing, once per pass. Fractions are
+    # reported raw (event time as measured) first; `frac_net_of_event_overhead` takes only this floor off.
     overhead_us = kernels.get("event_overhead", {}).get("us_per_launch")
     from cubert_b200 import kernels as kernel_lib
     workload_name = [k for k, v in WORKLOADS.items() if v is WORKLOAD][0]

@@ -159,7 +159,7 @@ private:
     // inputs and activations (shared by all layers)
     // input_ids (int32), input_mask (int8) and segment_ids (int8) of a request live in ONE device buffer at
     // fixed offsets; small models' requests arrive through one pinned staging buffer and one copy
-    DeviceBuffer inputs_, status_, calibration_;
+    DeviceBuffer inputs_, status_;
     int32_t *ids_ = nullptr;
     int8_t *mask_ = nullptr, *segments_ = nullptr;
     unsigned char *h_inputs_ = nullptr;  // pinned twin of inputs_, only when the whole span is small
@@ -225,7 +225,7 @@ private:
 
     // overlapped output copies
     static constexpr size_t kMaxTailChunks = 8;
-    int tail_chunks_ = 4, tail_layers_ = 2;
+    int tail_chunks_ = 4, tail_layers_ = 2, tail_last_percent_ = 0;
     cudaStream_t copy_stream_ = nullptr;
     cudaEvent_t embed_ready_ = nullptr;
     cudaEvent_t chunk_ready_[kMaxTailChunks] = {};

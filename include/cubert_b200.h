@@ -117,8 +117,8 @@ enum {
     CUBERT_B200_K_LOGITS_PROBS,
     CUBERT_B200_K_HALF_TO_FLOAT,
     CUBERT_B200_K_GEMM,          /* cuBLAS / cuBLASLt calls: outside the product, timed for context */
-    CUBERT_B200_K_EVENT_OVERHEAD, /* one-thread kernel bracketed the same way, once per timed forward pass:
-                                     what the event pair itself adds to every figure above */
+    CUBERT_B200_K_EVENT_OVERHEAD, /* an EMPTY event bracket, once per timed forward pass: the least the event pair
+                                     itself adds to every figure above (not a kernel; counted in `launches`) */
     CUBERT_B200_K_COUNT
 };
 struct cubert_b200_profile {

@@ -290,6 +290,21 @@ def test_masked_softmax(oracle, t, kind, batch, heads, seq, mask_terms, kernel_o
     assert torch.equal(got, got2)
 
 
+@pytest.mark.parametrize("t", DTYPES)
+@pytest.mark.parametrize("seq", [32, 128, 37])
+def test_masked_softmax_keeps_nan_and_infinity_visible(t, seq):
+    """A NaN score makes its whole row NaN, a row of -inf scores becomes NaN (-inf minus -inf), a +inf score
+    as well (inf minus inf): what the reference's max-subtracted softmax yields (src/cuBERT/op/Softmax.cpp:19-35).
+    Rows next to them are untouched."""
+    x = torch.zeros((4, seq), dtype=G.TORCH_DTYPE[t], device="cuda")
+    x[0, 3] = float("nan")
+    x[1, :] = -float("inf")
+    x[2, 5] = float("inf")
+    got = G.host(G.masked_softmax(x, None, 4, 1.0, t))
+    assert np.all(np.isnan(got[0])) and np.all(np.isnan(got[1])) and np.all(np.isnan(got[2]))
+    assert np.allclose(got[3], 1.0 / seq, rtol=2e-3)
+
+
 @pytest.mark.parametrize("zero_to", ["own", "common", "full"])
 @pytest.mark.parametrize("t", DTYPES)
 @pytest.mark.parametrize("batch,heads,seq", [(6, 3, 128), (3, 2, 512), (5, 2, 32), (4, 2, 64), (3, 1, 37), (2, 1, 1024),

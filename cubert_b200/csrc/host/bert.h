@@ -61,7 +61,8 @@ public:
     // last encoder layers run sub-batch by sub-batch and each sub-batch's rows start their device-to-host
     // copy on a second stream as soon as they are final, while the next sub-batch is computed;
     // embedding_output leaves right after the embedding kernel. Results are those of the plain pass.
-    // CUBERT_TAIL_CHUNKS (sub-batches, default 4, 1 = off) and CUBERT_TAIL_LAYERS (default 2) tune it.
+    // CUBERT_TAIL_CHUNKS (sub-batches, default 4, 1 = off), CUBERT_TAIL_LAYERS (default 2) and
+    // CUBERT_TAIL_LAST_PERCENT (size of the last sub-batch, default 6 % of the batch) tune it.
     void compute_output(size_t batch_size, const int *input_ids, const int8_t *input_mask,
                         const int8_t *segment_ids, cuBERT_Output *out, bool to_float);
 
@@ -225,7 +226,7 @@ private:
 
     // overlapped output copies
     static constexpr size_t kMaxTailChunks = 8;
-    int tail_chunks_ = 4, tail_layers_ = 2, tail_last_percent_ = 0;
+    int tail_chunks_ = 4, tail_layers_ = 2, tail_last_percent_ = 6;
     cudaStream_t copy_stream_ = nullptr;
     cudaEvent_t embed_ready_ = nullptr;
     cudaEvent_t chunk_ready_[kMaxTailChunks] = {};

@@ -21,17 +21,21 @@ namespace cubk {
 // scratch and are cleared by a memset node in front of the kernel.
 constexpr int kPoolBX = 32;
 constexpr int kPoolBY = 8;
-constexpr int kPoolUnroll = 8;
+constexpr int kPoolUnroll = 4;
+// The narrow layout: 8 column vectors x 32 sequence lanes per block (a warp reads four rows of 128 bytes).
+// Four times the blocks for the same tensor, so that a mid-sized batch fills the GPU without slicing the sequence.
+constexpr int kPoolNarrowBX = 8;
+constexpr int kPoolNarrowBY = 32;
 
-template <typename T>
-__global__ void __launch_bounds__(kPoolBX *kPoolBY)
+template <typename T, int BX, int BY>
+__global__ void __launch_bounds__(BX *BY)
 mean_pool_kernel(const T *x, T *out, float *partial, unsigned int *tickets, int seq, int hidden, int nvec, int splits,
                  int chunk) {
     constexpr int EPV = Vec<T>::EPV;
-    __shared__ float smem[kPoolBY][kPoolBX][EPV + 1];
+    __shared__ float smem[BY][BX][EPV + 1];
     __shared__ unsigned int s_ticket;
 
-    const int cv = blockIdx.x * kPoolBX + threadIdx.x;
+    const int cv = blockIdx.x * BX + threadIdx.x;
     const int split = blockIdx.y;
     const int b = blockIdx.z;
     const int s_begin = split * chunk;
@@ -44,11 +48,11 @@ mean_pool_kernel(const T *x, T *out, float *partial, unsigned int *tickets, int 
     }
     if (cv < nvec) {
         const T *base = x + ((size_t) b * seq) * hidden + (size_t) cv * EPV;
-        for (int s0 = s_begin + threadIdx.y; s0 < s_end; s0 += kPoolBY * kPoolUnroll) {
+        for (int s0 = s_begin + threadIdx.y; s0 < s_end; s0 += BY * kPoolUnroll) {
             uint4 raw[kPoolUnroll];
 #pragma unroll
             for (int u = 0; u < kPoolUnroll; ++u) {
-                const int s = s0 + u * kPoolBY;
+                const int s = s0 + u * BY;
                 raw[u] = s < s_end ? ld_stream(base + (size_t) s * hidden) : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
@@ -73,7 +77,7 @@ mean_pool_kernel(const T *x, T *out, float *partial, unsigned int *tickets, int 
         for (int e = 0; e < EPV; ++e) {
             float t = 0.f;
 #pragma unroll
-            for (int y = 0; y < kPoolBY; ++y) {
+            for (int y = 0; y < BY; ++y) {
                 t += smem[y][threadIdx.x][e];
             }
             acc[e] = t;
@@ -143,17 +147,28 @@ mean_pool_generic_kernel(const T *x, T *out, int batch, int seq, int hidden) {
     out[i] = from_float<T>(t / (float) seq);
 }
 
-// Number of sequence slices: 1 when batch * column blocks already gives four blocks per SM on 148 SMs
-// (half of what fits; measured at [64, 512, 1024] binary16, two waves of 148 left the GPU half empty),
-// otherwise enough slices to get there, each at least 32 positions long.
+// Blocks wanted in flight: four per SM on 148 SMs (half of what fits; measured at [64, 512, 1024] binary16,
+// two waves of 148 left the GPU half empty).
+constexpr int64_t kPoolWantBlocks = 4 * 148;
+
+// Whether the narrow layout is the one to use: the wide one would leave the GPU under-filled and the narrow
+// one fills it without slicing the sequence.
+static bool mean_pool_narrow(int batch, int seq, int nvec) {
+    const int64_t wide = (int64_t) batch * ((nvec + kPoolBX - 1) / kPoolBX);
+    const int64_t narrow = (int64_t) batch * ((nvec + kPoolNarrowBX - 1) / kPoolNarrowBX);
+    return wide < kPoolWantBlocks && narrow >= kPoolWantBlocks && seq >= 4 * kPoolNarrowBY;
+}
+
+// Number of sequence slices (wide layout): 1 when batch * column blocks already gives the blocks wanted or the
+// narrow layout does, otherwise enough slices to get there, each at least 32 positions long.
 static int mean_pool_splits(int batch, int seq, int hidden, int epv) {
     if (hidden % epv != 0) {
         return 1;
     }
     const int nvec = hidden / epv;
     const int64_t blocks = (int64_t) batch * ((nvec + kPoolBX - 1) / kPoolBX);
-    const int64_t want = 4 * 148;
-    if (blocks >= want || seq < 64) {
+    const int64_t want = kPoolWantBlocks;
+    if (blocks >= want || seq < 64 || mean_pool_narrow(batch, seq, nvec)) {
         return 1;
     }
     int64_t splits = (want + blocks - 1) / blocks;
@@ -221,9 +236,15 @@ int mean_pool(const T *x, int batch, int seq, int hidden, T *out, void *scratch,
         }
     }
     const int chunk = (seq + splits - 1) / splits;
+    if (splits == 1 && mean_pool_narrow(batch, seq, nvec)) {
+        const dim3 grid((nvec + kPoolNarrowBX - 1) / kPoolNarrowBX, 1, batch);
+        mean_pool_kernel<T, kPoolNarrowBX, kPoolNarrowBY><<<grid, dim3(kPoolNarrowBX, kPoolNarrowBY), 0, stream>>>(
+            x, out, nullptr, nullptr, seq, hidden, nvec, 1, chunk);
+        return check_launch();
+    }
     const dim3 grid((nvec + kPoolBX - 1) / kPoolBX, splits, batch);
-    mean_pool_kernel<T><<<grid, dim3(kPoolBX, kPoolBY), 0, stream>>>(x, out, (float *) scratch, tickets, seq, hidden,
-                                                                     nvec, splits, chunk);
+    mean_pool_kernel<T, kPoolBX, kPoolBY><<<grid, dim3(kPoolBX, kPoolBY), 0, stream>>>(x, out, (float *) scratch, tickets,
+                                                                                      seq, hidden, nvec, splits, chunk);
     return check_launch();
 }
 

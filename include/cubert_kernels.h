@@ -207,7 +207,7 @@ int cubk_mean_pool_f16(const void *x, int batch, int seq, int hidden, void *out,
  * calling path: latency-critical serving loops that ban calls which can take the driver's allocation
  * lock, plug-ins whose host process owns all device memory, sandboxes that filter allocator calls.
  *   - Shapes whose partial sums exceed the array (more than CUBK_STATIC_POOL_SCRATCH_BYTES; e.g.
- *     binary16 [70, 512, 1024] needs 560 KiB) are refused with CUBK_ERR_SCRATCH before anything runs.
+ *     binary16 [9, 512, 4096] needs 720 KiB) are refused with CUBK_ERR_SCRATCH before anything runs.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
  *     that device current); make that first call outside any stream capture.
  *   - All calls on a device share the one array. It keeps whatever the previous call left: every partial

@@ -469,7 +469,7 @@ def test_embed_gather_bit_exact(dtype, width, idt):
 
 @pytest.mark.parametrize("t", DTYPES)
 @pytest.mark.parametrize("batch,seq,hidden", [(2, 3, 2), (3, 5, 7), (4, 32, 768), (2, 512, 1024), (64, 512, 1024),
-                                              (1, 128, 768), (300, 16, 64), (2, 100, 200)])
+                                              (1, 128, 768), (300, 16, 64), (2, 100, 200), (80, 200, 1000), (700, 128, 24)])
 def test_mean_pool(oracle, t, batch, seq, hidden):
     rng = np.random.default_rng(batch + seq + hidden)
     x, xh = _prep(rng.standard_normal((batch, seq, hidden)), t)

@@ -69,6 +69,7 @@ WORKLOADS = {
                               "output pooled_output"),
 }
 WORKLOAD = WORKLOADS["base_seq128"]
+WORKLOAD_NAME = "base_seq128"
 UNIT = "sequences/s"
 L2_NOTE = ("no explicit L2 flush: one step streams the model's weights (218 MB or more) and >1 GB of activations, "
            "far more than the 126 MB L2")
@@ -424,7 +425,7 @@ def run_ours(args):
     # reported raw (event time as measured) first; `frac_net_of_event_overhead` takes only this floor off.
     overhead_us = kernels.get("event_overhead", {}).get("us_per_launch")
     from cubert_b200 import kernels as kernel_lib
-    workload_name = [k for k, v in WORKLOADS.items() if v is WORKLOAD][0]
+    workload_name = WORKLOAD_NAME
     traffic = ncu_traffic(top, workload_name, kernel_lib.load().cubk_version(), switches_at_defaults(os.environ))
     roofline = {"bound": "hbm", "kernel": top, "achieved": ours[top]["gbs"], "peak": peak, "peak_kind": peak_kind,
                 "unit": "GB/s", "frac": ours[top]["gbs"] / peak,
@@ -488,9 +489,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="base_seq128", choices=sorted(WORKLOADS))
+    ap.add_argument("--cpu-sample", type=int, default=0,
+                    help="sequences per step of the CPU reference (default: the workload's bounded sample)")
     args = ap.parse_args()
-    global WORKLOAD
+    global WORKLOAD, WORKLOAD_NAME
     WORKLOAD = WORKLOADS[args.workload]
+    WORKLOAD_NAME = args.workload
+    if args.cpu_sample > 0:
+        WORKLOAD = dict(WORKLOAD, cpu_sample=min(args.cpu_sample, WORKLOAD["batch"]))
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference_arm(args)

@@ -8,6 +8,7 @@
 #include <iostream>
 
 #include "cubert_kernels.h"
+#include "key_extents.h"
 
 namespace cubert {
 
@@ -489,25 +490,14 @@ void Bert<T>::build_key_plan(size_t batch_size, const int8_t *input_mask) {
     }
     // per-group products want few distinct extents; K4 alone can use them vector by vector
     const int granule = key_group_gemms_ ? key_granule_ : 8;
-    int count[kMaxKeyGroups + 2] = {};
-    const int buckets = (int) ((S + granule - 1) / granule);   // extent = bucket * granule, capped at S
-    if (key_group_gemms_ && buckets > kMaxKeyGroups) {
+    if (key_group_gemms_ && (int) ((S + granule - 1) / granule) > kMaxKeyGroups) {
         return;
     }
     int64_t columns = 0;
     uint64_t hash = 1469598103934665603ull;
     for (size_t b = 0; b < batch_size; ++b) {
-        const int8_t *m = input_mask + b * S;
-        int last = (int) S - 1;
-        while (last >= 0 && m[last] == 0) {
-            --last;
-        }
-        int extent = last < 0 ? (int) S : (last / granule + 1) * granule;
-        extent = extent > (int) S ? (int) S : extent;
+        const int extent = key_extent(input_mask + b * S, (int) S, granule);
         seq_extent_[b] = extent;
-        if (key_group_gemms_) {
-            count[(extent + granule - 1) / granule] += 1;
-        }
         columns += extent;
         hash = (hash ^ (uint64_t) extent) * 1099511628211ull;
     }
@@ -519,21 +509,10 @@ void Bert<T>::build_key_plan(size_t batch_size, const int8_t *input_mask) {
     int32_t *extents = h_plan_ + max_batch_size;
     int groups = 0;
     if (key_group_gemms_) {
-        // counting sort: groups in order of growing extent
-        int first[kMaxKeyGroups + 2] = {};
-        int at = 0;
-        for (int k = 1; k <= buckets; ++k) {
-            first[k] = at;
-            if (count[k] > 0) {
-                plan_.start[groups] = at;
-                plan_.extent[groups] = k * granule > (int) S ? (int) S : k * granule;
-                ++groups;
-            }
-            at += count[k];
-        }
-        plan_.start[groups] = at;
-        for (size_t b = 0; b < batch_size; ++b) {
-            order[first[(seq_extent_[b] + granule - 1) / granule]++] = (int32_t) b;
+        groups = group_by_extent(seq_extent_.data(), batch_size, (int) S, granule, kMaxKeyGroups, order, plan_.start,
+                                 plan_.extent);
+        if (groups == 0) {
+            return;
         }
     }
     for (size_t b = 0; b < batch_size; ++b) {

@@ -27,8 +27,10 @@ constexpr int kPoolUnroll = 4;
 constexpr int kPoolNarrowBX = 8;
 constexpr int kPoolNarrowBY = 32;
 
-template <typename T, int BX, int BY>
-__global__ void __launch_bounds__(BX *BY)
+// Compiled for eight resident blocks per SM (at most 32 registers): the grids this is launched with, up to
+// 8 * 148 blocks, then run as ONE wave; with six resident blocks 1024 blocks took 1.15 waves, i.e. two.
+template <typename T, int BX, int BY, bool SPLIT>
+__global__ void __launch_bounds__(BX *BY, 8)
 mean_pool_kernel(const T *x, T *out, float *partial, unsigned int *tickets, int seq, int hidden, int nvec, int splits,
                  int chunk) {
     constexpr int EPV = Vec<T>::EPV;
@@ -83,7 +85,7 @@ mean_pool_kernel(const T *x, T *out, float *partial, unsigned int *tickets, int 
             acc[e] = t;
         }
     }
-    if (splits > 1) {
+    if (SPLIT) {
         if (writer) {
             float4 *dst = reinterpret_cast<float4 *>(partial + ((size_t) b * splits + split) * hidden + (size_t) cv * EPV);
 #pragma unroll
@@ -238,13 +240,18 @@ int mean_pool(const T *x, int batch, int seq, int hidden, T *out, void *scratch,
     const int chunk = (seq + splits - 1) / splits;
     if (splits == 1 && mean_pool_narrow(batch, seq, nvec)) {
         const dim3 grid((nvec + kPoolNarrowBX - 1) / kPoolNarrowBX, 1, batch);
-        mean_pool_kernel<T, kPoolNarrowBX, kPoolNarrowBY><<<grid, dim3(kPoolNarrowBX, kPoolNarrowBY), 0, stream>>>(
+        mean_pool_kernel<T, kPoolNarrowBX, kPoolNarrowBY, false><<<grid, dim3(kPoolNarrowBX, kPoolNarrowBY), 0, stream>>>(
             x, out, nullptr, nullptr, seq, hidden, nvec, 1, chunk);
         return check_launch();
     }
     const dim3 grid((nvec + kPoolBX - 1) / kPoolBX, splits, batch);
-    mean_pool_kernel<T, kPoolBX, kPoolBY><<<grid, dim3(kPoolBX, kPoolBY), 0, stream>>>(x, out, (float *) scratch, tickets,
-                                                                                      seq, hidden, nvec, splits, chunk);
+    if (splits > 1) {
+        mean_pool_kernel<T, kPoolBX, kPoolBY, true><<<grid, dim3(kPoolBX, kPoolBY), 0, stream>>>(
+            x, out, (float *) scratch, tickets, seq, hidden, nvec, splits, chunk);
+    } else {
+        mean_pool_kernel<T, kPoolBX, kPoolBY, false><<<grid, dim3(kPoolBX, kPoolBY), 0, stream>>>(
+            x, out, nullptr, nullptr, seq, hidden, nvec, 1, chunk);
+    }
     return check_launch();
 }
 

@@ -3,6 +3,8 @@
 //   graph <float|half> <path>      open a frozen graph; prints "ok <tensors> <checksum>" or "rejected: <why>"
 //   model <float|half> <path> <seq_length> <layers> <heads>   open it and check every tensor's size against the
 //                                  geometry, as cuBERT_open does before building replicas; "ok" or "rejected: <why>"
+//   extents <seq> <granule> <max_groups> <hex of the int8 mask, batch * seq bytes>
+//                                  key extents of every row and their grouping; prints "ok e0 e1 ... | order ... | start ... | extent ..."
 //   tok <lower 0|1> <vocab path> <max_seq_length> <hex of UTF-8 text>    prints "ok <ids...>" or "rejected: <why>"
 // A malformed input must end in "rejected" (a C++ exception), never in a sanitizer report or a crash.
 #include <cstdint>
@@ -15,6 +17,7 @@
 #include <vector>
 
 #include "frozen_graph.h"
+#include "key_extents.h"
 #include "runtime.h"
 #include "tokenizer.h"
 
@@ -85,6 +88,31 @@ int main() {
                 } else {
                     open_model<float>(path, seq_length, layers, heads);
                 }
+            } else if (cmd == "extents") {
+                int seq = 0, granule = 0, max_groups = 0;
+                std::string hex;
+                in >> seq >> granule >> max_groups >> hex;
+                const std::string raw = unhex(hex);
+                if (seq <= 0 || granule <= 0 || raw.size() % (size_t) seq != 0) {
+                    throw std::invalid_argument("bad extents command");
+                }
+                const size_t batch = raw.size() / (size_t) seq;
+                std::vector<int32_t> extents(batch), order(batch);
+                std::vector<int> start((size_t) max_groups + 2), group_extent((size_t) max_groups + 1);
+                for (size_t b = 0; b < batch; ++b) {
+                    extents[b] = cubert::key_extent(reinterpret_cast<const int8_t *>(raw.data()) + b * (size_t) seq, seq, granule);
+                }
+                const int groups = cubert::group_by_extent(extents.data(), batch, seq, granule, max_groups, order.data(),
+                                                           start.data(), group_extent.data());
+                std::printf("ok");
+                for (int32_t e : extents) std::printf(" %d", e);
+                std::printf(" | order");
+                for (size_t i = 0; groups > 0 && i < batch; ++i) std::printf(" %d", order[i]);
+                std::printf(" | start");
+                for (int g = 0; groups > 0 && g <= groups; ++g) std::printf(" %d", start[(size_t) g]);
+                std::printf(" | extent");
+                for (int g = 0; g < groups; ++g) std::printf(" %d", group_extent[(size_t) g]);
+                std::printf("\n");
             } else if (cmd == "tok") {
                 int lower = 1;
                 std::string vocab, hex;

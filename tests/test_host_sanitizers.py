@@ -119,6 +119,42 @@ def test_model_whose_tensor_sizes_disagree_with_its_geometry_is_rejected(harness
     assert all(l.startswith("rejected: ") and "invalid" in l for l in lines[expect_ok:]), lines[expect_ok:]
 
 
+def test_key_extents_and_their_grouping(harness):
+    """The host arithmetic behind 'attention over kept keys only': extent = position after the last non-zero mask
+    entry, rounded up to the granule, the whole sequence when nothing is kept; sequences counting-sorted by extent."""
+    rng = np.random.default_rng(9)
+    commands, cases = [], []
+    for seq, granule, max_groups, batch in ((128, 32, 16, 37), (128, 8, 16, 5), (512, 64, 16, 64), (40, 32, 16, 9),
+                                            (64, 8, 4, 6), (1, 8, 16, 3), (100, 8, 16, 50)):
+        lengths = rng.integers(0, seq + 1, batch)
+        mask = np.zeros((batch, seq), np.int8)
+        for b, n in enumerate(lengths):
+            if n > 0:
+                mask[b, :n] = rng.integers(-3, 4, n)
+                mask[b, n - 1] = rng.choice([-7, 1, 99])         # the last kept key sits at n - 1; holes before it are fine
+        cases.append((seq, granule, max_groups, mask, lengths))
+        commands.append("extents %d %d %d %s" % (seq, granule, max_groups, mask.tobytes().hex()))
+    lines = run(harness, commands)
+    assert len(lines) == len(cases)
+    for line, (seq, granule, max_groups, mask, lengths) in zip(lines, cases):
+        assert line.startswith("ok "), line
+        parts = [p.split() for p in line[3:].split("|")]
+        extents = np.array(parts[0], int)
+        want = np.where(lengths == 0, seq, np.minimum((lengths + granule - 1) // granule * granule, seq))
+        assert np.array_equal(extents, want), (seq, granule)
+        order, start, group_extent = (np.array(p[1:], int) for p in parts[1:4])
+        buckets = (seq + granule - 1) // granule
+        if buckets > max_groups:
+            assert order.size == 0 and group_extent.size == 0       # too many distinct extents: no grouping
+            continue
+        assert sorted(order.tolist()) == list(range(len(lengths)))            # a permutation
+        assert np.all(np.diff(extents[order]) >= 0)                           # growing extent
+        assert start[0] == 0 and start[-1] == len(lengths) and np.all(np.diff(start) > 0)
+        for g, e in enumerate(group_extent):
+            assert np.all(extents[order[start[g]:start[g + 1]]] == e)
+        assert np.all(np.diff(group_extent) > 0)
+
+
 def test_tokenizer_on_valid_and_malformed_text(harness, tmp_path):
     vocab = ["[PAD]", "[UNK]", "[CLS]", "[SEP]", "hello", "world", "##s", "un", "##aff", "##able", "!", ",", "中", "文",
              "e", "cafe", "é"]

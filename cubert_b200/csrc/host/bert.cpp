@@ -270,8 +270,10 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
         seq_extent_.assign(B, (int32_t) S);
         CUDA_CHECK(cudaMallocHost(reinterpret_cast<void **>(&h_plan_), sizeof(int32_t) * 2 * B));
         plan_dev_.allocate(sizeof(int32_t) * 2 * B);
-        for (DeviceBuffer *sorted : {&q_sorted_, &k_sorted_, &v_sorted_, &score_sorted_, &ctx_sorted_}) {
-            sorted->allocate(sizeof(void *) * B * heads);
+        if (key_group_gemms_) {
+            for (DeviceBuffer *sorted : {&q_sorted_, &k_sorted_, &v_sorted_, &score_sorted_, &ctx_sorted_}) {
+                sorted->allocate(sizeof(void *) * B * heads);
+            }
         }
     }
     upload(q_ptrs_, qp.data(), qp.size());

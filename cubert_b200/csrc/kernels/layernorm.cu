@@ -606,8 +606,10 @@ bias_residual_ln_rows_kernel(const T *x, const T *bias, const T *residual, const
 
 // K1. Tokens are walked position-major as in embed_ln_kernel (the position row stays in registers
 // as float32 while a warp works through sequences at one position); the token-type rows sit in shared
-// memory beside gamma and beta (float32, up to kMaxTypeRowsSmem of them); the token indices are read
-// two steps ahead and the gathered word row one step ahead of the row being normalised.
+// memory beside gamma and beta (float32, up to kMaxTypeRowsSmem of them); the indices of the next token
+// are read while the current row is normalised. The gathered word row is NOT requested ahead: holding a
+// second row in registers pushed the kernel past the register budget of three resident blocks per SM, and
+// the version that spilled to stay there was slower (20.4 us against 19.4 us on 32768 x 768 binary16).
 constexpr int kMaxTypeRowsSmem = 4;
 
 template <typename T, int VPT, int MIN_BLOCKS>
@@ -640,27 +642,24 @@ embed_ln_rows_kernel(const int32_t *ids, const int8_t *segment_ids, const T *wor
     const uint32_t j_begin = w * share + min(w, extra);
     const uint32_t j_count = share + (w < extra ? 1u : 0u);
 
-    // (s, b) of the step whose indices are fetched next; token = b * seq + s
-    uint32_t fs = j_begin / batch;
-    uint32_t fb = j_begin - fs * batch;
-    uint32_t fetched = 0;
-    int id_q = 0, seg_q = 0;       // indices of the row after the one in flight
-    auto fetch_indices = [&]() {   // reads the indices of step `fetched`, if there is one
-        if (fetched < j_count) {
-            const uint32_t token = fb * seq + fs;
-            id_q = ids[token];
-            seg_q = segment_ids[token];
-            if (++fb == batch) {
-                fb = 0;
-                ++fs;
-            }
-        }
-        ++fetched;
-    };
-    uint4 rw[VPT];
-    int seg_in_flight = 0;
-    auto issue_word_row = [&]() {  // requests word[id_q]; its segment id travels with it
-        int wid = id_q, tid = seg_q;
+    uint32_t s = j_begin / batch;       // position and sequence of the current step; token = b * seq + s
+    uint32_t b = j_begin - s * batch;
+    int id = 0, seg = 0;                // indices of the current step
+    if (j_count > 0) {
+        id = ids[b * seq + s];
+        seg = segment_ids[b * seq + s];
+    }
+    stage_param<T>(gamma, s_params, NVEC, threadIdx.x, kRowsBlock);
+    stage_param<T>(beta, s_params + PV, NVEC, threadIdx.x, kRowsBlock);
+    for (int t = 0; t < type_vocab; ++t) {
+        stage_param<T>(type + (size_t) t * (NVEC * EPV), s_params + (2 + t) * PV, NVEC, threadIdx.x, kRowsBlock);
+    }
+    __syncthreads();
+
+    float2 pos_row[VPT][PAIRS];
+    bool new_pos = true;
+    for (uint32_t step = 0; step < j_count; ++step) {
+        int wid = id, tid = seg;
         uint32_t bad = 0;
         if (wid < 0 || wid >= vocab) {
             bad |= CUBK_STATUS_BAD_TOKEN_ID;
@@ -673,38 +672,32 @@ embed_ln_rows_kernel(const int32_t *ids, const int8_t *segment_ids, const T *wor
         if (bad != 0 && status != nullptr && lane == 0) {
             atomicOr(status, bad);
         }
-        seg_in_flight = tid;
+        uint4 rw[VPT];
         const uint4 *src = wv + (size_t) wid * NVEC;
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
             rw[k] = __ldg(src + 32 * k);
         }
-    };
-
-    fetch_indices();
-    if (j_count > 0) {
-        issue_word_row();
-    }
-    fetch_indices();
-    stage_param<T>(gamma, s_params, NVEC, threadIdx.x, kRowsBlock);
-    stage_param<T>(beta, s_params + PV, NVEC, threadIdx.x, kRowsBlock);
-    for (int t = 0; t < type_vocab; ++t) {
-        stage_param<T>(type + (size_t) t * (NVEC * EPV), s_params + (2 + t) * PV, NVEC, threadIdx.x, kRowsBlock);
-    }
-    __syncthreads();
-
-    float2 pos_row[VPT][PAIRS];
-    uint32_t s = j_begin / batch;
-    uint32_t b = j_begin - s * batch;
-    bool new_pos = true;
-    for (uint32_t step = 0; step < j_count; ++step) {
         if (new_pos) {  // uniform within the warp
 #pragma unroll
             for (int k = 0; k < VPT; ++k) {
                 Vec2<T>::unpack(__ldg(pv + (size_t) s * NVEC + 32 * k), pos_row[k]);
             }
         }
-        const float4 *s_trow = s_type + seg_in_flight * PV;
+        uint4 *dst = ov + ((size_t) b * seq + s) * NVEC;
+        // on to the next step's place, and its indices while this row's loads are in flight
+        new_pos = false;
+        if (++b == batch) {
+            b = 0;
+            ++s;
+            new_pos = true;
+        }
+        if (step + 1 < j_count) {
+            id = ids[b * seq + s];
+            seg = segment_ids[b * seq + s];
+        }
+
+        const float4 *s_trow = s_type + tid * PV;
         float2 v[VPT][PAIRS];
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
@@ -719,18 +712,6 @@ embed_ln_rows_kernel(const int32_t *ids, const int8_t *segment_ids, const T *wor
             for (int e = 0; e < PAIRS; ++e) {
                 v[k][e] = add2(v[k][e], t[e]);      //             + type, the reference's order
             }
-        }
-        uint4 *dst = ov + ((size_t) b * seq + s) * NVEC;
-        // the raw registers are free again: request the next word row, then the indices after it
-        if (step + 1 < j_count) {
-            issue_word_row();
-        }
-        fetch_indices();
-        new_pos = false;
-        if (++b == batch) {
-            b = 0;
-            ++s;
-            new_pos = true;
         }
         normalise_store_row<T, VPT>(v, lane, inv_hidden, s_gamma, s_beta, dst);
     }
@@ -973,7 +954,8 @@ bool launch_embed_bulk_depth(const int32_t *ids, const int8_t *segment_ids, cons
 
 // Launch of the exact-width K1 for one VPT; false = the staged rows do not fit shared memory.
 // Rows of three vectors per lane (hidden 768 in binary16) are compiled for three resident blocks per
-// SM (80 registers, a few spilled words): 20.1 us against 25.2 us without the cap on 32768 tokens.
+// SM (79 registers, nothing spilled), rows of four (hidden 1024) for two: 19.4 us on 32768 tokens of 768
+// against 26 us with the registers the compiler takes when left alone (136, one block per SM).
 template <typename T, int VPT>
 bool launch_embed_rows(const int32_t *ids, const int8_t *segment_ids, const T *word, const T *pos, const T *type,
                        const T *gamma, const T *beta, T *out, int64_t tokens, int batch, int seq, int hidden,
@@ -983,7 +965,7 @@ bool launch_embed_rows(const int32_t *ids, const int8_t *segment_ids, const T *w
     if (smem > kMaxParamSmem) {
         return false;
     }
-    auto kernel = embed_ln_rows_kernel<T, VPT, (VPT == 3 ? 3 : 1)>;
+    auto kernel = embed_ln_rows_kernel<T, VPT, (VPT == 3 ? 3 : (VPT == 4 ? 2 : 1))>;
     int64_t grid = (tokens + (kRowsBlock / 32) - 1) / (kRowsBlock / 32);
     const int resident = resident_blocks(kernel, kRowsBlock, smem, &cache);
     if (grid > resident) {

@@ -178,8 +178,8 @@ NCU_TRAFFIC = {
                              note="100.7 MB read + 7.5 MB written"),
     "masked_softmax": dict(bytes=123932032, kernel="masked_softmax_kernel<__half, 4, 4, 1, 256, true, true>",
                            note="77.1 MB read (scores past each sequence's last kept key are not read) + 46.8 MB written"),
-    "embed_ln": dict(bytes=33222528, kernel="embed_ln_rows_kernel<__half, 3, 3>",
-                     note="28.8 MB read + 4.4 MB written: word rows are served by L2"),
+    "embed_ln": dict(bytes=29022592, kernel="embed_ln_rows_kernel<__half, 3, 3>",
+                     note="26.0 MB read + 3.0 MB written: word rows are served by L2"),
 }
 NCU_TRAFFIC_SOURCE = dict(workload="base_seq128", cubk_version=110,
                           profile="profiles/fused_kernels_in_bench_f16_ncu_full.md")

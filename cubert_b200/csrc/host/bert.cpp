@@ -25,6 +25,7 @@ struct K<float> {
     static constexpr auto bias_gelu = cubk_bias_gelu_f32;
     static constexpr auto masked_softmax = cubk_masked_softmax_f32;
     static constexpr auto masked_softmax_extents = cubk_masked_softmax_extents_f32;
+    static constexpr auto attention_small = cubk_attention_small_f32;
     static constexpr auto bias_tanh = cubk_bias_tanh_f32;
     static constexpr auto mean_pool = cubk_mean_pool_f32;
     static constexpr auto logits_probs = cubk_logits_probs_f32;
@@ -38,6 +39,7 @@ struct K<__half> {
     static constexpr auto bias_gelu = cubk_bias_gelu_f16;
     static constexpr auto masked_softmax = cubk_masked_softmax_f16;
     static constexpr auto masked_softmax_extents = cubk_masked_softmax_extents_f16;
+    static constexpr auto attention_small = cubk_attention_small_f16;
     static constexpr auto bias_tanh = cubk_bias_tanh_f16;
     static constexpr auto mean_pool = cubk_mean_pool_f16;
     static constexpr auto logits_probs = cubk_logits_probs_f16;
@@ -180,6 +182,10 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
         logits_.allocate(sizeof(T) * B * num_labels);
         probs_.allocate(sizeof(T) * B * num_labels);
     }
+
+    // short sequences and heads of 64: requests of up to kSmallAttentionTokens tokens run the attention of a
+    // layer as one launch (cubk_attention_small_*) instead of two batched products and K4
+    small_attention_ = S <= 64 && H == heads * 64 && env_int("CUBERT_SMALL_ATTENTION", 1) != 0;
 
     // first-token pooler + a small classifier: K5a and K5c run as one launch (cubk_pooler_head_*)
     {
@@ -482,6 +488,7 @@ void Bert<T>::wait_for_staging() {
 
 // ------------------------------------------------------------------ attention over kept keys only
 constexpr size_t kMinPositionsForKeyPlan = 2048;
+constexpr size_t kSmallAttentionTokens = 2048;   // up to here a layer's attention is one launch on short sequences
 
 template <typename T>
 void Bert<T>::build_key_plan(size_t batch_size, const int8_t *input_mask) {
@@ -829,41 +836,48 @@ void Bert<T>::forward_layers(size_t l_begin, size_t l_end, size_t b0, size_t nb,
             KERNEL_CHECK(cubk_scatter_rows(tok, N, qkv_out, 3 * H, (int) e, qkv_.get(), (int) R, st));
         }
 
-        // scores[b, i, h, j] = (1/sqrt(d)) * sum_c K[b,j,h,c] * Q[b,i,h,c]   (op_att/BatchMatMul.cpp:57-68)
-        // With a key plan only the key columns j below each sequence's extent exist: one product per group
-        // of equal extent over the sorted pointer arrays, or (a range of sequences) the range's largest extent.
-        begin(CUBERT_B200_K_GEMM);
-        if (grouped) {
-            grouped_products(true, S, d, heads, H, att_scale, algo_qk_);
+        if (small_attention_ && packed == 0 && R <= (int64_t) kSmallAttentionTokens) {
+            // the whole attention of the layer in one launch (counted with K4, whose bytes it would have moved)
+            begin(CUBERT_B200_K_MASKED_SOFTMAX);
+            KERNEL_CHECK(K<T>::attention_small(qkv, mask, B, S, heads, H, att_scale, context, st));
+            end(CUBERT_B200_K_MASKED_SOFTMAX, 2 * R * heads * S * e + R);
         } else {
-            blas_->gemm_batched<T>(true, false, keys, S, d, att_scale, k_ptrs_.template as<const T *>() + p0, 3 * H,
-                                   q_ptrs_.template as<const T *>() + p0, 3 * H, 0.f, score_ptrs_.template as<T *>() + p0,
-                                   S * heads, B * heads, algo_qk_);
-        }
-        end(CUBERT_B200_K_GEMM, 0);
+            // scores[b, i, h, j] = (1/sqrt(d)) * sum_c K[b,j,h,c] * Q[b,i,h,c]   (op_att/BatchMatMul.cpp:57-68)
+            // With a key plan only the key columns j below each sequence's extent exist: one product per group
+            // of equal extent over the sorted pointer arrays, or (a range of sequences) the range's largest extent.
+            begin(CUBERT_B200_K_GEMM);
+            if (grouped) {
+                grouped_products(true, S, d, heads, H, att_scale, algo_qk_);
+            } else {
+                blas_->gemm_batched<T>(true, false, keys, S, d, att_scale, k_ptrs_.template as<const T *>() + p0, 3 * H,
+                                       q_ptrs_.template as<const T *>() + p0, 3 * H, 0.f, score_ptrs_.template as<T *>() + p0,
+                                       S * heads, B * heads, algo_qk_);
+            }
+            end(CUBERT_B200_K_GEMM, 0);
 
-        // K4: mask + softmax in place over rows [B*S*heads, S]
-        begin(CUBERT_B200_K_MASKED_SOFTMAX);
-        if (plan_.active) {
-            KERNEL_CHECK(K<T>::masked_softmax_extents(scores, mask, extents, grouped ? 0 : keys, R * heads, (int64_t) S * heads,
-                                                      S, 1.0f, scores, st));
-        } else {
-            KERNEL_CHECK(K<T>::masked_softmax(scores, mask, R * heads, (int64_t) S * heads, S, 1.0f, scores, st));
-        }
-        // charged with the bytes of the whole score matrix (the figure the roofline is quoted on), whatever
-        // the key extents let it skip
-        end(CUBERT_B200_K_MASKED_SOFTMAX, 2 * R * heads * S * e + R);
+            // K4: mask + softmax in place over rows [B*S*heads, S]
+            begin(CUBERT_B200_K_MASKED_SOFTMAX);
+            if (plan_.active) {
+                KERNEL_CHECK(K<T>::masked_softmax_extents(scores, mask, extents, grouped ? 0 : keys, R * heads, (int64_t) S * heads,
+                                                          S, 1.0f, scores, st));
+            } else {
+                KERNEL_CHECK(K<T>::masked_softmax(scores, mask, R * heads, (int64_t) S * heads, S, 1.0f, scores, st));
+            }
+            // charged with the bytes of the whole score matrix (the figure the roofline is quoted on), whatever
+            // the key extents let it skip
+            end(CUBERT_B200_K_MASKED_SOFTMAX, 2 * R * heads * S * e + R);
 
-        // context[b, i, h, c] = sum_j V[b,j,h,c] * P[b,i,h,j]   (op_att/BatchMatMul.cpp:124-135)
-        begin(CUBERT_B200_K_GEMM);
-        if (grouped) {
-            grouped_products(false, S, d, heads, H, 1.f, algo_qkv_);
-        } else {
-            blas_->gemm_batched<T>(false, false, d, S, keys, 1.f, v_ptrs_.template as<const T *>() + p0, 3 * H,
-                                   score_ptrs_.template as<const T *>() + p0, S * heads, 0.f, ctx_ptrs_.template as<T *>() + p0,
-                                   H, B * heads, algo_qkv_);
+            // context[b, i, h, c] = sum_j V[b,j,h,c] * P[b,i,h,j]   (op_att/BatchMatMul.cpp:124-135)
+            begin(CUBERT_B200_K_GEMM);
+            if (grouped) {
+                grouped_products(false, S, d, heads, H, 1.f, algo_qkv_);
+            } else {
+                blas_->gemm_batched<T>(false, false, d, S, keys, 1.f, v_ptrs_.template as<const T *>() + p0, 3 * H,
+                                       score_ptrs_.template as<const T *>() + p0, S * heads, 0.f, ctx_ptrs_.template as<T *>() + p0,
+                                       H, B * heads, algo_qkv_);
+            }
+            end(CUBERT_B200_K_GEMM, 0);
         }
-        end(CUBERT_B200_K_GEMM, 0);
 
         // attention output projection, then K2: LayerNorm(dense + bias + layer input)
         const T *ctx = context;

@@ -348,6 +348,128 @@ int masked_softmax(const T *scores, const int8_t *mask, int64_t rows, int64_t ro
     return check_launch();
 }
 
+// ------------------------------------------------------------------ whole attention of short sequences
+// For requests of a few hundred tokens the forward pass is bound by its chain of dependent launches, not
+// by work: the scores of one (sequence, head) are a 32 x 32 or 64 x 64 tile. This kernel does Q.K^T, the
+// masked softmax and P.V of one (sequence, head) per block on the ordinary float32 pipes, in place of two
+// batched library products and K4: two launches fewer per layer. It rounds where the three-launch path
+// rounds (scores and probabilities pass through the storage type), so the results differ from that
+// path only by the order of the additions inside the two dot products.
+//   qkv      [batch * seq, 3 * hidden]: per token Q | K | V, head h at columns h * 64 of each part
+//   context  [batch * seq, hidden]
+constexpr int kSmallHeadDim = 64;
+constexpr int kSmallAttentionWarps = 4;
+
+template <typename T, int SMAX>
+__global__ void __launch_bounds__(32 * kSmallAttentionWarps)
+small_attention_kernel(const T *qkv, const int8_t *mask, T *context, int seq, int heads, int hidden, float scale) {
+    constexpr int D = kSmallHeadDim;
+    constexpr int KPL = SMAX / 32;  // keys per lane
+    __shared__ float s_k[SMAX][D + 1];
+    __shared__ float s_v[SMAX][D];
+    __shared__ float s_q[kSmallAttentionWarps][D];
+    __shared__ float s_madd[SMAX];
+    const int b = blockIdx.x / heads;
+    const int h = blockIdx.x - b * heads;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const size_t row_stride = 3 * (size_t) hidden;
+    const T *base = qkv + (size_t) b * seq * row_stride + (size_t) h * D;
+
+    for (int i = threadIdx.x; i < seq * D; i += blockDim.x) {
+        const int j = i / D, c = i - j * D;
+        s_k[j][c] = to_float<T>(base[(size_t) j * row_stride + hidden + c]);
+        s_v[j][c] = to_float<T>(base[(size_t) j * row_stride + 2 * hidden + c]);
+    }
+    for (int j = threadIdx.x; j < SMAX; j += blockDim.x) {
+        s_madd[j] = (j < seq && (mask == nullptr || mask[(size_t) b * seq + j] != 0)) ? 0.f : kMaskedScore;
+    }
+    __syncthreads();
+
+    for (int i = warp; i < seq; i += kSmallAttentionWarps) {
+        // the query row, shared by the warp
+        for (int c = lane; c < D; c += 32) {
+            s_q[warp][c] = to_float<T>(base[(size_t) i * row_stride + c]);
+        }
+        __syncwarp();
+        float v[KPL];
+        float mx = -3.0e38f;
+#pragma unroll
+        for (int u = 0; u < KPL; ++u) {
+            const int j = lane + 32 * u;
+            float dot = 0.f;
+            if (j < seq) {
+#pragma unroll 16
+                for (int c = 0; c < D; ++c) {
+                    dot = fmaf(s_q[warp][c], s_k[j][c], dot);
+                }
+            }
+            // the stored score (storage precision), then the additive mask, as K4 reads it
+            v[u] = j < seq ? to_float<T>(from_float<T>(scale * dot)) + s_madd[j] : -3.0e38f;
+            mx = fmaxf(mx, v[u]);
+        }
+        mx = group_max<32>(mx);
+        float p[KPL];
+        float sum = 0.f;
+#pragma unroll
+        for (int u = 0; u < KPL; ++u) {
+            p[u] = lane + 32 * u < seq ? fast_exp2(fmaf(v[u], kLog2e, -mx * kLog2e)) : 0.f;
+            sum += p[u];
+        }
+        sum = group_sum<32>(sum);
+        const float inv = 1.f / sum;
+#pragma unroll
+        for (int u = 0; u < KPL; ++u) {
+            p[u] = to_float<T>(from_float<T>(p[u] * inv));  // the stored probability
+        }
+        // context columns 2 * lane and 2 * lane + 1
+        float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < KPL; ++u) {
+            for (int jj = 0; jj < 32; ++jj) {
+                const int j = jj + 32 * u;
+                const float pj = __shfl_sync(0xffffffffu, p[u], jj);
+                if (j < seq) {
+                    const float2 vv = *reinterpret_cast<const float2 *>(&s_v[j][2 * lane]);
+                    acc.x = fmaf(pj, vv.x, acc.x);
+                    acc.y = fmaf(pj, vv.y, acc.y);
+                }
+            }
+        }
+        T *dst = context + ((size_t) b * seq + i) * hidden + (size_t) h * D + 2 * lane;
+        if (sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(dst) & 3u) == 0) {
+            *reinterpret_cast<__half2 *>(dst) = __floats2half2_rn(acc.x, acc.y);
+        } else {
+            dst[0] = from_float<T>(acc.x);
+            dst[1] = from_float<T>(acc.y);
+        }
+        __syncwarp();  // s_q[warp] is rewritten by the next row
+    }
+}
+
+template <typename T>
+int small_attention(const T *qkv, const int8_t *mask, int batch, int seq, int heads, int hidden, float scale, T *context,
+                    cudaStream_t stream) {
+    if (qkv == nullptr || context == nullptr || batch < 0 || seq <= 0 || heads <= 0 || hidden <= 0) {
+        return CUBK_ERR_INVALID_ARG;
+    }
+    if (seq > 64 || hidden != heads * kSmallHeadDim || (int64_t) batch * heads > 0x7fffffffLL) {
+        return CUBK_ERR_UNSUPPORTED;
+    }
+    if (batch == 0) {
+        return CUBK_OK;
+    }
+    const unsigned grid = (unsigned) (batch * heads);
+    if (seq <= 32) {
+        small_attention_kernel<T, 32><<<grid, 32 * kSmallAttentionWarps, 0, stream>>>(qkv, mask, context, seq, heads, hidden,
+                                                                                    scale);
+    } else {
+        small_attention_kernel<T, 64><<<grid, 32 * kSmallAttentionWarps, 0, stream>>>(qkv, mask, context, seq, heads, hidden,
+                                                                                    scale);
+    }
+    return check_launch();
+}
+
 }  // namespace cubk
 
 extern "C" {
@@ -362,6 +484,17 @@ int cubk_masked_softmax_f16(const void *scores, const int8_t *mask, int64_t rows
                             int seq, float scale, void *out, void *stream) {
     return cubk::masked_softmax<__half>((const __half *) scores, mask, rows, rows_per_batch, seq, scale,
                                         (__half *) out, (cudaStream_t) stream);
+}
+
+int cubk_attention_small_f32(const float *qkv, const int8_t *mask, int batch, int seq, int heads, int hidden, float scale,
+                             float *context, void *stream) {
+    return cubk::small_attention<float>(qkv, mask, batch, seq, heads, hidden, scale, context, (cudaStream_t) stream);
+}
+
+int cubk_attention_small_f16(const void *qkv, const int8_t *mask, int batch, int seq, int heads, int hidden, float scale,
+                             void *context, void *stream) {
+    return cubk::small_attention<__half>((const __half *) qkv, mask, batch, seq, heads, hidden, scale, (__half *) context,
+                                         (cudaStream_t) stream);
 }
 
 int cubk_masked_softmax_extents_f32(const float *scores, const int8_t *mask, const int32_t *key_extents, int zero_to,

@@ -49,6 +49,7 @@ _SIGNATURES = {
     "cubk_bias_gelu_{t}": (_I, [_P, _P, _L, _I, _P, _P]),
     "cubk_masked_softmax_{t}": (_I, [_P, _P, _L, _L, _I, _F, _P, _P]),
     "cubk_masked_softmax_extents_{t}": (_I, [_P, _P, _P, _I, _L, _L, _I, _F, _P, _P]),
+    "cubk_attention_small_{t}": (_I, [_P, _P, _I, _I, _I, _I, _F, _P, _P]),
     "cubk_bias_tanh_{t}": (_I, [_P, _P, _L, _I, _P, _P]),
     "cubk_mean_pool_scratch_bytes": (_Z, [_I, _I, _I]),
     "cubk_mean_pool_{t}": (_I, [_P, _I, _I, _I, _P, _P, _Z, _P]),

@@ -175,6 +175,22 @@ int cubk_masked_softmax_extents_f16(const void *scores, const int8_t *mask, cons
                                     int zero_to, int64_t rows, int64_t rows_per_batch, int seq, float scale,
                                     void *out, void *stream);
 
+/* Whole attention of short sequences in one launch: for every (sequence, head)
+ *   scores = scale * Q.K^T, rounded to the storage type;  P = masked softmax(scores) as cubk_masked_softmax_*,
+ *   rounded to the storage type;  context = P.V
+ * i.e. what the reference's Att_Q_K product, mask, softmax and Att_QK_V product compute
+ * (src/cuBERT/op_att/AttentionSelf.cpp:96-111, op_att/BatchMatMul.cpp:57-68,124-135, op/Softmax.cpp:19-35), rounding
+ * where those round, for the sizes at which a forward pass is bound by its chain of launches rather than by
+ * work (serving requests of a few sequences): one launch in place of two batched library products and K4.
+ * qkv [batch * seq, 3 * hidden] holds per token Q | K | V (head h at columns 64 * h of each part); mask int8
+ * [batch, seq] over the keys or NULL; context [batch * seq, hidden]. Runs on the float32 pipes (no tensor
+ * cores): CUBK_ERR_UNSUPPORTED unless seq <= 64 and hidden == 64 * heads; the caller decides up to which
+ * size it pays (the host library: requests of at most 2048 tokens). */
+int cubk_attention_small_f32(const float *qkv, const int8_t *mask, int batch, int seq, int heads, int hidden,
+                             float scale, float *context, void *stream);
+int cubk_attention_small_f16(const void *qkv, const int8_t *mask, int batch, int seq, int heads, int hidden,
+                             float scale, void *context, void *stream);
+
 /* ---- K5a: bias + tanh (BERT pooler activation) ---------------------------------------------------
  * out = tanh(x (+ bias)). Replaces tanh_<T> (src/cuBERT/op_bert/BertPooler.h:9,
  * op_bert/BertPooler.cu:14-26) plus the bias prefill of BertPooler<T>::compute

@@ -87,6 +87,14 @@ def pooler_head(x, pooler_bias, weights, bias, t="f32", want_probs=True):
     return rc, pooled, logits, probs
 
 
+def attention_small(qkv, mask, batch, seq, heads, scale, t="f32"):
+    """qkv: torch [batch * seq, 3 * hidden]; returns (status, context [batch * seq, hidden])."""
+    hidden = qkv.shape[1] // 3
+    ctx = torch.full((batch * seq, hidden), float("nan"), dtype=qkv.dtype, device="cuda")
+    rc = fn("attention_small", t)(ptr(qkv), ptr(mask), batch, seq, heads, hidden, float(scale), ptr(ctx), stream())
+    return rc, ctx
+
+
 def embed_ln(ids, seg, word, pos, typ, gamma, beta, t="f32", status=None):
     b, s = ids.shape
     vocab, hidden = word.shape

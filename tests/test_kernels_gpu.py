@@ -361,6 +361,49 @@ def test_gelu_hands_on_nan_and_infinity(t):
     assert np.all(np.isfinite(got[3:6])) and abs(got[3] - 0.8413447) < 2e-3 and abs(got[4] + 0.1586553) < 2e-3
 
 
+@pytest.mark.parametrize("t", DTYPES)
+@pytest.mark.parametrize("batch,seq,heads,kind", [(1, 32, 12, "prefix"), (8, 32, 12, "random"), (32, 32, 12, "prefix"),
+                                                  (3, 64, 16, "random"), (5, 17, 2, "prefix"), (2, 49, 3, "none"),
+                                                  (4, 1, 1, "none"), (3, 32, 4, "empty_row")])
+def test_attention_of_short_sequences_in_one_launch(oracle, t, batch, seq, heads, kind):
+    """cubk_attention_small_* against the three steps it stands for, computed on the host with the reference's
+    softmax: scores = scale * Q.K^T rounded to the storage type, masked softmax rounded to the storage type, P.V."""
+    rng = np.random.default_rng(batch * 100 + seq + heads)
+    hidden = heads * 64
+    qkv, qkvh = _prep(rng.standard_normal((batch * seq, 3 * hidden)), t)
+    mask = _mask(rng, batch, seq, kind)
+    scale = 0.125
+    rc, ctx = G.attention_small(qkv, None if mask is None else G.dev(mask), batch, seq, heads, scale, t)
+    assert rc == kernels.CUBK_OK
+    dt = np.float32 if t == "f32" else np.float16
+    x = qkvh.reshape(batch, seq, 3, heads, 64).astype(np.float64)
+    q, k, v = x[:, :, 0], x[:, :, 1], x[:, :, 2]
+    scores = (scale * np.einsum("bihc,bjhc->bihj", q, k)).astype(np.float32).astype(dt).astype(np.float32)
+    probs = oracle.masked_softmax(scores, mask, 1.0).astype(dt).astype(np.float64)
+    ref = np.einsum("bihj,bjhc->bihc", probs, v).reshape(batch * seq, hidden)
+    got = G.host(ctx).astype(np.float64)
+    assert np.all(np.isfinite(got))
+    # a probability that falls on the other side of a rounding boundary of the storage type moves one term
+    tol = 2e-5 if t == "f32" else 4e-3
+    first = 0
+    if kind == "empty_row":
+        # sequence 0 has every key masked: scores near -10000, where float32 resolves 1e-3 (see test_masked_softmax)
+        assert np.max(np.abs(got[:seq] - ref[:seq])) <= 5e-3 * max(1.0, float(np.max(np.abs(ref))))
+        first = seq
+    err = float(np.max(np.abs(got[first:] - ref[first:])))
+    assert err <= tol * max(1.0, float(np.max(np.abs(ref)))), err
+
+
+def test_attention_small_declines_what_it_does_not_cover():
+    lib = kernels.load()
+    x = torch.zeros(65 * 3 * 128, device="cuda")
+    p, s = x.data_ptr(), G.stream()
+    assert lib.cubk_attention_small_f32(p, None, 1, 65, 2, 128, 1.0, p, s) == kernels.CUBK_ERR_UNSUPPORTED   # too long
+    assert lib.cubk_attention_small_f32(p, None, 1, 32, 2, 96, 1.0, p, s) == kernels.CUBK_ERR_UNSUPPORTED    # head size
+    assert lib.cubk_attention_small_f32(None, None, 1, 32, 2, 128, 1.0, p, s) == kernels.CUBK_ERR_INVALID_ARG
+    assert lib.cubk_attention_small_f32(p, None, 0, 32, 2, 128, 1.0, p, s) == kernels.CUBK_OK
+
+
 # ============================================================================ K1 embedding + add + LayerNorm
 
 def _choose_embed_kernel(kernel_options, which):

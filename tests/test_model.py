@@ -291,7 +291,10 @@ def test_device_resident_forward_and_profile(model_files):
     assert prof["bias_gelu"]["launches"] == L and prof["masked_softmax"]["launches"] == L
     # pooler activation and the two-label classifier run as one launch, counted with the former
     assert prof["bias_tanh"]["launches"] == 1 and prof["logits_probs"]["launches"] == 0
-    assert prof["gemm"]["launches"] == 6 * L + 1 and prof["event_overhead"]["launches"] == 1
+    # a request this small runs each layer's attention as one launch (counted with the softmax) in place of the
+    # two batched products: four library products per layer, not six
+    small = s <= 64 and cfg["hidden"] == 64 * cfg["heads"] and b * s <= 2048
+    assert prof["gemm"]["launches"] == (4 if small else 6) * L + 1 and prof["event_overhead"]["launches"] == 1
     assert prof["bias_gelu"]["ms"] > 0
     assert prof["bias_gelu"]["bytes"] == L * (2 * b * s * cfg["intermediate"] * 4 + cfg["intermediate"] * 4)
     # the results stayed in the replica's device buffers
@@ -491,6 +494,42 @@ def test_masked_key_columns_are_left_out_of_the_attention(model_files, oracle, c
         assert rel_err(seq_out, want["sequence_output"]) < tol
     if ct == model.ComputeType.FLOAT:
         truth = oracle.bert_forward(var, synthetic.model_geometry(cfg, S), ids, mask, seg)
+        for k in ("sequence_output", "pooled_output", "probs"):
+            assert rel_err(got[k], truth[k]) < 1e-5, (k, rel_err(got[k], truth[k]))
+    m.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ct", [model.ComputeType.FLOAT, model.ComputeType.HALF])
+@pytest.mark.parametrize("batch,seq", [(1, 32), (8, 32), (32, 32), (5, 64), (3, 20)])
+def test_small_requests_run_each_layers_attention_as_one_launch(tmp_path, oracle, ct, batch, seq, monkeypatch):
+    """Requests of up to 2048 tokens on sequences of at most 64 (heads of 64) take cubk_attention_small_* in place
+    of two batched products and the softmax kernel: same outputs as with the switch off, and as the oracle."""
+    cfg = synthetic.config("small", hidden=128, heads=2, intermediate=256, layers=2)    # heads of 64
+    var = synthetic.random_weights(cfg, 7)
+    path = str(tmp_path / "m.pb")
+    frozen_graph.write_frozen_graph(path, var)
+    ids, mask, seg, _ = synthetic.random_inputs(cfg, batch, seq, 13, lengths=(1, seq), segments="random")
+    tol = 1e-5 if ct == model.ComputeType.FLOAT else 4e-3
+    monkeypatch.setenv("CUBERT_SMALL_ATTENTION", "0")
+    plain = model.Model(path, batch, seq, cfg["layers"], cfg["heads"], ct)
+    want = _run(plain, ids, mask, seg, cfg)
+    plain.close()
+    monkeypatch.delenv("CUBERT_SMALL_ATTENTION")
+    m = model.Model(path, batch, seq, cfg["layers"], cfg["heads"], ct)
+    m.profile_read()
+    m.profile_enable(True)
+    got = _run(m, ids, mask, seg, cfg)
+    prof = m.profile_read()
+    m.profile_enable(False)
+    assert prof["gemm"]["launches"] == 4 * cfg["layers"] + 1 and prof["masked_softmax"]["launches"] == cfg["layers"]
+    for _ in range(2):                                   # captured, replayed
+        again = _run(m, ids, mask, seg, cfg)
+    for k, ref in want.items():
+        assert rel_err(got[k], ref) < tol, (k, rel_err(got[k], ref))
+        assert np.array_equal(again[k], got[k]), k
+    if ct == model.ComputeType.FLOAT:
+        truth = oracle.bert_forward(var, synthetic.model_geometry(cfg, seq), ids, mask, seg)
         for k in ("sequence_output", "pooled_output", "probs"):
             assert rel_err(got[k], truth[k]) < 1e-5, (k, rel_err(got[k], truth[k]))
     m.close()

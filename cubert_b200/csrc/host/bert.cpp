@@ -488,7 +488,9 @@ void Bert<T>::wait_for_staging() {
 
 // ------------------------------------------------------------------ attention over kept keys only
 constexpr size_t kMinPositionsForKeyPlan = 2048;
-constexpr size_t kSmallAttentionTokens = 2048;   // up to here a layer's attention is one launch on short sequences
+// Up to here a layer's attention is one launch on short sequences. Measured on the batch 1/8/32 serving mix
+// (seq 32): requests of 32 and 256 tokens gain 40 us (0.43 -> 0.39 ms), requests of 1024 tokens lose 24 us.
+constexpr size_t kSmallAttentionTokens = 512;
 
 template <typename T>
 void Bert<T>::build_key_plan(size_t batch_size, const int8_t *input_mask) {

@@ -358,16 +358,23 @@ int masked_softmax(const T *scores, const int8_t *mask, int64_t rows, int64_t ro
 //   qkv      [batch * seq, 3 * hidden]: per token Q | K | V, head h at columns h * 64 of each part
 //   context  [batch * seq, hidden]
 constexpr int kSmallHeadDim = 64;
-constexpr int kSmallAttentionWarps = 4;
+constexpr int kSmallAttentionWarps = 8;   // query rows per block: one per warp
+constexpr int kSmallKeyStride = kSmallHeadDim + 4;   // floats per K row in shared memory: 128-bit reads by 32
+                                                     // lanes of 32 different rows are conflict-free at 68
 
+// Block = (sequence, head) x a group of 8 query rows. K and V of the head go to shared memory as float32
+// (every block of the head's groups loads them again: 16 KB from L2), then each warp takes one query row:
+// lane j owns key j (and j + 32 when seq > 32) for the scores and the softmax, columns 2 * lane and
+// 2 * lane + 1 for the context.
 template <typename T, int SMAX>
 __global__ void __launch_bounds__(32 * kSmallAttentionWarps)
 small_attention_kernel(const T *qkv, const int8_t *mask, T *context, int seq, int heads, int hidden, float scale) {
     constexpr int D = kSmallHeadDim;
     constexpr int KPL = SMAX / 32;  // keys per lane
-    __shared__ float s_k[SMAX][D + 1];
-    __shared__ float s_v[SMAX][D];
-    __shared__ float s_q[kSmallAttentionWarps][D];
+    __shared__ __align__(16) float s_k[SMAX][kSmallKeyStride];
+    __shared__ __align__(16) float s_v[SMAX][D];
+    __shared__ __align__(16) float s_q[kSmallAttentionWarps][D];
+    __shared__ __align__(16) float s_p[kSmallAttentionWarps][SMAX];
     __shared__ float s_madd[SMAX];
     const int b = blockIdx.x / heads;
     const int h = blockIdx.x - b * heads;
@@ -376,74 +383,92 @@ small_attention_kernel(const T *qkv, const int8_t *mask, T *context, int seq, in
     const size_t row_stride = 3 * (size_t) hidden;
     const T *base = qkv + (size_t) b * seq * row_stride + (size_t) h * D;
 
-    for (int i = threadIdx.x; i < seq * D; i += blockDim.x) {
-        const int j = i / D, c = i - j * D;
-        s_k[j][c] = to_float<T>(base[(size_t) j * row_stride + hidden + c]);
-        s_v[j][c] = to_float<T>(base[(size_t) j * row_stride + 2 * hidden + c]);
+    // K and V: pairs of adjacent columns per thread (4- or 8-byte loads, a row of 64 columns per warp)
+    for (int i = threadIdx.x; i < seq * (D / 2); i += blockDim.x) {
+        const int j = i / (D / 2), c = 2 * (i - j * (D / 2));
+        const T *kp = base + (size_t) j * row_stride + hidden + c;
+        const T *vp = kp + hidden;
+        s_k[j][c] = to_float<T>(kp[0]);
+        s_k[j][c + 1] = to_float<T>(kp[1]);
+        s_v[j][c] = to_float<T>(vp[0]);
+        s_v[j][c + 1] = to_float<T>(vp[1]);
     }
     for (int j = threadIdx.x; j < SMAX; j += blockDim.x) {
         s_madd[j] = (j < seq && (mask == nullptr || mask[(size_t) b * seq + j] != 0)) ? 0.f : kMaskedScore;
     }
+    const int i = blockIdx.y * kSmallAttentionWarps + warp;   // this warp's query row
+    if (i < seq) {
+        const T *qp = base + (size_t) i * row_stride + 2 * lane;
+        s_q[warp][2 * lane] = to_float<T>(qp[0]);
+        s_q[warp][2 * lane + 1] = to_float<T>(qp[1]);
+    }
     __syncthreads();
+    if (i >= seq) {
+        return;
+    }
 
-    for (int i = warp; i < seq; i += kSmallAttentionWarps) {
-        // the query row, shared by the warp
-        for (int c = lane; c < D; c += 32) {
-            s_q[warp][c] = to_float<T>(base[(size_t) i * row_stride + c]);
-        }
-        __syncwarp();
-        float v[KPL];
-        float mx = -3.0e38f;
+    float v[KPL];
+    float mx = -3.0e38f;
 #pragma unroll
-        for (int u = 0; u < KPL; ++u) {
-            const int j = lane + 32 * u;
-            float dot = 0.f;
-            if (j < seq) {
-#pragma unroll 16
-                for (int c = 0; c < D; ++c) {
-                    dot = fmaf(s_q[warp][c], s_k[j][c], dot);
-                }
-            }
-            // the stored score (storage precision), then the additive mask, as K4 reads it
-            v[u] = j < seq ? to_float<T>(from_float<T>(scale * dot)) + s_madd[j] : -3.0e38f;
-            mx = fmaxf(mx, v[u]);
-        }
-        mx = group_max<32>(mx);
-        float p[KPL];
-        float sum = 0.f;
+    for (int u = 0; u < KPL; ++u) {
+        const int j = lane + 32 * u;
+        const int jr = j < seq ? j : 0;   // rows past the sequence are not staged: read row 0, discard
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int u = 0; u < KPL; ++u) {
-            p[u] = lane + 32 * u < seq ? fast_exp2(fmaf(v[u], kLog2e, -mx * kLog2e)) : 0.f;
-            sum += p[u];
+        for (int c = 0; c < D; c += 4) {
+            const float4 q4 = *reinterpret_cast<const float4 *>(&s_q[warp][c]);
+            const float4 k4 = *reinterpret_cast<const float4 *>(&s_k[jr][c]);
+            acc.x = fmaf(q4.x, k4.x, acc.x);
+            acc.y = fmaf(q4.y, k4.y, acc.y);
+            acc.z = fmaf(q4.z, k4.z, acc.z);
+            acc.w = fmaf(q4.w, k4.w, acc.w);
         }
-        sum = group_sum<32>(sum);
-        const float inv = 1.f / sum;
+        const float dot = (acc.x + acc.y) + (acc.z + acc.w);
+        // the stored score (storage precision), then the additive mask, as K4 reads it
+        v[u] = j < seq ? to_float<T>(from_float<T>(scale * dot)) + s_madd[j] : -3.0e38f;
+        mx = fmaxf(mx, v[u]);
+    }
+    mx = group_max<32>(mx);
+    float p[KPL];
+    float sum = 0.f;
 #pragma unroll
-        for (int u = 0; u < KPL; ++u) {
-            p[u] = to_float<T>(from_float<T>(p[u] * inv));  // the stored probability
-        }
-        // context columns 2 * lane and 2 * lane + 1
-        float2 acc = make_float2(0.f, 0.f);
+    for (int u = 0; u < KPL; ++u) {
+        p[u] = lane + 32 * u < seq ? fast_exp2(fmaf(v[u], kLog2e, -mx * kLog2e)) : 0.f;
+        sum += p[u];
+    }
+    sum = group_sum<32>(sum);
+    const float inv = 1.f / sum;
 #pragma unroll
-        for (int u = 0; u < KPL; ++u) {
-            for (int jj = 0; jj < 32; ++jj) {
-                const int j = jj + 32 * u;
-                const float pj = __shfl_sync(0xffffffffu, p[u], jj);
-                if (j < seq) {
-                    const float2 vv = *reinterpret_cast<const float2 *>(&s_v[j][2 * lane]);
-                    acc.x = fmaf(pj, vv.x, acc.x);
-                    acc.y = fmaf(pj, vv.y, acc.y);
-                }
-            }
-        }
-        T *dst = context + ((size_t) b * seq + i) * hidden + (size_t) h * D + 2 * lane;
-        if (sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(dst) & 3u) == 0) {
-            *reinterpret_cast<__half2 *>(dst) = __floats2half2_rn(acc.x, acc.y);
-        } else {
-            dst[0] = from_float<T>(acc.x);
-            dst[1] = from_float<T>(acc.y);
-        }
-        __syncwarp();  // s_q[warp] is rewritten by the next row
+    for (int u = 0; u < KPL; ++u) {
+        s_p[warp][lane + 32 * u] = to_float<T>(from_float<T>(p[u] * inv));  // the stored probability
+    }
+    __syncwarp();
+    // context columns 2 * lane and 2 * lane + 1; keys past the sequence carry probability 0 and stale V rows
+    // are never read (the loop stops at seq)
+    float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+    int j = 0;
+    for (; j + 1 < seq; j += 2) {
+        const float2 pp = *reinterpret_cast<const float2 *>(&s_p[warp][j]);
+        const float2 va = *reinterpret_cast<const float2 *>(&s_v[j][2 * lane]);
+        const float2 vb = *reinterpret_cast<const float2 *>(&s_v[j + 1][2 * lane]);
+        acc0.x = fmaf(pp.x, va.x, acc0.x);
+        acc0.y = fmaf(pp.x, va.y, acc0.y);
+        acc1.x = fmaf(pp.y, vb.x, acc1.x);
+        acc1.y = fmaf(pp.y, vb.y, acc1.y);
+    }
+    if (j < seq) {
+        const float pj = s_p[warp][j];
+        const float2 va = *reinterpret_cast<const float2 *>(&s_v[j][2 * lane]);
+        acc0.x = fmaf(pj, va.x, acc0.x);
+        acc0.y = fmaf(pj, va.y, acc0.y);
+    }
+    const float cx = acc0.x + acc1.x, cy = acc0.y + acc1.y;
+    T *dst = context + ((size_t) b * seq + i) * hidden + (size_t) h * D + 2 * lane;
+    if (sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(dst) & 3u) == 0) {
+        *reinterpret_cast<__half2 *>(dst) = __floats2half2_rn(cx, cy);
+    } else {
+        dst[0] = from_float<T>(cx);
+        dst[1] = from_float<T>(cy);
     }
 }
 
@@ -459,7 +484,7 @@ int small_attention(const T *qkv, const int8_t *mask, int batch, int seq, int he
     if (batch == 0) {
         return CUBK_OK;
     }
-    const unsigned grid = (unsigned) (batch * heads);
+    const dim3 grid((unsigned) (batch * heads), (unsigned) ((seq + kSmallAttentionWarps - 1) / kSmallAttentionWarps));
     if (seq <= 32) {
         small_attention_kernel<T, 32><<<grid, 32 * kSmallAttentionWarps, 0, stream>>>(qkv, mask, context, seq, heads, hidden,
                                                                                     scale);

@@ -185,7 +185,7 @@ int cubk_masked_softmax_extents_f16(const void *scores, const int8_t *mask, cons
  * qkv [batch * seq, 3 * hidden] holds per token Q | K | V (head h at columns 64 * h of each part); mask int8
  * [batch, seq] over the keys or NULL; context [batch * seq, hidden]. Runs on the float32 pipes (no tensor
  * cores): CUBK_ERR_UNSUPPORTED unless seq <= 64 and hidden == 64 * heads; the caller decides up to which
- * size it pays (the host library: requests of at most 2048 tokens). */
+ * size it pays (the host library: requests of at most 512 tokens). */
 int cubk_attention_small_f32(const float *qkv, const int8_t *mask, int batch, int seq, int heads, int hidden,
                              float scale, float *context, void *stream);
 int cubk_attention_small_f16(const void *qkv, const int8_t *mask, int batch, int seq, int heads, int hidden,

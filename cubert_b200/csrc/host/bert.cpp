@@ -57,6 +57,11 @@ const T *find(const std::unordered_map<std::string, const T *> &var, const std::
 
 constexpr size_t kMaxStagedInputBytes = 64 * 1024;  // one staged copy of the whole input span up to this size
 
+// Up to here a layer's attention is one launch on short sequences (CUBERT_SMALL_ATTENTION_TOKENS overrides).
+// Measured on the batch 1/8/32 serving mix (seq 32): requests of 32 and 256 tokens gain 40 us
+// (0.43 -> 0.39 ms), requests of 1024 tokens lose 24-37 us (one or two query rows per warp alike).
+constexpr size_t kSmallAttentionTokens = 512;
+
 template <typename T>
 void upload(DeviceBuffer &dst, const T *src, size_t count) {
     dst.allocate(count * sizeof(T));
@@ -186,6 +191,7 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
     // short sequences and heads of 64: requests of up to kSmallAttentionTokens tokens run the attention of a
     // layer as one launch (cubk_attention_small_*) instead of two batched products and K4
     small_attention_ = S <= 64 && H == heads * 64 && env_int("CUBERT_SMALL_ATTENTION", 1) != 0;
+    small_attention_tokens_ = env_int("CUBERT_SMALL_ATTENTION_TOKENS", (int) kSmallAttentionTokens);
 
     // first-token pooler + a small classifier: K5a and K5c run as one launch (cubk_pooler_head_*)
     {
@@ -488,9 +494,7 @@ void Bert<T>::wait_for_staging() {
 
 // ------------------------------------------------------------------ attention over kept keys only
 constexpr size_t kMinPositionsForKeyPlan = 2048;
-// Up to here a layer's attention is one launch on short sequences. Measured on the batch 1/8/32 serving mix
-// (seq 32): requests of 32 and 256 tokens gain 40 us (0.43 -> 0.39 ms), requests of 1024 tokens lose 24 us.
-constexpr size_t kSmallAttentionTokens = 512;
+
 
 template <typename T>
 void Bert<T>::build_key_plan(size_t batch_size, const int8_t *input_mask) {
@@ -838,7 +842,7 @@ void Bert<T>::forward_layers(size_t l_begin, size_t l_end, size_t b0, size_t nb,
             KERNEL_CHECK(cubk_scatter_rows(tok, N, qkv_out, 3 * H, (int) e, qkv_.get(), (int) R, st));
         }
 
-        if (small_attention_ && packed == 0 && R <= (int64_t) kSmallAttentionTokens) {
+        if (small_attention_ && packed == 0 && R <= small_attention_tokens_) {
             // the whole attention of the layer in one launch (counted with K4, whose bytes it would have moved)
             begin(CUBERT_B200_K_MASKED_SOFTMAX);
             KERNEL_CHECK(K<T>::attention_small(qkv, mask, B, S, heads, H, att_scale, context, st));

@@ -152,6 +152,7 @@ private:
     bool has_classifier_bias_ = false;
     bool fuse_heads_ = false;
     bool small_attention_ = false;
+    int64_t small_attention_tokens_ = 512;
 
     // weights
     DeviceBuffer word_emb_, type_emb_, pos_emb_, emb_ln_gamma_, emb_ln_beta_;

@@ -366,15 +366,16 @@ constexpr int kSmallKeyStride = kSmallHeadDim + 4;   // floats per K row in shar
 // (every block of the head's groups loads them again: 16 KB from L2), then each warp takes one query row:
 // lane j owns key j (and j + 32 when seq > 32) for the scores and the softmax, columns 2 * lane and
 // 2 * lane + 1 for the context.
-template <typename T, int SMAX>
-__global__ void __launch_bounds__(32 * kSmallAttentionWarps)
+template <typename T, int SMAX, int RPW>
+__global__ void __launch_bounds__(32 * kSmallAttentionWarps, (SMAX == 64 && RPW == 2 ? 2 : 1))
 small_attention_kernel(const T *qkv, const int8_t *mask, T *context, int seq, int heads, int hidden, float scale) {
     constexpr int D = kSmallHeadDim;
     constexpr int KPL = SMAX / 32;  // keys per lane
+    constexpr int ROWS = kSmallAttentionWarps * RPW;   // query rows per block, RPW of them per warp
     __shared__ __align__(16) float s_k[SMAX][kSmallKeyStride];
     __shared__ __align__(16) float s_v[SMAX][D];
-    __shared__ __align__(16) float s_q[kSmallAttentionWarps][D];
-    __shared__ __align__(16) float s_p[kSmallAttentionWarps][SMAX];
+    __shared__ __align__(16) float s_q[ROWS][D];
+    __shared__ __align__(16) float s_p[ROWS][SMAX];
     __shared__ float s_madd[SMAX];
     const int b = blockIdx.x / heads;
     const int h = blockIdx.x - b * heads;
@@ -396,79 +397,100 @@ small_attention_kernel(const T *qkv, const int8_t *mask, T *context, int seq, in
     for (int j = threadIdx.x; j < SMAX; j += blockDim.x) {
         s_madd[j] = (j < seq && (mask == nullptr || mask[(size_t) b * seq + j] != 0)) ? 0.f : kMaskedScore;
     }
-    const int i = blockIdx.y * kSmallAttentionWarps + warp;   // this warp's query row
-    if (i < seq) {
-        const T *qp = base + (size_t) i * row_stride + 2 * lane;
-        s_q[warp][2 * lane] = to_float<T>(qp[0]);
-        s_q[warp][2 * lane + 1] = to_float<T>(qp[1]);
+    const int row0 = blockIdx.y * ROWS + warp * RPW;   // this warp's first query row
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+        if (row0 + r < seq) {
+            const T *qp = base + (size_t) (row0 + r) * row_stride + 2 * lane;
+            s_q[warp * RPW + r][2 * lane] = to_float<T>(qp[0]);
+            s_q[warp * RPW + r][2 * lane + 1] = to_float<T>(qp[1]);
+        }
     }
     __syncthreads();
-    if (i >= seq) {
+    if (row0 >= seq) {
         return;
     }
 
-    float v[KPL];
-    float mx = -3.0e38f;
+    // scores of RPW rows at once (independent chains), softmax per row
+    float v[RPW][KPL];
+    float mx[RPW];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+        mx[r] = -3.0e38f;
+    }
 #pragma unroll
     for (int u = 0; u < KPL; ++u) {
         const int j = lane + 32 * u;
         const int jr = j < seq ? j : 0;   // rows past the sequence are not staged: read row 0, discard
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 acc[RPW];
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+            acc[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
 #pragma unroll
         for (int c = 0; c < D; c += 4) {
-            const float4 q4 = *reinterpret_cast<const float4 *>(&s_q[warp][c]);
             const float4 k4 = *reinterpret_cast<const float4 *>(&s_k[jr][c]);
-            acc.x = fmaf(q4.x, k4.x, acc.x);
-            acc.y = fmaf(q4.y, k4.y, acc.y);
-            acc.z = fmaf(q4.z, k4.z, acc.z);
-            acc.w = fmaf(q4.w, k4.w, acc.w);
+#pragma unroll
+            for (int r = 0; r < RPW; ++r) {
+                const float4 q4 = *reinterpret_cast<const float4 *>(&s_q[warp * RPW + r][c]);
+                acc[r].x = fmaf(q4.x, k4.x, acc[r].x);
+                acc[r].y = fmaf(q4.y, k4.y, acc[r].y);
+                acc[r].z = fmaf(q4.z, k4.z, acc[r].z);
+                acc[r].w = fmaf(q4.w, k4.w, acc[r].w);
+            }
         }
-        const float dot = (acc.x + acc.y) + (acc.z + acc.w);
-        // the stored score (storage precision), then the additive mask, as K4 reads it
-        v[u] = j < seq ? to_float<T>(from_float<T>(scale * dot)) + s_madd[j] : -3.0e38f;
-        mx = fmaxf(mx, v[u]);
-    }
-    mx = group_max<32>(mx);
-    float p[KPL];
-    float sum = 0.f;
 #pragma unroll
-    for (int u = 0; u < KPL; ++u) {
-        p[u] = lane + 32 * u < seq ? fast_exp2(fmaf(v[u], kLog2e, -mx * kLog2e)) : 0.f;
-        sum += p[u];
+        for (int r = 0; r < RPW; ++r) {
+            const float dot = (acc[r].x + acc[r].y) + (acc[r].z + acc[r].w);
+            // the stored score (storage precision), then the additive mask, as K4 reads it
+            v[r][u] = j < seq ? to_float<T>(from_float<T>(scale * dot)) + s_madd[j] : -3.0e38f;
+            mx[r] = fmaxf(mx[r], v[r][u]);
+        }
     }
-    sum = group_sum<32>(sum);
-    const float inv = 1.f / sum;
 #pragma unroll
-    for (int u = 0; u < KPL; ++u) {
-        s_p[warp][lane + 32 * u] = to_float<T>(from_float<T>(p[u] * inv));  // the stored probability
+    for (int r = 0; r < RPW; ++r) {
+        const float m = group_max<32>(mx[r]);
+        float p[KPL];
+        float sum = 0.f;
+#pragma unroll
+        for (int u = 0; u < KPL; ++u) {
+            p[u] = lane + 32 * u < seq ? fast_exp2(fmaf(v[r][u], kLog2e, -m * kLog2e)) : 0.f;
+            sum += p[u];
+        }
+        sum = group_sum<32>(sum);
+        const float inv = 1.f / sum;
+#pragma unroll
+        for (int u = 0; u < KPL; ++u) {
+            s_p[warp * RPW + r][lane + 32 * u] = to_float<T>(from_float<T>(p[u] * inv));  // the stored probability
+        }
     }
     __syncwarp();
-    // context columns 2 * lane and 2 * lane + 1; keys past the sequence carry probability 0 and stale V rows
-    // are never read (the loop stops at seq)
-    float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
-    int j = 0;
-    for (; j + 1 < seq; j += 2) {
-        const float2 pp = *reinterpret_cast<const float2 *>(&s_p[warp][j]);
-        const float2 va = *reinterpret_cast<const float2 *>(&s_v[j][2 * lane]);
-        const float2 vb = *reinterpret_cast<const float2 *>(&s_v[j + 1][2 * lane]);
-        acc0.x = fmaf(pp.x, va.x, acc0.x);
-        acc0.y = fmaf(pp.x, va.y, acc0.y);
-        acc1.x = fmaf(pp.y, vb.x, acc1.x);
-        acc1.y = fmaf(pp.y, vb.y, acc1.y);
+    // context columns 2 * lane and 2 * lane + 1 of the RPW rows; keys past the sequence are never read
+    float2 acc[RPW];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+        acc[r] = make_float2(0.f, 0.f);
     }
-    if (j < seq) {
-        const float pj = s_p[warp][j];
-        const float2 va = *reinterpret_cast<const float2 *>(&s_v[j][2 * lane]);
-        acc0.x = fmaf(pj, va.x, acc0.x);
-        acc0.y = fmaf(pj, va.y, acc0.y);
+    for (int j = 0; j < seq; ++j) {
+        const float2 vv = *reinterpret_cast<const float2 *>(&s_v[j][2 * lane]);
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+            const float pj = s_p[warp * RPW + r][j];
+            acc[r].x = fmaf(pj, vv.x, acc[r].x);
+            acc[r].y = fmaf(pj, vv.y, acc[r].y);
+        }
     }
-    const float cx = acc0.x + acc1.x, cy = acc0.y + acc1.y;
-    T *dst = context + ((size_t) b * seq + i) * hidden + (size_t) h * D + 2 * lane;
-    if (sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(dst) & 3u) == 0) {
-        *reinterpret_cast<__half2 *>(dst) = __floats2half2_rn(cx, cy);
-    } else {
-        dst[0] = from_float<T>(cx);
-        dst[1] = from_float<T>(cy);
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+        if (row0 + r < seq) {
+            T *dst = context + ((size_t) b * seq + row0 + r) * hidden + (size_t) h * D + 2 * lane;
+            if (sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(dst) & 3u) == 0) {
+                *reinterpret_cast<__half2 *>(dst) = __floats2half2_rn(acc[r].x, acc[r].y);
+            } else {
+                dst[0] = from_float<T>(acc[r].x);
+                dst[1] = from_float<T>(acc[r].y);
+            }
+        }
     }
 }
 
@@ -484,14 +506,20 @@ int small_attention(const T *qkv, const int8_t *mask, int batch, int seq, int he
     if (batch == 0) {
         return CUBK_OK;
     }
-    const dim3 grid((unsigned) (batch * heads), (unsigned) ((seq + kSmallAttentionWarps - 1) / kSmallAttentionWarps));
+    // one query row per warp while that already gives every SM a few blocks, two rows per warp beyond
+    // (half the blocks, each loading K and V once for twice the rows)
+    const bool two_rows = (int64_t) batch * heads * ((seq + 7) / 8) > 2 * 148;
+    const int rows = kSmallAttentionWarps * (two_rows ? 2 : 1);
+    const dim3 grid((unsigned) (batch * heads), (unsigned) ((seq + rows - 1) / rows));
+#define SMALL_ATTENTION(SMAX, RPW)                                                                              \
+    small_attention_kernel<T, SMAX, RPW><<<grid, 32 * kSmallAttentionWarps, 0, stream>>>(qkv, mask, context, seq, heads, \
+                                                                                         hidden, scale)
     if (seq <= 32) {
-        small_attention_kernel<T, 32><<<grid, 32 * kSmallAttentionWarps, 0, stream>>>(qkv, mask, context, seq, heads, hidden,
-                                                                                    scale);
+        if (two_rows) SMALL_ATTENTION(32, 2); else SMALL_ATTENTION(32, 1);
     } else {
-        small_attention_kernel<T, 64><<<grid, 32 * kSmallAttentionWarps, 0, stream>>>(qkv, mask, context, seq, heads, hidden,
-                                                                                    scale);
+        if (two_rows) SMALL_ATTENTION(64, 2); else SMALL_ATTENTION(64, 1);
     }
+#undef SMALL_ATTENTION
     return check_launch();
 }
 

@@ -92,7 +92,7 @@ private:
 
     // `packed` > 0: padding is skipped. The token-wise GEMMs, LayerNorms and GELU run on a packed list
     // of `packed` tokens (the positions whose mask is non-zero, plus position 0 of every sequence for
-    // the pooler; rounded up to a multiple of 64 by repeating the last one); only the attention
+    // the pooler; rounded up to a sixteenth of the request, at least 64, by repeating the last one); only the attention
     // products and the softmax keep the [batch, seq] layout, with rows scattered in and gathered out.
     // A masked position never influences an unmasked one (its keys get probability exactly 0), so
     // pooled_output, logits and probs are the same as in the full computation.

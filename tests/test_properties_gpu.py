@@ -144,3 +144,84 @@ def test_embed_ln(oracle, t, batch, seq, hidden, vocab, seed, staged):
     finally:
         kernels.set_option(kernels.OPT_EMBED_STAGED_ROWS, saved[0])
         kernels.set_option(kernels.OPT_EXACT_WIDTH_EMBED, saved[1])
+
+
+@settings(**SETTINGS)
+@given(t=DT, batch=st.integers(1, 5), heads=st.integers(1, 3), seq=st.one_of(st.integers(1, 72), st.sampled_from([128, 264, 512])),
+       seed=st.integers(0, 2 ** 31 - 1), zero_to=st.sampled_from(["own", "common", "full"]))
+def test_masked_softmax_with_key_extents(t, batch, heads, seq, seed, zero_to):
+    """Any extents that cover every kept key: below them the extents call equals the plain call bit for bit,
+    from there to zero_to it writes zeros, beyond it touches nothing; rows stay distributions."""
+    rng = np.random.default_rng(seed)
+    x, _ = _prep(rng.standard_normal((batch, seq, heads, seq)) * 3, t)
+    lengths = rng.integers(1, seq + 1, batch)
+    mask = np.zeros((batch, seq), np.int8)
+    for b, n in enumerate(lengths):
+        mask[b, :n] = rng.integers(0, 2, n) * 3
+        mask[b, n - 1] = 1
+    slack = rng.integers(0, 20, batch)                      # an extent may lie beyond the last kept key
+    extents = np.minimum(lengths + slack, seq).astype(np.int32)
+    z = {"own": 0, "common": int(extents.max()), "full": seq}[zero_to]
+    plain = G.masked_softmax(x.view(-1, seq), G.dev(mask), seq * heads, 0.125, t).view(batch, seq, heads, seq)
+    got = G.masked_softmax_extents(x.view(-1, seq), G.dev(mask), G.dev(extents), z, seq * heads, 0.125, t)
+    got = got.view(batch, seq, heads, seq)
+    epv = 4 if t == "f32" else 8
+    vector_path = seq % epv == 0 and seq // epv <= 256
+    for b in range(batch):
+        n, w = int(extents[b]), max(int(extents[b]), z)
+        if vector_path:      # whole 16-byte vectors: the boundaries move up to the next vector
+            n, w = min(seq, -(-n // epv) * epv), min(seq, -(-w // epv) * epv)
+        assert torch.equal(got[b, :, :, :n], plain[b, :, :, :n])
+        assert bool((got[b, :, :, n:w] == 0).all())
+        assert bool(torch.isnan(got[b, :, :, w:]).all())
+        sums = got[b, :, :, :n].float().sum(-1)
+        assert bool(((sums - 1).abs() < (1e-4 if t == "f32" else 5e-3)).all())
+
+
+@settings(**SETTINGS)
+@given(t=DT, batch=st.integers(1, 6), heads=st.integers(1, 3), seq=st.integers(1, 64), seed=st.integers(0, 2 ** 31 - 1),
+       keep=st.sampled_from([0.0, 0.4, 1.0]))
+def test_attention_of_short_sequences(oracle, t, batch, heads, seq, seed, keep):
+    """The one-launch attention against its three steps on the host (reference softmax), for any short shape
+    and any mask, fully masked sequences included."""
+    rng = np.random.default_rng(seed)
+    hidden = heads * 64
+    qkv, qkvh = _prep(rng.standard_normal((batch * seq, 3 * hidden)), t)
+    mask = (rng.random((batch, seq)) < keep).astype(np.int8) * rng.integers(1, 100, (batch, seq)).astype(np.int8)
+    rc, ctx = G.attention_small(qkv, G.dev(mask), batch, seq, heads, 0.125, t)
+    assert rc == kernels.CUBK_OK
+    dt = np.float32 if t == "f32" else np.float16
+    x = qkvh.reshape(batch, seq, 3, heads, 64).astype(np.float64)
+    scores = (0.125 * np.einsum("bihc,bjhc->bihj", x[:, :, 0], x[:, :, 1])).astype(np.float32).astype(dt).astype(np.float32)
+    probs = oracle.masked_softmax(scores, mask, 1.0).astype(dt).astype(np.float64)
+    ref = np.einsum("bihj,bjhc->bihc", probs, x[:, :, 2]).reshape(batch * seq, hidden)
+    got = G.host(ctx).astype(np.float64)
+    assert np.all(np.isfinite(got))
+    # sequences without a kept key sit at -10000, where float32 resolves 1e-3 (see the softmax tests)
+    loose = np.repeat(~mask.any(axis=1), seq)
+    tol = 2e-5 if t == "f32" else 4e-3
+    scale = max(1.0, float(np.max(np.abs(ref))))
+    if (~loose).any():
+        assert np.max(np.abs(got[~loose] - ref[~loose])) <= tol * scale
+    if loose.any():
+        assert np.max(np.abs(got[loose] - ref[loose])) <= 5e-3 * scale
+
+
+@settings(**SETTINGS)
+@given(t=DT, batch=st.integers(1, 40), hidden=st.sampled_from([8, 64, 256, 768, 1024, 2048]), labels=st.integers(1, 8),
+       seed=st.integers(0, 2 ** 31 - 1), bias=st.booleans())
+def test_pooler_head_in_one_launch(oracle, t, batch, hidden, labels, seed, bias):
+    """pooled row bit-equal to bias+tanh; logits and probs as the classifier gives them on the stored pooled row."""
+    rng = np.random.default_rng(seed)
+    x, _ = _prep(rng.standard_normal((batch, hidden)) * 2, t)
+    pb, _ = _prep(rng.standard_normal(hidden), t)
+    w, wh = _prep(rng.standard_normal((labels, hidden)) * 0.1, t)
+    b, bh = _prep(rng.standard_normal(labels), t) if bias else (None, None)
+    rc, pooled, logits, probs = G.pooler_head(x, pb, w, b, t)
+    assert rc == kernels.CUBK_OK
+    assert torch.equal(pooled, G.bias_tanh(x, pb, t))
+    ref_logits, ref_probs = oracle.classifier(G.host(pooled), wh, bh)
+    _close(logits, ref_logits, t)
+    p = G.host(probs)
+    assert np.max(np.abs(p - ref_probs)) <= (1e-5 if t == "f32" else G.F16_ATOL)
+    assert np.all(np.abs(p.sum(-1) - 1) <= (1e-5 if t == "f32" else 5e-3))

@@ -308,9 +308,13 @@ def test_device_resident_forward_and_profile(model_files):
 
 
 @pytest.mark.gpu
-def test_concurrent_callers_are_serialised_per_replica(model_files):
-    """Several threads on one model: every call must return the right answer
-    (src/cuBERT/BertM.cpp:69-76 locks the chosen replica)."""
+@pytest.mark.parametrize("per_gpu,strict", [("1", "0"), ("3", "0"), ("3", "1")])
+def test_concurrent_callers_are_serialised_per_replica(model_files, per_gpu, strict, monkeypatch):
+    """Several threads on one model, more threads than replicas: every call must return the right answer
+    (src/cuBERT/BertM.cpp:69-76 locks the chosen replica; here a caller takes any free replica and waits only
+    when all are busy, or, with CUBERT_STRICT_ROUND_ROBIN=1, waits for the replica the rotation dealt it)."""
+    monkeypatch.setenv("CUBERT_NUM_MODELS_PER_GPU", per_gpu)
+    monkeypatch.setenv("CUBERT_STRICT_ROUND_ROBIN", strict)
     path, cfg, var = model_files["tiny"]
     g = golden("tiny")
     ids, mask, seg, want = g["ids"], g["mask"], g["seg"], g["probs"]  # read the archive before threading

@@ -350,23 +350,6 @@ logits_probs_kernel(const T *pooled, const T *weights, const T *bias, int hidden
     }
 }
 
-template <typename T>
-int logits_probs(const T *pooled, const T *weights, const T *bias, int batch, int hidden, int labels,
-                 T *logits, T *probs, cudaStream_t stream) {
-    if (pooled == nullptr || weights == nullptr || logits == nullptr || batch < 0 || hidden <= 0 || labels <= 0) {
-        return CUBK_ERR_INVALID_ARG;
-    }
-    if (labels > kMaxLabels) {
-        return CUBK_ERR_UNSUPPORTED;
-    }
-    if (batch == 0) {
-        return CUBK_OK;
-    }
-    logits_probs_kernel<T><<<batch, 128, sizeof(float) * labels, stream>>>(pooled, weights, bias, hidden, labels,
-                                                                          logits, probs);
-    return check_launch();
-}
-
 // ------------------------------------------------------------------ K5a + K5c in one launch
 // pooled = tanh(x + pooler_bias) written out, then the classifier on it: what bias_act_kernel<Tanh>
 // followed by logits_probs_kernel computes, for the small label counts of a classification head.
@@ -379,7 +362,9 @@ int logits_probs(const T *pooled, const T *weights, const T *bias, int batch, in
 constexpr int kHeadLabels = 8;        // label rows handled per launch
 constexpr int kHeadMaxVectors = 4;    // vectors per thread: rows up to 128 * 4 vectors
 
-template <typename T>
+// POOLER = false: x is the pooled row already (no bias, no tanh, nothing stored back): the classifier alone
+// for small label counts, which is how cubk_logits_probs_* runs them.
+template <typename T, bool POOLER>
 __global__ void __launch_bounds__(128)
 pooler_head_kernel(const T *x, const T *pooler_bias, const T *weights, const T *bias, int hidden, int nvec, int labels,
                    T *pooled, T *logits, T *probs) {
@@ -399,16 +384,19 @@ pooler_head_kernel(const T *x, const T *pooler_bias, const T *weights, const T *
     for (int k = 0; k < kHeadMaxVectors; ++k) {
         const int idx = threadIdx.x + k * 128;
         if (idx < nvec) {
-            float v[EPV], pb[EPV];
+            float v[EPV];
             Vec<T>::unpack(ld_stream(x + (size_t) b * hidden + (size_t) idx * EPV), v);
-            Vec<T>::unpack(ld_param(pooler_bias + (size_t) idx * EPV), pb);
+            if (POOLER) {
+                float pb[EPV];
+                Vec<T>::unpack(ld_param(pooler_bias + (size_t) idx * EPV), pb);
 #pragma unroll
-            for (int e = 0; e < EPV; ++e) {
-                v[e] = tanhf(v[e] + pb[e]);
+                for (int e = 0; e < EPV; ++e) {
+                    v[e] = tanhf(v[e] + pb[e]);
+                }
+                const uint4 stored = Vec<T>::pack(v);
+                st_vec(pooled + (size_t) b * hidden + (size_t) idx * EPV, stored);
+                Vec<T>::unpack(stored, v);  // what the classifier sees is the stored pooled output
             }
-            const uint4 stored = Vec<T>::pack(v);
-            st_vec(pooled + (size_t) b * hidden + (size_t) idx * EPV, stored);
-            Vec<T>::unpack(stored, v);  // what the classifier sees is the stored pooled output
 #pragma unroll
             for (int l = 0; l < kHeadLabels; ++l) {
                 if (l < labels) {
@@ -473,8 +461,34 @@ int pooler_head(const T *x, const T *pooler_bias, const T *weights, const T *bia
     if (batch == 0) {
         return CUBK_OK;
     }
-    pooler_head_kernel<T><<<batch, 128, 0, stream>>>(x, pooler_bias, weights, bias, hidden, hidden / EPV, labels, pooled,
-                                                     logits, probs);
+    pooler_head_kernel<T, true><<<batch, 128, 0, stream>>>(x, pooler_bias, weights, bias, hidden, hidden / EPV, labels,
+                                                           pooled, logits, probs);
+    return check_launch();
+}
+
+template <typename T>
+int logits_probs(const T *pooled, const T *weights, const T *bias, int batch, int hidden, int labels,
+                 T *logits, T *probs, cudaStream_t stream) {
+    if (pooled == nullptr || weights == nullptr || logits == nullptr || batch < 0 || hidden <= 0 || labels <= 0) {
+        return CUBK_ERR_INVALID_ARG;
+    }
+    if (labels > kMaxLabels) {
+        return CUBK_ERR_UNSUPPORTED;
+    }
+    if (batch == 0) {
+        return CUBK_OK;
+    }
+    constexpr int EPV = Vec<T>::EPV;
+    if (labels <= kHeadLabels && hidden % EPV == 0 && hidden / EPV <= 128 * kHeadMaxVectors && aligned16(pooled) &&
+        aligned16(weights)) {
+        // few labels: 128-bit loads and every thread on every label (the kernel of cubk_pooler_head_* without
+        // its pooler part); 2 labels, hidden 768, 256 sequences: 11 us with the kernel below
+        pooler_head_kernel<T, false><<<batch, 128, 0, stream>>>(pooled, nullptr, weights, bias, hidden, hidden / EPV,
+                                                                labels, nullptr, logits, probs);
+        return check_launch();
+    }
+    logits_probs_kernel<T><<<batch, 128, sizeof(float) * labels, stream>>>(pooled, weights, bias, hidden, labels,
+                                                                          logits, probs);
     return check_launch();
 }
 

@@ -1,6 +1,6 @@
 """Isolated sweep of the fused kernels: achieved HBM GB/s per kernel and shape.
 
-    python -m cubert_b200.sweep [--quick] [--large] [--only ln,gelu,softmax,embed,pool] [--dtype f16,f32]
+    python -m cubert_b200.sweep [--quick] [--large] [--only ln,gelu,softmax,embed,pool,attention] [--dtype f16,f32]
                                 [--iters N] [--json out.json]
 
 Each case is timed with CUDA events on the launching stream: `iters` back-to-back launches
@@ -13,6 +13,7 @@ ALGORITHMIC bytes / time:
     masked softmax     2*B*H*S*S*e + B*S
     embed+LN           2*B*S*H*e + 5*B*S + S*H*e + type_vocab*H*e + 2*H*e
     mean pool          B*S*H*e + B*H*e
+    one-launch attention  4*B*S*H*e + B*S   (Q, K, V read, context written; latency-bound at its sizes)
 
 torch provides device memory and the stream only.
 """
@@ -191,6 +192,29 @@ def case_pool(t, batch, seq, hidden, iters):
                 sec=sec, sets=n)
 
 
+def case_attention(t, batch, seq, iters, heads=12):
+    """The one-launch attention of short requests (at most 512 tokens in the host library)."""
+    e = 4 if t == "f32" else 2
+    hidden = 64 * heads
+    per_set = 4 * batch * seq * hidden * e
+    n = min(64, _nsets(per_set))
+    g = torch.Generator(device="cuda").manual_seed(1)
+    qkv = [torch.randn((batch * seq, 3 * hidden), device="cuda", generator=g, dtype=torch.float32).to(_dt(t))
+           for _ in range(n)]
+    outs = [torch.empty((batch * seq, hidden), device="cuda", dtype=_dt(t)) for _ in range(n)]
+    lens = torch.randint(4, seq + 1, (batch,), device="cuda", generator=g)
+    mask = (torch.arange(seq, device="cuda")[None, :] < lens[:, None]).to(torch.int8).contiguous()
+    f = _fn("attention_small", t)
+
+    def launch(i):
+        kernels.check(f(qkv[i].data_ptr(), mask.data_ptr(), batch, seq, heads, hidden, 0.125, outs[i].data_ptr(),
+                        _stream()))
+
+    sec = _time(launch, n, iters)
+    return dict(kernel="attention_small", dtype=t, shape=[batch, seq, hidden], bytes=per_set + batch * seq, sec=sec,
+                sets=n)
+
+
 def run(only=None, dtypes=("f16", "f32"), quick=False, iters=20, large=False):
     kernels.load()
     peak, peak_kind = measured_peak_gbs()
@@ -238,6 +262,10 @@ def run(only=None, dtypes=("f16", "f32"), quick=False, iters=20, large=False):
             for (b, s, h) in ((64, 512, 1024), (512, 512, 1024)):
                 results.append(case_pool(t, b, s, h, iters))
                 torch.cuda.empty_cache()
+        if want("attention"):
+            for (b, s) in ((1, 32), (8, 32), (16, 32), (32, 32), (8, 64)):
+                results.append(case_attention(t, b, s, iters))
+                torch.cuda.empty_cache()
     for r in results:
         r["gbs"] = r["bytes"] / r["sec"] / 1e9
         r["frac_of_%s_peak" % peak_kind] = r["gbs"] / peak
@@ -253,7 +281,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", default=None)
     ap.add_argument("--no-graph", action="store_true", help="time plain stream launches instead of a graph replay")
-    ap.add_argument("--large", action="store_true", help="the BERT-large / seq 512 shapes instead of the config-2 sweep")
+    ap.add_argument("--large", action="store_true", help="the BERT-large / seq 512 shapes instead of the BERT-base sweep")
     a = ap.parse_args()
     global USE_GRAPH
     USE_GRAPH = not a.no_graph

@@ -105,7 +105,7 @@ def _rel(a, b):
     return float(np.max(np.abs(a - b)) / (np.sqrt(np.mean(b * b)) + 1e-30))
 
 
-def test_config1_bert_base_f32_seq32_batch128(base_model_file, reference_cpu):
+def test_bert_base_f32_seq32_batch128(base_model_file, reference_cpu):
     """The reference's published case: BERT-base float32, seq 32, batch 128, logits and probs, against the
     reference's CPU build on the same weights and inputs (seed 0, ids in [1, 21128), full mask,
     segment 0 for the first 16 positions)."""
@@ -128,7 +128,7 @@ def test_config1_bert_base_f32_seq32_batch128(base_model_file, reference_cpu):
     assert np.max(np.abs(out.probs - ref["probs"])) < 1e-5
 
 
-def test_config3_bert_base_f16_seq128_variable_length(base_model_file, reference_cpu):
+def test_bert_base_f16_seq128_variable_length(base_model_file, reference_cpu):
     """The headline benchmark workload (BERT-base, seq 128, ragged masks) on a 32-sequence slice: binary16 storage against the
     float32 reference on binary16-rounded weights."""
     path, cfg, var = base_model_file
@@ -149,7 +149,7 @@ def test_config3_bert_base_f16_seq128_variable_length(base_model_file, reference
     assert np.sqrt(np.mean(err ** 2)) < 1e-2 and err.max() < 1e-1
 
 
-def test_config4_bert_large_f16_seq512_mean_pooler(tmp_path, reference_cpu):
+def test_bert_large_f16_seq512_mean_pooler(tmp_path, reference_cpu):
     """The BERT-large workload on a 4-sequence slice: BERT-large geometry, seq 512, no pooler weights
     (mean pooler) and no classifier, cuBERT_POOLED_OUTPUT."""
     cfg = synthetic.config("large", layers=4)   # 4 of the 24 layers keep the CPU reference to seconds

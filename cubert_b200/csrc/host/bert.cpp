@@ -188,10 +188,12 @@ Bert<T>::Bert(const std::unordered_map<std::string, const T *> &var, size_t max_
         probs_.allocate(sizeof(T) * B * num_labels);
     }
 
-    // short sequences and heads of 64: requests of up to kSmallAttentionTokens tokens run the attention of a
-    // layer as one launch (cubk_attention_small_*) instead of two batched products and K4
-    small_attention_ = S <= 64 && H == heads * 64 && env_int("CUBERT_SMALL_ATTENTION", 1) != 0;
-    small_attention_tokens_ = env_int("CUBERT_SMALL_ATTENTION_TOKENS", (int) kSmallAttentionTokens);
+    // heads of 64 and short sequences: the attention of a layer runs as one launch (cubk_attention_small_*)
+    // instead of two batched products and K4. Binary16: up to 128 positions and any number of tokens (matrix
+    // instructions; the scores never reach HBM). Float32: up to 64 positions, requests of up to
+    // kSmallAttentionTokens tokens (float32 pipes: beyond that the library's products are ahead).
+    small_attention_ = S <= (sizeof(T) == 2 ? 128 : 64) && H == heads * 64 && env_int("CUBERT_SMALL_ATTENTION", 1) != 0;
+    small_attention_tokens_ = env_int("CUBERT_SMALL_ATTENTION_TOKENS", sizeof(T) == 2 ? 0x7fffffff : (int) kSmallAttentionTokens);
 
     // first-token pooler + a small classifier: K5a and K5c run as one launch (cubk_pooler_head_*)
     {
@@ -842,11 +844,12 @@ void Bert<T>::forward_layers(size_t l_begin, size_t l_end, size_t b0, size_t nb,
             KERNEL_CHECK(cubk_scatter_rows(tok, N, qkv_out, 3 * H, (int) e, qkv_.get(), (int) R, st));
         }
 
-        if (small_attention_ && packed == 0 && R <= small_attention_tokens_) {
-            // the whole attention of the layer in one launch (counted with K4, whose bytes it would have moved)
+        if (small_attention_ && R <= small_attention_tokens_) {
+            // the whole attention of the layer in one launch (timed in K4's slot; its bytes: Q | K | V read,
+            // the context written, the mask)
             begin(CUBERT_B200_K_MASKED_SOFTMAX);
             KERNEL_CHECK(K<T>::attention_small(qkv, mask, B, S, heads, H, att_scale, context, st));
-            end(CUBERT_B200_K_MASKED_SOFTMAX, 2 * R * heads * S * e + R);
+            end(CUBERT_B200_K_MASKED_SOFTMAX, 4 * R * H * e + R);
         } else {
             // scores[b, i, h, j] = (1/sqrt(d)) * sum_c K[b,j,h,c] * Q[b,i,h,c]   (op_att/BatchMatMul.cpp:57-68)
             // With a key plan only the key columns j below each sequence's extent exist: one product per group

@@ -180,12 +180,19 @@ int cubk_masked_softmax_extents_f16(const void *scores, const int8_t *mask, cons
  *   rounded to the storage type;  context = P.V
  * i.e. what the reference's Att_Q_K product, mask, softmax and Att_QK_V product compute
  * (src/cuBERT/op_att/AttentionSelf.cpp:96-111, op_att/BatchMatMul.cpp:57-68,124-135, op/Softmax.cpp:19-35), rounding
- * where those round, for the sizes at which a forward pass is bound by its chain of launches rather than by
- * work (serving requests of a few sequences): one launch in place of two batched library products and K4.
+ * where those round: one launch in place of two batched library products and K4, and the [seq, seq] scores
+ * never reach device memory.
  * qkv [batch * seq, 3 * hidden] holds per token Q | K | V (head h at columns 64 * h of each part); mask int8
- * [batch, seq] over the keys or NULL; context [batch * seq, hidden]. Runs on the float32 pipes (no tensor
- * cores): CUBK_ERR_UNSUPPORTED unless seq <= 64 and hidden == 64 * heads; the caller decides up to which
- * size it pays (the host library: requests of at most 512 tokens). */
+ * [batch, seq] over the keys or NULL; context [batch * seq, hidden]. hidden must be 64 * heads.
+ *   _f16, seq <= 128, qkv on a 16-byte and context on a 4-byte boundary: warp-level matrix instructions
+ *     (binary16 operands, float32 accumulators), a block per (sequence, head), a strip of 16 query rows per warp
+ *     kept in registers from the scores to the context. Past 64 positions the kernel finds each sequence's last
+ *     kept key and neither loads nor multiplies the keys behind it (their probabilities are exactly 0; where
+ *     that differs from the full computation is stated at cubk_masked_softmax_extents_*). Moves Q | K | V once
+ *     and the context once: 4 * batch * seq * hidden elements.
+ *   _f32 (and _f16 at other addresses), seq <= 64: the float32 pipes; pays for requests of a few hundred
+ *     tokens, where a forward pass is bound by its chain of launches rather than by work.
+ * Anything else: CUBK_ERR_UNSUPPORTED. */
 int cubk_attention_small_f32(const float *qkv, const int8_t *mask, int batch, int seq, int heads, int hidden,
                              float scale, float *context, void *stream);
 int cubk_attention_small_f16(const void *qkv, const int8_t *mask, int batch, int seq, int heads, int hidden,

@@ -364,7 +364,9 @@ def test_gelu_hands_on_nan_and_infinity(t):
 @pytest.mark.parametrize("t", DTYPES)
 @pytest.mark.parametrize("batch,seq,heads,kind", [(1, 32, 12, "prefix"), (8, 32, 12, "random"), (32, 32, 12, "prefix"),
                                                   (3, 64, 16, "random"), (5, 17, 2, "prefix"), (2, 49, 3, "none"),
-                                                  (4, 1, 1, "none"), (3, 32, 4, "empty_row")])
+                                                  (4, 1, 1, "none"), (3, 32, 4, "empty_row"), (4, 128, 12, "prefix"),
+                                                  (3, 100, 2, "random"), (2, 128, 3, "empty_row"), (2, 77, 2, "none"),
+                                                  (5, 65, 1, "prefix")])
 def test_attention_of_short_sequences_in_one_launch(oracle, t, batch, seq, heads, kind):
     """cubk_attention_small_* against the three steps it stands for, computed on the host with the reference's
     softmax: scores = scale * Q.K^T rounded to the storage type, masked softmax rounded to the storage type, P.V."""
@@ -374,6 +376,9 @@ def test_attention_of_short_sequences_in_one_launch(oracle, t, batch, seq, heads
     mask = _mask(rng, batch, seq, kind)
     scale = 0.125
     rc, ctx = G.attention_small(qkv, None if mask is None else G.dev(mask), batch, seq, heads, scale, t)
+    if t == "f32" and seq > 64:
+        assert rc == kernels.CUBK_ERR_UNSUPPORTED   # 65 to 128 positions: binary16 only
+        return
     assert rc == kernels.CUBK_OK
     dt = np.float32 if t == "f32" else np.float16
     x = qkvh.reshape(batch, seq, 3, heads, 64).astype(np.float64)
@@ -394,11 +399,34 @@ def test_attention_of_short_sequences_in_one_launch(oracle, t, batch, seq, heads
     assert err <= tol * max(1.0, float(np.max(np.abs(ref)))), err
 
 
+@pytest.mark.parametrize("batch,seq,heads", [(2, 32, 3), (3, 50, 2)])
+def test_attention_small_binary16_kernels_agree(batch, seq, heads):
+    """Binary16 inputs on a 16-byte boundary take the matrix-instruction kernel, any other address the float32-pipe
+    kernel: the same rounding points, so the two differ by the order of additions only."""
+    rng = np.random.default_rng(seq)
+    hidden = heads * 64
+    n = batch * seq * 3 * hidden
+    flat = torch.zeros(n + 8, dtype=torch.float16, device="cuda")
+    vals = G.dev(G.round_f16(rng.standard_normal(n).astype(np.float32)), torch.float16)
+    mask = G.dev(_mask(rng, batch, seq, "random"))
+    flat[:n] = vals
+    rc, aligned = G.attention_small(flat[:n].view(batch * seq, 3 * hidden), mask, batch, seq, heads, 0.125, "f16")
+    assert rc == kernels.CUBK_OK and flat.data_ptr() % 16 == 0
+    flat[1:n + 1] = vals
+    rc, shifted = G.attention_small(flat[1:n + 1].view(batch * seq, 3 * hidden), mask, batch, seq, heads, 0.125, "f16")
+    assert rc == kernels.CUBK_OK
+    a, b = G.host(aligned).astype(np.float64), G.host(shifted).astype(np.float64)
+    assert np.all(np.isfinite(a)) and np.all(np.isfinite(b))
+    assert np.max(np.abs(a - b)) <= 4e-3 * max(1.0, float(np.max(np.abs(a))))
+
+
 def test_attention_small_declines_what_it_does_not_cover():
     lib = kernels.load()
     x = torch.zeros(65 * 3 * 128, device="cuda")
     p, s = x.data_ptr(), G.stream()
     assert lib.cubk_attention_small_f32(p, None, 1, 65, 2, 128, 1.0, p, s) == kernels.CUBK_ERR_UNSUPPORTED   # too long
+    assert lib.cubk_attention_small_f16(p, None, 1, 129, 2, 128, 1.0, p, s) == kernels.CUBK_ERR_UNSUPPORTED  # too long
+    assert lib.cubk_attention_small_f16(p + 2, None, 1, 65, 2, 128, 1.0, p, s) == kernels.CUBK_ERR_UNSUPPORTED  # past 64: 16-byte rows only
     assert lib.cubk_attention_small_f32(p, None, 1, 32, 2, 96, 1.0, p, s) == kernels.CUBK_ERR_UNSUPPORTED    # head size
     assert lib.cubk_attention_small_f32(None, None, 1, 32, 2, 128, 1.0, p, s) == kernels.CUBK_ERR_INVALID_ARG
     assert lib.cubk_attention_small_f32(p, None, 0, 32, 2, 128, 1.0, p, s) == kernels.CUBK_OK

@@ -434,15 +434,21 @@ def test_a_sequence_without_any_kept_key_is_not_packed(model_files, oracle, ct):
 @pytest.mark.gpu
 @pytest.mark.parametrize("ct", [model.ComputeType.FLOAT, model.ComputeType.HALF])
 @pytest.mark.parametrize("batch", [24, 130])     # 130 x 128 positions: per-position outputs leave in sub-batches
-@pytest.mark.parametrize("products_too", ["0", "1"])
-def test_masked_key_columns_are_left_out_of_the_attention(model_files, oracle, ct, batch, products_too, monkeypatch):
+@pytest.mark.parametrize("how", ["softmax_only", "products_too", "one_launch"])
+def test_masked_key_columns_are_left_out_of_the_attention(model_files, oracle, ct, batch, how, monkeypatch):
     """With the mask visible on the host, the softmax (and with CUBERT_KEY_GEMM=1 the two attention products as
     well, per group of sequences) works only on the key columns below each sequence's last kept key, rounded
     up to 8 (32 with the products). Those columns carry probability exactly 0 in the full computation, so every
     output must be what the library gives with the feature off -- for ragged prefixes, masks with holes, a full
     sequence, a sequence without any kept key -- eagerly, captured and replayed, for per-position requests,
     pooled-only requests and device-resident inputs."""
+    # "one_launch": binary16 models of up to 128 positions run the attention as one kernel, which finds each
+    # sequence's last kept key itself and neither loads nor multiplies the keys behind it
+    if how == "one_launch" and ct == model.ComputeType.FLOAT:
+        pytest.skip("binary16 only")
+    products_too = "1" if how == "products_too" else "0"
     monkeypatch.setenv("CUBERT_KEY_GEMM", products_too)
+    monkeypatch.setenv("CUBERT_SMALL_ATTENTION", "0")
     step = 32 if products_too == "1" else 8
     import torch
     path, cfg, var = model_files["small"]
@@ -466,6 +472,8 @@ def test_masked_key_columns_are_left_out_of_the_attention(model_files, oracle, c
     want_b = _run(plain, ids, mask_b, seg, cfg)
     plain.close()
     monkeypatch.delenv("CUBERT_SKIP_MASKED_KEYS")
+    if how == "one_launch":
+        monkeypatch.delenv("CUBERT_SMALL_ATTENTION")
 
     m = model.Model(path, batch, S, cfg["layers"], cfg["heads"], ct)
     for _ in range(3):                               # eager, captured, replayed
@@ -505,10 +513,13 @@ def test_masked_key_columns_are_left_out_of_the_attention(model_files, oracle, c
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("ct", [model.ComputeType.FLOAT, model.ComputeType.HALF])
-@pytest.mark.parametrize("batch,seq", [(1, 32), (8, 32), (16, 32), (5, 64), (3, 20)])
+@pytest.mark.parametrize("batch,seq", [(1, 32), (8, 32), (16, 32), (5, 64), (3, 20), (40, 32), (4, 128), (3, 100)])
 def test_small_requests_run_each_layers_attention_as_one_launch(tmp_path, oracle, ct, batch, seq, monkeypatch):
-    """Requests of up to 512 tokens on sequences of at most 64 (heads of 64) take cubk_attention_small_* in place
-    of two batched products and the softmax kernel: same outputs as with the switch off, and as the oracle."""
+    """With heads of 64, binary16 models of up to 128 positions (any request) and float32 models of up to 64
+    positions (requests of up to 512 tokens) take cubk_attention_small_* in place of two batched products and the
+    softmax kernel: same outputs as with the switch off, and as the oracle."""
+    if ct == model.ComputeType.FLOAT and (seq > 64 or batch * seq > 512):
+        pytest.skip("float32: the one-launch attention stops at 64 positions and 512 tokens")
     cfg = synthetic.config("small", hidden=128, heads=2, intermediate=256, layers=2)    # heads of 64
     var = synthetic.random_weights(cfg, 7)
     path = str(tmp_path / "m.pb")

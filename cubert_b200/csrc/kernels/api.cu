@@ -27,6 +27,7 @@ static const OptionSpec kOptionSpecs[CUBK_OPT_COUNT] = {
     {"CUBK_SOFTMAX_MASK_SMEM", 1, 0, 1},    // CUBK_OPT_SOFTMAX_MASK_SMEM
     {"CUBK_EXACT_WIDTH_ROWS", 1, 0, 1},     // CUBK_OPT_EXACT_WIDTH_ROWS
     {"CUBK_EXACT_WIDTH_EMBED", 1, 0, 1},    // CUBK_OPT_EXACT_WIDTH_EMBED
+    {"CUBK_ATTENTION_TENSOR_MEMORY", 0, 0, 1},   // CUBK_OPT_ATTENTION_TENSOR_MEMORY
 };
 
 static std::atomic<int> g_options[CUBK_OPT_COUNT];

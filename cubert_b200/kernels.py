@@ -26,6 +26,7 @@ OPT_EMBED_STAGED_ROWS = 0
 OPT_SOFTMAX_MASK_SMEM = 1
 OPT_EXACT_WIDTH_ROWS = 2
 OPT_EXACT_WIDTH_EMBED = 3
+OPT_ATTENTION_TENSOR_MEMORY = 4
 
 _P = C.c_void_p
 _I = C.c_int

@@ -63,12 +63,16 @@ const char *cubk_last_cuda_error(void);
  *                               specialised for rows of exactly 32, 64, 96, 128, 192 or 256 16-byte vectors when
  *                               the shape allows, 0 = always the general kernel
  *   CUBK_OPT_EXACT_WIDTH_EMBED  (env CUBK_EXACT_WIDTH_EMBED)  the same for cubk_embed_ln_*
+ *   CUBK_OPT_ATTENTION_TENSOR_MEMORY (env CUBK_ATTENTION_TENSOR_MEMORY)  1 = cubk_attention_small_f16 of 65 to 128
+ *                               positions runs on tcgen05 with accumulators in tensor memory, 0 = on warp-level
+ *                               matrix instructions
  * Both return CUBK_ERR_INVALID_ARG for an unknown switch or a value outside its range. */
 #define CUBK_OPT_EMBED_STAGED_ROWS 0
 #define CUBK_OPT_SOFTMAX_MASK_SMEM 1
 #define CUBK_OPT_EXACT_WIDTH_ROWS  2
 #define CUBK_OPT_EXACT_WIDTH_EMBED 3
-#define CUBK_OPT_COUNT             4
+#define CUBK_OPT_ATTENTION_TENSOR_MEMORY 4
+#define CUBK_OPT_COUNT             5
 int cubk_set_option(int option, int value);
 int cubk_get_option(int option, int *value);
 

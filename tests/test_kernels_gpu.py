@@ -367,9 +367,13 @@ def test_gelu_hands_on_nan_and_infinity(t):
                                                   (4, 1, 1, "none"), (3, 32, 4, "empty_row"), (4, 128, 12, "prefix"),
                                                   (3, 100, 2, "random"), (2, 128, 3, "empty_row"), (2, 77, 2, "none"),
                                                   (5, 65, 1, "prefix")])
-def test_attention_of_short_sequences_in_one_launch(oracle, t, batch, seq, heads, kind):
+@pytest.mark.parametrize("tensor_memory", [0, 1])   # binary16 past 64 positions: mma.sync or tcgen05
+def test_attention_of_short_sequences_in_one_launch(oracle, t, batch, seq, heads, kind, tensor_memory, kernel_options):
     """cubk_attention_small_* against the three steps it stands for, computed on the host with the reference's
     softmax: scores = scale * Q.K^T rounded to the storage type, masked softmax rounded to the storage type, P.V."""
+    if tensor_memory == 1 and not (t == "f16" and seq > 64):
+        pytest.skip("the same kernel either way")
+    kernel_options(kernels.OPT_ATTENTION_TENSOR_MEMORY, tensor_memory)
     rng = np.random.default_rng(batch * 100 + seq + heads)
     hidden = heads * 64
     qkv, qkvh = _prep(rng.standard_normal((batch * seq, 3 * hidden)), t)

@@ -180,8 +180,8 @@ def test_masked_softmax_with_key_extents(t, batch, heads, seq, seed, zero_to):
 
 @settings(**SETTINGS)
 @given(t=DT, batch=st.integers(1, 6), heads=st.integers(1, 3), seq=st.integers(1, 128), seed=st.integers(0, 2 ** 31 - 1),
-       keep=st.sampled_from([0.0, 0.4, 1.0]), tail=st.integers(0, 100))
-def test_attention_of_short_sequences(oracle, t, batch, heads, seq, seed, keep, tail):
+       keep=st.sampled_from([0.0, 0.4, 1.0]), tail=st.integers(0, 100), tensor_memory=st.sampled_from([0, 1]))
+def test_attention_of_short_sequences(oracle, t, batch, heads, seq, seed, keep, tail, tensor_memory):
     """The one-launch attention against its three steps on the host (reference softmax), for any short shape
     and any mask, fully masked sequences included."""
     rng = np.random.default_rng(seed)
@@ -193,7 +193,11 @@ def test_attention_of_short_sequences(oracle, t, batch, heads, seq, seed, keep, 
         seq_ok = seq <= 64
     else:
         seq_ok = True
-    rc, ctx = G.attention_small(qkv, G.dev(mask), batch, seq, heads, 0.125, t)
+    saved = kernels.set_option(kernels.OPT_ATTENTION_TENSOR_MEMORY, tensor_memory)   # binary16 past 64 positions
+    try:
+        rc, ctx = G.attention_small(qkv, G.dev(mask), batch, seq, heads, 0.125, t)
+    finally:
+        kernels.set_option(kernels.OPT_ATTENTION_TENSOR_MEMORY, saved)
     if not seq_ok:
         assert rc == kernels.CUBK_ERR_UNSUPPORTED
         return

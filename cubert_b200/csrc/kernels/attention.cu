@@ -531,6 +531,9 @@ attention_tc_kernel(const __half *qkv, const int8_t *mask, __half *context, int 
         ext = last > 0 ? last : seq;
     }
     const int ext16 = (ext + 15) & ~15;
+    if (row >= ext) {
+        s_madd[row] = -1.0e30f;   // a column at or beyond the extent: exp2 gives it exactly 0 (read after the next barrier)
+    }
     // this thread's K and V rows: below the extent from memory, up to ext16 zeros, beyond never read
     if (row < ext16) {
         uint4 k[8], v[8];
@@ -567,47 +570,65 @@ attention_tc_kernel(const __half *qkv, const int8_t *mask, __half *context, int 
     ok = __all_sync(0xffffffffu, ok);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-    // masked softmax of this thread's row (tensor-memory lane 32 * warp + lane), 16 columns at a time
+    // masked softmax of this thread's row (tensor-memory lane 32 * warp + lane). One pass over tensor memory:
+    // the stored scores (scale * S rounded to binary16) stay in 64 registers, two per register; the additive
+    // terms come from shared memory four columns at a time (broadcast reads).
     const uint32_t trow = tmem + ((uint32_t) (32 * warp) << 16);
+    const float2 scale2 = splat2(scale);
+    const float2 log2e2 = splat2(kLog2e);
+    uint32_t sh[kTcRows / 2];
     float mx = -3.0e38f;
-    for (int c0 = 0; c0 < ext16; c0 += 16) {
-        uint32_t r[16];
-        tc_load16(trow + c0, r);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const float sv = __half2float(__float2half_rn(scale * __uint_as_float(r[i]))) + s_madd[c0 + i];
-            mx = fmaxf(mx, c0 + i < ext ? sv : -3.0e38f);
+    for (int c0 = 0; c0 < kTcRows; c0 += 16) {
+        if (c0 < ext16) {   // uniform over the block
+            uint32_t r[16];
+            tc_load16(trow + c0, r);
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+                const float4 madd = *reinterpret_cast<const float4 *>(&s_madd[c0 + i]);
+                const __half2 h0 = __float22half2_rn(mul2(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2));
+                const __half2 h1 = __float22half2_rn(mul2(make_float2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])), scale2));
+                sh[(c0 + i) / 2] = *reinterpret_cast<const uint32_t *>(&h0);
+                sh[(c0 + i) / 2 + 1] = *reinterpret_cast<const uint32_t *>(&h1);
+                const float2 v0 = add2(__half22float2(h0), make_float2(madd.x, madd.y));
+                const float2 v1 = add2(__half22float2(h1), make_float2(madd.z, madd.w));
+                mx = fmaxf(mx, fmaxf(fmaxf(v0.x, v0.y), fmaxf(v1.x, v1.y)));
+            }
         }
     }
-    const float nm = -mx * kLog2e;
-    float sum = 0.f;
-    for (int c0 = 0; c0 < ext16; c0 += 16) {
-        uint32_t r[16];
-        tc_load16(trow + c0, r);
+    const float2 nm2 = splat2(-mx * kLog2e);
+    float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const float sv = __half2float(__float2half_rn(scale * __uint_as_float(r[i]))) + s_madd[c0 + i];
-            sum += c0 + i < ext ? fast_exp2(fmaf(sv, kLog2e, nm)) : 0.f;
+    for (int c0 = 0; c0 < kTcRows; c0 += 4) {
+        if (c0 < ext16) {
+            const float4 madd = *reinterpret_cast<const float4 *>(&s_madd[c0]);
+            const float2 v0 = add2(__half22float2(*reinterpret_cast<const __half2 *>(&sh[c0 / 2])), make_float2(madd.x, madd.y));
+            const float2 v1 = add2(__half22float2(*reinterpret_cast<const __half2 *>(&sh[c0 / 2 + 1])), make_float2(madd.z, madd.w));
+            const float2 e0 = fma2(v0, log2e2, nm2), e1 = fma2(v1, log2e2, nm2);
+            acc = add2(acc, make_float2(fast_exp2(e0.x), fast_exp2(e0.y)));
+            acc = add2(acc, make_float2(fast_exp2(e1.x), fast_exp2(e1.y)));
         }
     }
-    const float inv = 1.f / sum;
-    // every thread has read S before P overwrites Q and K (the MMA that read them has completed)
-    for (int c0 = 0; c0 < ext16; c0 += 16) {
-        uint32_t r[16];
-        tc_load16(trow + c0, r);
-        uint32_t p[8];
+    const float2 inv2 = splat2(1.f / (acc.x + acc.y));
+    // the stored probabilities: P takes the place of Q and K (the MMA that read them has completed)
 #pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-            const float s0 = __half2float(__float2half_rn(scale * __uint_as_float(r[i]))) + s_madd[c0 + i];
-            const float s1 = __half2float(__float2half_rn(scale * __uint_as_float(r[i + 1]))) + s_madd[c0 + i + 1];
-            const float p0 = c0 + i < ext ? fast_exp2(fmaf(s0, kLog2e, nm)) * inv : 0.f;
-            const float p1 = c0 + i + 1 < ext ? fast_exp2(fmaf(s1, kLog2e, nm)) * inv : 0.f;
-            const __half2 hp = __floats2half2_rn(p0, p1);
-            p[i / 2] = *reinterpret_cast<const uint32_t *>(&hp);
+    for (int c0 = 0; c0 < kTcRows; c0 += 8) {
+        if (c0 < ext16) {
+            uint32_t p[4];
+#pragma unroll
+            for (int i = 0; i < 8; i += 4) {
+                const float4 madd = *reinterpret_cast<const float4 *>(&s_madd[c0 + i]);
+                const float2 v0 = add2(__half22float2(*reinterpret_cast<const __half2 *>(&sh[(c0 + i) / 2])), make_float2(madd.x, madd.y));
+                const float2 v1 = add2(__half22float2(*reinterpret_cast<const __half2 *>(&sh[(c0 + i) / 2 + 1])), make_float2(madd.z, madd.w));
+                const float2 e0 = fma2(v0, log2e2, nm2), e1 = fma2(v1, log2e2, nm2);
+                const __half2 p0 = __float22half2_rn(mul2(make_float2(fast_exp2(e0.x), fast_exp2(e0.y)), inv2));
+                const __half2 p1 = __float22half2_rn(mul2(make_float2(fast_exp2(e1.x), fast_exp2(e1.y)), inv2));
+                p[i / 2] = *reinterpret_cast<const uint32_t *>(&p0);
+                p[i / 2 + 1] = *reinterpret_cast<const uint32_t *>(&p1);
+            }
+            // columns c0..c0+7 of this row: chunk c0 / 8 of P
+            *reinterpret_cast<uint4 *>(s_q + (c0 / 8) * kTcChunkBytes + row * 16) = make_uint4(p[0], p[1], p[2], p[3]);
         }
-        // columns c0..c0+15 of this row: chunks c0/8 and c0/8 + 1 of P (P spans Q's and K's 32 KB)
-        *reinterpret_cast<uint4 *>(s_q + (c0 / 8) * kTcChunkBytes + row * 16) = make_uint4(p[0], p[1], p[2], p[3]);
-        *reinterpret_cast<uint4 *>(s_q + (c0 / 8 + 1) * kTcChunkBytes + row * 16) = make_uint4(p[4], p[5], p[6], p[7]);
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

@@ -473,6 +473,23 @@ __device__ __forceinline__ void tc_load16(uint32_t taddr, uint32_t (&r)[16]) {
         : "memory");
 }
 
+// 32 columns of this thread's lane; no wait: the caller issues what it needs, then waits once
+__device__ __forceinline__ void tc_load32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_wait_loads() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
 __global__ void __launch_bounds__(kTcRows, 4)
 attention_tc_kernel(const __half *qkv, const int8_t *mask, __half *context, int seq, int heads, int hidden, float scale) {
     extern __shared__ __align__(128) unsigned char tc_smem[];
@@ -492,21 +509,16 @@ attention_tc_kernel(const __half *qkv, const int8_t *mask, __half *context, int 
     const size_t row_stride = 3 * (size_t) hidden;
     const __half *base = qkv + (size_t) b * seq * row_stride + (size_t) h * D;
 
-    if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(s_tmem)),
-                     "r"((uint32_t) kTcTmemCols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    if (threadIdx.x == 0) {
-        mbar_init(s_bar, 1);
-        mbar_init_fence();
-    }
     // this thread's Q row, in flight while the mask is read
+    // (vector u of this thread: 16-byte chunk (tid & 7) of row (tid >> 3) + 16 u, so that a warp reads four whole
+    // 128-byte rows per instruction)
+    const int chunk = threadIdx.x & 7;
+    const int row8 = threadIdx.x >> 3;
     uint4 q[8];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        q[c] = row < seq ? __ldg(reinterpret_cast<const uint4 *>(base + (size_t) row * row_stride) + c) : make_uint4(0u, 0u, 0u, 0u);
+    for (int u = 0; u < 8; ++u) {
+        const int j = row8 + 16 * u;
+        q[u] = j < seq ? __ldg(reinterpret_cast<const uint4 *>(base + (size_t) j * row_stride) + chunk) : make_uint4(0u, 0u, 0u, 0u);
     }
     // additive mask terms and the key extent: one past the last kept key (every key when none is kept)
     {
@@ -517,9 +529,16 @@ attention_tc_kernel(const __half *qkv, const int8_t *mask, __half *context, int 
             s_last[warp] = ballot != 0u ? 32 * warp + 32 - __clz(ballot) : 0;
         }
     }
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        *reinterpret_cast<uint4 *>(s_q + c * kTcChunkBytes + row * 16) = q[c];
+    // tensor memory and the MMA barrier, once this thread's loads are in flight
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(s_tmem)),
+                     "r"((uint32_t) kTcTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (threadIdx.x == 0) {
+        mbar_init(s_bar, 1);
+        mbar_init_fence();
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -534,20 +553,29 @@ attention_tc_kernel(const __half *qkv, const int8_t *mask, __half *context, int 
     if (row >= ext) {
         s_madd[row] = -1.0e30f;   // a column at or beyond the extent: exp2 gives it exactly 0 (read after the next barrier)
     }
-    // this thread's K and V rows: below the extent from memory, up to ext16 zeros, beyond never read
-    if (row < ext16) {
+    // this thread's K and V rows: below the extent from memory, up to ext16 zeros, beyond never read. Their
+    // loads are issued while the Q row is still in flight (the barrier above waited for the mask only).
+    {
         uint4 k[8], v[8];
-        const uint4 *kp = reinterpret_cast<const uint4 *>(base + (size_t) row * row_stride + hidden);
-        const uint4 *vp = reinterpret_cast<const uint4 *>(base + (size_t) row * row_stride + 2 * (size_t) hidden);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            k[c] = row < ext ? __ldg(kp + c) : make_uint4(0u, 0u, 0u, 0u);
-            v[c] = row < ext ? __ldg(vp + c) : make_uint4(0u, 0u, 0u, 0u);
+        for (int u = 0; u < 8; ++u) {
+            const int j = row8 + 16 * u;
+            const uint4 *kp = reinterpret_cast<const uint4 *>(base + (size_t) j * row_stride + hidden) + chunk;
+            k[u] = j < ext ? __ldg(kp) : make_uint4(0u, 0u, 0u, 0u);
+            v[u] = j < ext ? __ldg(kp + hidden / 8) : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            *reinterpret_cast<uint4 *>(s_k + c * kTcChunkBytes + row * 16) = k[c];
-            *reinterpret_cast<uint4 *>(s_v + c * kTcChunkBytes + row * 16) = v[c];
+        for (int u = 0; u < 8; ++u) {
+            const int j = row8 + 16 * u;
+            *reinterpret_cast<uint4 *>(s_q + chunk * kTcChunkBytes + j * 16) = q[u];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int j = row8 + 16 * u;
+            if (j < ext16) {
+                *reinterpret_cast<uint4 *>(s_k + chunk * kTcChunkBytes + j * 16) = k[u];
+                *reinterpret_cast<uint4 *>(s_v + chunk * kTcChunkBytes + j * 16) = v[u];
+            }
         }
     }
     // generic-proxy stores -> visible to the tensor core's reads of shared memory
@@ -579,12 +607,16 @@ attention_tc_kernel(const __half *qkv, const int8_t *mask, __half *context, int 
     uint32_t sh[kTcRows / 2];
     float mx = -3.0e38f;
 #pragma unroll
-    for (int c0 = 0; c0 < kTcRows; c0 += 16) {
+    for (int c0 = 0; c0 < kTcRows; c0 += 32) {
         if (c0 < ext16) {   // uniform over the block
-            uint32_t r[16];
-            tc_load16(trow + c0, r);
+            uint32_t r[32];
+            tc_load32_nowait(trow + c0, r);
+            tc_wait_loads();
 #pragma unroll
-            for (int i = 0; i < 16; i += 4) {
+            for (int i = 0; i < 32; i += 4) {
+                if (c0 + i >= ext16) {
+                    break;   // columns the product did not write (the load may reach past ext16)
+                }
                 const float4 madd = *reinterpret_cast<const float4 *>(&s_madd[c0 + i]);
                 const __half2 h0 = __float22half2_rn(mul2(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2));
                 const __half2 h1 = __float22half2_rn(mul2(make_float2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])), scale2));
@@ -649,27 +681,38 @@ attention_tc_kernel(const __half *qkv, const int8_t *mask, __half *context, int 
     ok = __all_sync(0xffffffffu, ok);   // tensor-memory loads are warp-wide
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     {
-        uint4 *dst = reinterpret_cast<uint4 *>(context + ((size_t) b * seq + row) * hidden + (size_t) h * D);
+        uint32_t r[2][32];
+        if (ok) {
+            tc_load32_nowait(trow, r[0]);
+            tc_load32_nowait(trow + 32, r[1]);
+            tc_wait_loads();
+        } else {
 #pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 16) {
-            uint32_t r[16];
-            uint32_t o[8];
-            if (ok) {
-                tc_load16(trow + c0, r);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    r[i] = 0x7fc00000u;   // the block gave up: NaN rows
-                }
+            for (int i = 0; i < 32; ++i) {
+                r[0][i] = r[1][i] = 0x7fc00000u;   // the block gave up: NaN rows
             }
+        }
+        // through shared memory (P is no longer read) so that a warp stores four whole 128-byte rows per
+        // instruction; a warp re-reads only the 32 rows it wrote itself. Rows of 144 B: conflict-free both ways.
+        unsigned char *s_o = s_q;
 #pragma unroll
-            for (int i = 0; i < 16; i += 2) {
-                const __half2 ho = __floats2half2_rn(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+        for (int c0 = 0; c0 < D; c0 += 8) {
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 8; i += 2) {
+                const __half2 ho = __floats2half2_rn(__uint_as_float(r[c0 / 32][c0 % 32 + i]),
+                                                     __uint_as_float(r[c0 / 32][c0 % 32 + i + 1]));
                 o[i / 2] = *reinterpret_cast<const uint32_t *>(&ho);
             }
-            if (row < seq) {
-                dst[c0 / 8] = make_uint4(o[0], o[1], o[2], o[3]);
-                dst[c0 / 8 + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+            *reinterpret_cast<uint4 *>(s_o + row * 144 + (c0 / 8) * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int j = 32 * warp + (lane >> 3) + 4 * u;
+            if (j < seq) {
+                const uint4 val = *reinterpret_cast<const uint4 *>(s_o + j * 144 + (lane & 7) * 16);
+                reinterpret_cast<uint4 *>(context + ((size_t) b * seq + j) * hidden + (size_t) h * D)[lane & 7] = val;
             }
         }
     }

@@ -193,7 +193,10 @@ int cubk_masked_softmax_extents_f16(const void *scores, const int8_t *mask, cons
  *     kept in registers from the scores to the context. Past 64 positions the kernel finds each sequence's last
  *     kept key and neither loads nor multiplies the keys behind it (their probabilities are exactly 0; where
  *     that differs from the full computation is stated at cubk_masked_softmax_extents_*). Moves Q | K | V once
- *     and the context once: 4 * batch * seq * hidden elements.
+ *     and the context once: 4 * batch * seq * hidden elements. With CUBK_OPT_ATTENTION_TENSOR_MEMORY set, 65 to
+ *     128 positions run on tcgen05 instead: one 128-row tile per (sequence, head), accumulators in tensor
+ *     memory, a score row per thread; every wait on its MMA barrier is bounded (0.2 s), after which the block
+ *     writes NaN rows, frees its tensor memory and returns.
  *   _f32 (and _f16 at other addresses), seq <= 64: the float32 pipes; pays for requests of a few hundred
  *     tokens, where a forward pass is bound by its chain of launches rather than by work.
  * Anything else: CUBK_ERR_UNSUPPORTED. */

@@ -158,6 +158,15 @@ small_attention_kernel(const T *qkv, const int8_t *mask, T *context, int seq, in
     }
 }
 
+// float(binary16 pair) + float32 pair without a conversion instruction (add.rn.f32.f16: the binary16 operand
+// is widened exactly, one rounding, as convert-then-add); the conversions share the 16-lane pipe of the
+// exponentials, which is what paces the softmax of these kernels
+__device__ __forceinline__ float2 add_pair_f16(uint32_t packed, float2 c) {
+    uint16_t lo, hi;
+    asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(packed));
+    return make_float2(add_f32_f16(lo, c.x), add_f32_f16(hi, c.y));
+}
+
 // ---- binary16 storage, up to 128 positions: the same computation on warp-level matrix instructions
 // The scores of one (sequence, head) never leave the SM: a warp keeps a strip of 16 query rows in registers
 // from Q.K^T (mma.sync m16n8k16, binary16 in, float32 accumulators: what the library's products of binary16
@@ -335,10 +344,10 @@ small_attention_mma_kernel(const __half *qkv, const int8_t *mask, __half *contex
             }
             const int col = 8 * n + 2 * t;
             const float2 madd = *reinterpret_cast<const float2 *>(&s_madd[col]);
-            float2 r0 = __half22float2(__float22half2_rn(mul2(sc[n][0], scale2)));
-            float2 r1 = __half22float2(__float22half2_rn(mul2(sc[n][1], scale2)));
-            r0 = add2(r0, madd);
-            r1 = add2(r1, madd);
+            const __half2 h0 = __float22half2_rn(mul2(sc[n][0], scale2));
+            const __half2 h1 = __float22half2_rn(mul2(sc[n][1], scale2));
+            float2 r0 = add_pair_f16(*reinterpret_cast<const uint32_t *>(&h0), madd);
+            float2 r1 = add_pair_f16(*reinterpret_cast<const uint32_t *>(&h1), madd);
             if (col >= ext) {
                 r0.x = r1.x = kLeftOut;
             }
@@ -622,8 +631,8 @@ attention_tc_kernel(const __half *qkv, const int8_t *mask, __half *context, int 
                 const __half2 h1 = __float22half2_rn(mul2(make_float2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])), scale2));
                 sh[(c0 + i) / 2] = *reinterpret_cast<const uint32_t *>(&h0);
                 sh[(c0 + i) / 2 + 1] = *reinterpret_cast<const uint32_t *>(&h1);
-                const float2 v0 = add2(__half22float2(h0), make_float2(madd.x, madd.y));
-                const float2 v1 = add2(__half22float2(h1), make_float2(madd.z, madd.w));
+                const float2 v0 = add_pair_f16(sh[(c0 + i) / 2], make_float2(madd.x, madd.y));
+                const float2 v1 = add_pair_f16(sh[(c0 + i) / 2 + 1], make_float2(madd.z, madd.w));
                 mx = fmaxf(mx, fmaxf(fmaxf(v0.x, v0.y), fmaxf(v1.x, v1.y)));
             }
         }
@@ -634,8 +643,8 @@ attention_tc_kernel(const __half *qkv, const int8_t *mask, __half *context, int 
     for (int c0 = 0; c0 < kTcRows; c0 += 4) {
         if (c0 < ext16) {
             const float4 madd = *reinterpret_cast<const float4 *>(&s_madd[c0]);
-            const float2 v0 = add2(__half22float2(*reinterpret_cast<const __half2 *>(&sh[c0 / 2])), make_float2(madd.x, madd.y));
-            const float2 v1 = add2(__half22float2(*reinterpret_cast<const __half2 *>(&sh[c0 / 2 + 1])), make_float2(madd.z, madd.w));
+            const float2 v0 = add_pair_f16(sh[c0 / 2], make_float2(madd.x, madd.y));
+            const float2 v1 = add_pair_f16(sh[c0 / 2 + 1], make_float2(madd.z, madd.w));
             const float2 e0 = fma2(v0, log2e2, nm2), e1 = fma2(v1, log2e2, nm2);
             acc = add2(acc, make_float2(fast_exp2(e0.x), fast_exp2(e0.y)));
             acc = add2(acc, make_float2(fast_exp2(e1.x), fast_exp2(e1.y)));
@@ -650,8 +659,8 @@ attention_tc_kernel(const __half *qkv, const int8_t *mask, __half *context, int 
 #pragma unroll
             for (int i = 0; i < 8; i += 4) {
                 const float4 madd = *reinterpret_cast<const float4 *>(&s_madd[c0 + i]);
-                const float2 v0 = add2(__half22float2(*reinterpret_cast<const __half2 *>(&sh[(c0 + i) / 2])), make_float2(madd.x, madd.y));
-                const float2 v1 = add2(__half22float2(*reinterpret_cast<const __half2 *>(&sh[(c0 + i) / 2 + 1])), make_float2(madd.z, madd.w));
+                const float2 v0 = add_pair_f16(sh[(c0 + i) / 2], make_float2(madd.x, madd.y));
+                const float2 v1 = add_pair_f16(sh[(c0 + i) / 2 + 1], make_float2(madd.z, madd.w));
                 const float2 e0 = fma2(v0, log2e2, nm2), e1 = fma2(v1, log2e2, nm2);
                 const __half2 p0 = __float22half2_rn(mul2(make_float2(fast_exp2(e0.x), fast_exp2(e0.y)), inv2));
                 const __half2 p1 = __float22half2_rn(mul2(make_float2(fast_exp2(e1.x), fast_exp2(e1.y)), inv2));

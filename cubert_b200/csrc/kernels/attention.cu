@@ -337,9 +337,12 @@ small_attention_mma_kernel(const __half *qkv, const int8_t *mask, __half *contex
         // masked softmax of rows g and g + 8; a row lives in the four lanes of a quad. The stored score
         // (storage precision), then the additive mask, as K4 reads it.
         float mx0 = -3.0e38f, mx1 = -3.0e38f;
+        // (tiles are walked in groups of four, one uniform branch per 32 columns, so that the conversions,
+        // exponentials and shared-memory reads of a group overlap; a tile past ext16 inside a group holds
+        // zeros and comes out as zeros)
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
-            if (8 * n >= ext16) {
+            if ((n & 3) == 0 && 8 * n >= ext16) {
                 break;
             }
             const int col = 8 * n + 2 * t;
@@ -367,7 +370,7 @@ small_attention_mma_kernel(const __half *qkv, const int8_t *mask, __half *contex
         float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
-            if (8 * n >= ext16) {
+            if ((n & 3) == 0 && 8 * n >= ext16) {
                 break;
             }
             float2 e0 = fma2(sc[n][0], log2e2, nm0), e1 = fma2(sc[n][1], log2e2, nm1);
@@ -623,12 +626,15 @@ attention_tc_kernel(const __half *qkv, const int8_t *mask, __half *context, int 
             tc_wait_loads();
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
-                if (c0 + i >= ext16) {
-                    break;   // columns the product did not write (the load may reach past ext16)
-                }
+                // columns the product did not write (the load may reach past ext16) count as zeros; their
+                // additive term is -1e30, so they come out as probability 0. No branch inside the 32 columns:
+                // conversions, exponentials and shared-memory reads of the group overlap.
+                const bool written = c0 + i < ext16;
                 const float4 madd = *reinterpret_cast<const float4 *>(&s_madd[c0 + i]);
-                const __half2 h0 = __float22half2_rn(mul2(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2));
-                const __half2 h1 = __float22half2_rn(mul2(make_float2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])), scale2));
+                const float2 a0 = written ? make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])) : make_float2(0.f, 0.f);
+                const float2 a1 = written ? make_float2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])) : make_float2(0.f, 0.f);
+                const __half2 h0 = __float22half2_rn(mul2(a0, scale2));
+                const __half2 h1 = __float22half2_rn(mul2(a1, scale2));
                 sh[(c0 + i) / 2] = *reinterpret_cast<const uint32_t *>(&h0);
                 sh[(c0 + i) / 2 + 1] = *reinterpret_cast<const uint32_t *>(&h1);
                 const float2 v0 = add_pair_f16(sh[(c0 + i) / 2], make_float2(madd.x, madd.y));
@@ -641,7 +647,7 @@ attention_tc_kernel(const __half *qkv, const int8_t *mask, __half *context, int 
     float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
     for (int c0 = 0; c0 < kTcRows; c0 += 4) {
-        if (c0 < ext16) {
+        if ((c0 & ~31) < ext16) {
             const float4 madd = *reinterpret_cast<const float4 *>(&s_madd[c0]);
             const float2 v0 = add_pair_f16(sh[c0 / 2], make_float2(madd.x, madd.y));
             const float2 v1 = add_pair_f16(sh[c0 / 2 + 1], make_float2(madd.z, madd.w));
@@ -654,7 +660,7 @@ attention_tc_kernel(const __half *qkv, const int8_t *mask, __half *context, int 
     // the stored probabilities: P takes the place of Q and K (the MMA that read them has completed)
 #pragma unroll
     for (int c0 = 0; c0 < kTcRows; c0 += 8) {
-        if (c0 < ext16) {
+        if ((c0 & ~31) < ext16) {
             uint32_t p[4];
 #pragma unroll
             for (int i = 0; i < 8; i += 4) {

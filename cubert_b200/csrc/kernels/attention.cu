@@ -179,8 +179,8 @@ __device__ __forceinline__ float2 add_pair_f16(uint32_t packed, float2 c) {
 // two products the accumulators have to come back to registers anyway, and the kernel is bound by the
 // latency of a launch (short requests) or by reading Q | K | V once from HBM (long ones), not by arithmetic.
 //
-// Block = one (sequence, head); warp w owns query rows 16 w .. 16 w + 15 and loads them straight into
-// A-operand registers. K and V of the head are staged as binary16 rows of 64 + 8 elements (144 B: the eight
+// Block = one (sequence, head); a warp owns strips of 16 query rows, which it reads as whole 128-byte rows and
+// turns into A-operand fragments through a 16-row buffer of its own (the context strip leaves the same way). K and V of the head are staged as binary16 rows of 64 + 8 elements (144 B: the eight
 // 16-byte rows of an 8 x 8 ldmatrix tile fall into eight different bank groups); rows at and beyond seq are
 // zero so that a probability of 0 never meets a stray NaN. Fragment layouts are those of the PTX ISA for
 // mma.m16n8k16: with g = lane / 4, t = lane % 4 a thread holds accumulator elements (g, 2t), (g, 2t+1),
@@ -227,6 +227,7 @@ small_attention_mma_kernel(const __half *qkv, const int8_t *mask, __half *contex
     __shared__ __align__(16) __half s_v[SMAX][LD];
     __shared__ __align__(8) float s_madd[SMAX];
     __shared__ int s_last[SMAX / 32];
+    __shared__ __align__(16) __half s_w[SMAX / 16 / STRIPS][16][LD];   // per warp: a Q strip in, a context strip out
     const int b = blockIdx.x / heads;
     const int h = blockIdx.x - b * heads;
     const int lane = threadIdx.x & 31;
@@ -235,23 +236,20 @@ small_attention_mma_kernel(const __half *qkv, const int8_t *mask, __half *contex
     const size_t row_stride = 3 * (size_t) hidden;
     const __half *base = qkv + (size_t) b * seq * row_stride + (size_t) h * D;
 
-    // the Q rows of this warp's strips go straight into A-operand registers (rows g and g + 8, four
-    // 16-column steps); rows at and beyond seq are zeros and their results are dropped
-    uint32_t qa[STRIPS][D / 16][4];
+    // A strip of 16 Q rows is 2 KB: four 16-byte vectors per lane (vector lane + 32 u = chunk (lane & 7) of row
+    // lane / 8 + 4 u), read as whole 128-byte rows, passed through this warp's own 16-row buffer and picked up
+    // as A-operand fragments by ldmatrix. Rows at and beyond seq are zeros and their results are dropped. The
+    // first strip's vectors are in flight during the staging of K and V, the next strip's during the products.
+    const int qrow = lane >> 3, qcol = (lane & 7) * 8;
+    uint4 qv[4];
+    auto load_q = [&](int m0) {
 #pragma unroll
-    for (int s = 0; s < STRIPS; ++s) {
-        const int m0 = 16 * (warp + WARPS * s);
-        const bool live0 = m0 + g < seq, live1 = m0 + g + 8 < seq;
-        const __half *q0 = base + (size_t) (m0 + g) * row_stride + 2 * t;
-        const __half *q1 = q0 + 8 * row_stride;
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-            qa[s][kk][0] = live0 ? __ldg(reinterpret_cast<const uint32_t *>(q0 + 16 * kk)) : 0u;
-            qa[s][kk][1] = live1 ? __ldg(reinterpret_cast<const uint32_t *>(q1 + 16 * kk)) : 0u;
-            qa[s][kk][2] = live0 ? __ldg(reinterpret_cast<const uint32_t *>(q0 + 16 * kk + 8)) : 0u;
-            qa[s][kk][3] = live1 ? __ldg(reinterpret_cast<const uint32_t *>(q1 + 16 * kk + 8)) : 0u;
+        for (int u = 0; u < 4; ++u) {
+            const int j = m0 + qrow + 4 * u;
+            qv[u] = j < seq ? __ldg(reinterpret_cast<const uint4 *>(base + (size_t) j * row_stride + qcol)) : make_uint4(0u, 0u, 0u, 0u);
         }
-    }
+    };
+    load_q(16 * warp);
     // additive mask terms; for long sequences also the key extent of this sequence: one past its last kept key.
     // Keys from there on are all masked: their probabilities are exactly 0 (exp of about -10000 below the
     // row's largest score), so they are neither loaded nor multiplied. No kept key at all: every key counts.
@@ -313,6 +311,21 @@ small_attention_mma_kernel(const __half *qkv, const int8_t *mask, __half *contex
         if (m0 >= seq) {
             break;   // the strips of a warp ascend
         }
+        uint32_t qa[D / 16][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            *reinterpret_cast<uint4 *>(&s_w[warp][qrow + 4 * u][qcol]) = qv[u];
+        }
+        __syncwarp();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            // tiles: rows 0-7 | rows 8-15 at columns 16 kk, then the same rows at columns 16 kk + 8
+            ldmatrix_x4(qa[kk], &s_w[warp][lane & 15][16 * kk + 8 * (lane >> 4)]);
+        }
+        if (s + 1 < STRIPS) {
+            load_q(16 * (warp + WARPS * (s + 1)));
+        }
+        __syncwarp();   // the buffer is free again: the context strip goes through it below
         // scores of the strip: S[16, SMAX] = Q[16, 64] . K^T; sc[n][0] = row g, sc[n][1] = row g + 8 of tile n
         float2 sc[NT][2];
 #pragma unroll
@@ -329,8 +342,8 @@ small_attention_mma_kernel(const __half *qkv, const int8_t *mask, __half *contex
                 uint32_t kb[4];
                 // tiles: keys 8n..8n+7 at columns 16 kk and 16 kk + 8, then keys 8n+8..8n+15 likewise
                 ldmatrix_x4(kb, &s_k[8 * n + (lane & 7) + 8 * (lane >> 4)][16 * kk + 8 * ((lane >> 3) & 1)]);
-                mma_16x8x16(sc[n], qa[s][kk], kb[0], kb[1]);
-                mma_16x8x16(sc[n + 1], qa[s][kk], kb[2], kb[3]);
+                mma_16x8x16(sc[n], qa[kk], kb[0], kb[1]);
+                mma_16x8x16(sc[n + 1], qa[kk], kb[2], kb[3]);
             }
         }
 
@@ -418,17 +431,22 @@ small_attention_mma_kernel(const __half *qkv, const int8_t *mask, __half *contex
                 mma_16x8x16(o[n + 1], a, vb[2], vb[3]);
             }
         }
-        __half *out0 = context + ((size_t) b * seq + m0 + g) * hidden + (size_t) h * D + 2 * t;
-        __half *out1 = out0 + 8 * (size_t) hidden;
+        // the context strip: through the warp's buffer, so that it leaves as whole 128-byte rows
 #pragma unroll
         for (int n = 0; n < D / 8; ++n) {
-            if (m0 + g < seq) {
-                *reinterpret_cast<__half2 *>(out0 + 8 * n) = __float22half2_rn(o[n][0]);
-            }
-            if (m0 + g + 8 < seq) {
-                *reinterpret_cast<__half2 *>(out1 + 8 * n) = __float22half2_rn(o[n][1]);
+            *reinterpret_cast<__half2 *>(&s_w[warp][g][8 * n + 2 * t]) = __float22half2_rn(o[n][0]);
+            *reinterpret_cast<__half2 *>(&s_w[warp][g + 8][8 * n + 2 * t]) = __float22half2_rn(o[n][1]);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = m0 + qrow + 4 * u;
+            if (j < seq) {
+                *reinterpret_cast<uint4 *>(context + ((size_t) b * seq + j) * hidden + (size_t) h * D + qcol) =
+                    *reinterpret_cast<const uint4 *>(&s_w[warp][qrow + 4 * u][qcol]);
             }
         }
+        __syncwarp();   // before the next strip's Q rows overwrite the buffer
     }
 }
 
@@ -775,8 +793,8 @@ int small_attention(const T *qkv, const int8_t *mask, int batch, int seq, int he
         return CUBK_OK;
     }
     if constexpr (sizeof(T) == 2) {
-        // 16-byte vectors of K | V rows (their strides are multiples of 128 bytes), 4-byte loads and stores
-        if ((reinterpret_cast<uintptr_t>(qkv) & 15u) == 0 && (reinterpret_cast<uintptr_t>(context) & 3u) == 0) {
+        // 16-byte vectors of Q | K | V and context rows (their strides are multiples of 128 bytes)
+        if ((reinterpret_cast<uintptr_t>(qkv) & 15u) == 0 && (reinterpret_cast<uintptr_t>(context) & 15u) == 0) {
             const unsigned blocks = (unsigned) (batch * heads);
             if (seq <= 32) {
                 small_attention_mma_kernel<32, 1><<<blocks, 64, 0, stream>>>(qkv, mask, context, seq, heads, hidden, scale);

@@ -188,7 +188,7 @@ int cubk_masked_softmax_extents_f16(const void *scores, const int8_t *mask, cons
  * never reach device memory.
  * qkv [batch * seq, 3 * hidden] holds per token Q | K | V (head h at columns 64 * h of each part); mask int8
  * [batch, seq] over the keys or NULL; context [batch * seq, hidden]. hidden must be 64 * heads.
- *   _f16, seq <= 128, qkv on a 16-byte and context on a 4-byte boundary: warp-level matrix instructions
+ *   _f16, seq <= 128, qkv and context on 16-byte boundaries: warp-level matrix instructions
  *     (binary16 operands, float32 accumulators), a block per (sequence, head), a strip of 16 query rows per warp
  *     kept in registers from the scores to the context. Past 64 positions the kernel finds each sequence's last
  *     kept key and neither loads nor multiplies the keys behind it (their probabilities are exactly 0; where
